@@ -1,0 +1,379 @@
+#!/usr/bin/env python
+"""Benchmark of the blockwise masked attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl ours|reference]
+
+A step is one forward + backward pass of ``masked_attention_via_map`` over one batch of
+synthetic input.  The metric is attention TFLOP/s counted on non-empty (full + partial) blocks
+only: forward 4*bq*bk*d per block, backward 2.5x that.  With N > 1 (torchrun, one rank per GPU)
+every rank runs the same per-GPU batch on its own data (batch x head shards need no
+collective): weak scaling, value = total FLOPs of all ranks / max-over-ranks time.
+
+``--impl reference`` times the CPU restatement of the reference algorithm (oracle/, torch CPU,
+all host threads) on a bounded sample of the same workload; rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import numpy as np
+import torch
+
+METRIC = "attention_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+
+WORKLOADS = {
+    # BASELINE.json configs[1]: the dense-causal reference shape the metric is quoted on
+    "c2": dict(B=8, L=4096, H=32, d=128, bs=128, mask="causal", dtype="bf16", qkv_scale="rsqrt_d",
+               desc="causal bf16 B=8 L=4096 H=32 d=128 block_size=128"),
+    # headline target shape of the north star (bf16 causal, L=8192, d=128)
+    "t0": dict(B=4, L=8192, H=32, d=128, bs=128, mask="causal", dtype="bf16", qkv_scale="one",
+               desc="causal bf16 B=4 L=8192 H=32 d=128 block_size=128"),
+    "c3": dict(B=4, L=8192, H=16, d=128, bs=128, mask="sliding256", dtype="bf16", qkv_scale="one",
+               desc="sliding window |q-k|<=256 bf16 B=4 L=8192 H=16 d=128 window_size=(256,256) block_size=128"),
+    "c4": dict(B=4, L=16384, H=16, d=128, bs=128, mask="documents", dtype="bf16", qkv_scale="one",
+               desc="packed documents (segments 256..4096) & causal, bf16 B=4 L=16384 H=16 d=128"),
+    "c1": dict(B=2, L=128, H=8, d=64, bs=32, mask="causal", dtype="f32", qkv_scale="one",
+               desc="causal fp32 B=2 L=128 H=8 d=64 block_size=32"),
+}
+
+
+def synth(shape, seed, dtype, scale=1.0, device="cpu", pin=False):
+    """Seeded N(0,1) tensors: numpy PCG64(seed) -> float32 -> dtype (the configs' definition)."""
+    x = np.random.Generator(np.random.PCG64(seed)).standard_normal(shape, dtype=np.float32)
+    t = torch.from_numpy(x)
+    if scale != 1.0:
+        t = t * scale
+    t = t.to(dtype)
+    if pin:
+        t = t.pin_memory()
+    return t.to(device) if device != "cpu" else t
+
+
+def document_segments(B, L, seed=4, lo=256, hi=4096):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    seg = np.zeros((B, L), dtype=np.int32)
+    for b in range(B):
+        pos, sid = 0, 0
+        while pos < L:
+            n = int(rng.integers(lo, hi + 1))
+            seg[b, pos:pos + n] = sid
+            pos += n
+            sid += 1
+    return seg
+
+
+def mask_kwargs(w, masks_mod, B=None, L=None):
+    B, L = B or w["B"], L or w["L"]
+    if w["mask"] == "causal":
+        return dict(is_causal=True, block_size=w["bs"])
+    if w["mask"] == "sliding256":
+        return dict(mask_fn=masks_mod.sliding_window_mask(256, 256), window_size=(256, 256), block_size=w["bs"])
+    if w["mask"] == "documents":
+        return dict(mask_fn=masks_mod.document_mask(document_segments(B, L), causal=True), block_size=w["bs"])
+    raise KeyError(w["mask"])
+
+
+def torch_dtype(name):
+    return {"bf16": torch.bfloat16, "f32": torch.float32}[name]
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        # keep the samples taken under load (the upper half of the observed clocks)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def flops_of(lists_tensors, w_bs, d, B, H):
+    """(fwd, fwd+bwd) FLOPs counted on non-empty blocks from the compiled block lists."""
+    n = lists_tensors["kv_num_blocks"].sum(dtype=torch.int64) + lists_tensors["full_kv_num_blocks"].sum(dtype=torch.int64)
+    lb, lh = lists_tensors["kv_num_blocks"].shape[:2]
+    blocks = int(n) * (B // lb) * (H // lh)
+    fwd = 4.0 * w_bs * w_bs * d * blocks
+    return fwd, 3.5 * fwd, blocks
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        j = json.loads(p.read_text())
+        return j.get("bf16_tflops_sustained", 1385.6), j.get("bf16_tflops", 1648.3), j.get("hbm_gbs", 6548.8), "measured"
+    return 1400.0, 1590.0, 6650.0, "fallback"
+
+
+def cpu_reference_run(w, steps, warmup, threads=None):
+    """Times the CPU restatement of the reference (oracle/attention_oracle.py, torch CPU) on a
+    bounded sample: one (batch, head) slice of the workload at full sequence length."""
+    from oracle import attention_oracle as ao
+    from jaxmodules_b200 import masks as M
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    Bs, Hs = 1, 1
+    L, d = w["L"], w["d"]
+    dt = torch_dtype(w["dtype"])
+    scale = 1 / math.sqrt(d) if w["qkv_scale"] == "rsqrt_d" else 1.0
+    Q, K, V = (synth((Bs, L, Hs, d), s, dt, scale) for s in (0, 1, 2))
+    dO = synth((Bs, L, Hs, d), 3, torch.float32)
+    kw = mask_kwargs(w, M, B=Bs, L=L)
+    # useful FLOPs of the slice (non-empty 128-blocks), from a dense evaluation of the mask per block row
+    mask_fn = ao.canonical_mask_fn(kw.get("mask_fn"), kw.get("is_causal", False))
+    bs = w["bs"]
+    blocks = 0
+    for i in range(L // bs):
+        row = ao.eval_mask_grid(mask_fn, Bs, Hs, np.arange(i * bs, (i + 1) * bs), np.arange(L))
+        if kw.get("window_size") is not None:
+            lb, rb = ao.window_blocks(kw["window_size"], bs)
+            s = ao.window_start(i, lb, rb, L // bs)
+            row[..., : s * bs] = False
+            row[..., (s + lb + rb) * bs:] = False
+        blocks += int(row.reshape(Bs, Hs, bs, L // bs, bs).any(axis=(2, 4)).sum())
+    flops = 3.5 * 4.0 * bs * bs * d * blocks
+    times = []
+    for i in range(warmup + steps):
+        t = time.perf_counter()
+        ao.masked_attention_via_map(Q, K, V, dO=dO, **kw)
+        if i >= warmup:
+            times.append(time.perf_counter() - t)
+    sec = float(np.mean(times))
+    return dict(value=flops / sec / 1e12, seconds_per_step=sec, cores=threads,
+                sample=f"B=1,H=1 slice of the workload at full L={L} (fwd+bwd of the reference algorithm, "
+                       f"which visits every block; FLOPs counted on the {blocks} non-empty blocks only)")
+
+
+def run_reference(args, w, rank):
+    if rank != 0:
+        return
+    r = cpu_reference_run(w, steps=max(1, min(args.steps, 3)), warmup=min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": max(1, min(args.steps, 3)), "warmup": min(args.warmup, 1), "ms_per_step": r["seconds_per_step"] * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": w["desc"], "note": "reference algorithm restated on CPU (JAX is not installed on this box)"},
+        "cpu_baseline": {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+        "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, w, rank)
+        return
+
+    import jaxmodules_b200 as jm
+    from jaxmodules_b200 import _native as nat, attention as A, masks as M
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    warmup = max(args.warmup, 3)
+
+    B, L, H, d = w["B"], w["L"], w["H"], w["d"]
+    dt = torch_dtype(w["dtype"])
+    scale = 1 / math.sqrt(d) if w["qkv_scale"] == "rsqrt_d" else 1.0
+    # every rank owns its own batch (seeds offset by rank): batch x head shards, no collective
+    hQ, hK, hV = (synth((B, L, H, d), 10 * rank + s, dt, scale, pin=True) for s in (0, 1, 2))
+    hdO = synth((B, L, H, d), 10 * rank + 3, torch.float32, pin=True)
+    Q, K, V = (x.to(dev).requires_grad_(True) for x in (hQ, hK, hV))
+    dO = hdO.to(dev)
+    kw = mask_kwargs(w, M)
+
+    def step():
+        O = jm.masked_attention_via_map(Q, K, V, **kw)
+        Q.grad = K.grad = V.grad = None
+        O.backward(dO)
+        return O
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # FLOP count from the block lists the kernels actually walk
+    be, tq, tk = A.plan(Q, K, V)
+    terms = M.MaskTerms(causal=True) if kw.get("is_causal") else M.terms_from_mask_fn(kw["mask_fn"], B, H, L, L)
+    if kw.get("window_size") is not None:
+        bs = w["bs"]
+        lb, rb = (kw["window_size"][0] + bs - 1) // bs, 1 + (kw["window_size"][1] + bs - 1) // bs
+        terms = terms.merged(M.MaskTerms(window=(bs, lb, rb, L // bs)))
+    from jaxmodules_b200.block_mask import compile_block_lists
+    dm = M.to_device_mask(terms, L, L, dev)
+    _, lt = compile_block_lists(dm, B, H, L, L, tq, tk, dev, q_side=False)
+    fwd_flops, step_flops, blocks = flops_of(lt, tq, d, B, H)
+
+    for _ in range(warmup):
+        step()
+    barrier()
+
+    sink = {}
+    A.set_profile_sink(sink)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = nat.lib().bma_launch_count()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for _ in range(args.steps):
+        step()
+    t1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    launches = nat.lib().bma_launch_count() - launches0
+    A.set_profile_sink(None)
+    ms_total = t0.elapsed_time(t1)
+    per_kernel = {k: float(np.mean([a.elapsed_time(b) for a, b in v])) for k, v in sink.items()}
+
+    # end to end through the public API with host buffers (H2D of inputs, D2H of results inside the timed region)
+    e2e = None
+    if not args.no_e2e:
+        outs = [torch.empty((B, L, H, d), dtype=torch.float32).pin_memory()] + \
+               [torch.empty((B, L, H, d), dtype=dt).pin_memory() for _ in range(3)]
+
+        def e2e_step():
+            q, k, v = (x.to(dev, non_blocking=True).requires_grad_(True) for x in (hQ, hK, hV))
+            g = hdO.to(dev, non_blocking=True)
+            o = jm.masked_attention_via_map(q, k, v, **kw)
+            o.backward(g)
+            for dst, src in zip(outs, (o.detach(), q.grad, k.grad, v.grad)):
+                dst.copy_(src, non_blocking=True)
+
+        e2e_steps = max(2, min(args.steps, 5))
+        e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / e2e_steps
+        h2d = sum(x.numel() * x.element_size() for x in (hQ, hK, hV, hdO))
+        d2h = sum(x.numel() * x.element_size() for x in outs)
+        e2e = (e2e_ms, h2d, d2h)
+
+    ms_step = ms_total / args.steps
+    if dist is not None:
+        t = torch.tensor([ms_step, e2e[0] if e2e else 0.0], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, e2e_ms_max = float(t[0]), float(t[1])
+        if e2e:
+            e2e = (e2e_ms_max, e2e[1], e2e[2])
+
+    if rank == 0:
+        sustained, burst, hbm, peak_kind = peaks()
+        total_flops = step_flops * world
+        bwd_ms = per_kernel.get("bwd")
+        fwd_ms = per_kernel.get("fwd")
+        bwd_tf = (step_flops - fwd_flops) / (bwd_ms * 1e-3) / 1e12 if bwd_ms else None
+        fwd_tf = fwd_flops / (fwd_ms * 1e-3) / 1e12 if fwd_ms else None
+        traffic_path = ROOT / "profiles" / "traffic.json"
+        traffic = None
+        if traffic_path.exists():
+            traffic = json.loads(traffic_path.read_text()).get(f"{args.workload}:bwd")
+        line = {
+            "metric": METRIC, "value": total_flops / (ms_step * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": w["desc"], "per_gpu_batch": B, "global_batch": B * world,
+                       "parallelism": f"batch x head shards, {world} GPU(s), no collective",
+                       "backend": {1: "simt", 2: "tcgen05"}.get(be, str(be)), "tile": tq, "nonempty_blocks_per_gpu": blocks,
+                       "l2": "inputs (Q,K,V,dO > 1 GB) exceed the 126 MB L2; no flush needed",
+                       "flop_model": "fwd 4*bq*bk*d per non-empty block, bwd 2.5x fwd"},
+            "fwd_tflops": fwd_tf, "bwd_tflops": bwd_tf,
+            "kernel_ms": per_kernel,
+            "roofline": {"bound": "tensor", "kernel": "backward (dQ/dK/dV)", "achieved": bwd_tf, "peak": sustained,
+                         "unit": "TFLOP/s", "frac": (bwd_tf / sustained) if bwd_tf else None, "traffic": traffic,
+                         "peak_kind": f"{peak_kind} sustained dense bf16 (kernel timed inside a long step)"},
+            "roofline_fwd": {"bound": "tensor", "kernel": "forward", "achieved": fwd_tf, "peak": sustained, "unit": "TFLOP/s",
+                             "frac": (fwd_tf / sustained) if fwd_tf else None},
+            "clocks": clocks, "gpu_launches": int(launches),
+        }
+        if e2e:
+            line["e2e"] = {"value": total_flops / (e2e[0] * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e[0],
+                           "h2d_bytes_per_step": e2e[1], "d2h_bytes_per_step": e2e[2]}
+        if world == 1 and not args.no_cpu_baseline:
+            r = cpu_reference_run(w, steps=1, warmup=0)
+            line["cpu_baseline"] = {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port",
+                                    "sample": r["sample"], "seconds": r["seconds_per_step"]}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

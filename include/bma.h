@@ -1,0 +1,196 @@
+/*
+ * bma.h — C ABI of the B200-native blockwise masked attention library (libbma.so).
+ *
+ * The reference (acutkosky/jaxmodules) is pure Python on JAX and has no native boundary of
+ * its own; the seam this ABI replaces is the body of the custom_vjp triple
+ *   _masked_attention_via_map       jaxmodules/attention.py:180-241   (primal)
+ *   _masked_attention_via_map_fwd   jaxmodules/attention.py:244-264   (vjp forward rule)
+ *   _masked_attention_via_map_bwd   jaxmodules/attention.py:266-342   (vjp backward rule)
+ * and the array builder behind create_block_mask, jaxmodules/block_mask.py:411-498.
+ * Each entry point below names the reference code it stands in for.
+ *
+ * Conventions
+ *   - plain C types only; every function returns an int status (BMA_OK == 0, negative =
+ *     rejected arguments / host-side failure, positive = a device-side check tripped) and
+ *     never throws, exits or synchronises the device;
+ *   - the caller owns every buffer (inputs, outputs, workspace); all pointers are device
+ *     pointers on the current device unless stated otherwise; the mask/args structs
+ *     themselves are host memory and are copied at call time;
+ *   - work is enqueued on the stream that is passed (a cudaStream_t cast to void*);
+ *   - tensors are [B, L, H, d] with d contiguous and explicit element strides for B, L, H.
+ */
+#ifndef BMA_H_
+#define BMA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* bma_stream_t; /* cudaStream_t */
+
+/* ---- status codes ------------------------------------------------------------------ */
+enum {
+  BMA_OK = 0,
+  BMA_ERR_ARG = -1,         /* null pointer, negative size, inconsistent shapes           */
+  BMA_ERR_UNSUPPORTED = -2, /* valid request that no kernel covers (dtype, head dim ...)   */
+  BMA_ERR_WORKSPACE = -3,   /* workspace missing or smaller than *_workspace_bytes()       */
+  BMA_ERR_CUDA = -4,        /* a CUDA runtime / driver call failed; see bma_error_string   */
+  BMA_ERR_LIMIT = -5,       /* size beyond a documented fixed limit                        */
+  BMA_ERR_DEVICE_CHECK = 1  /* a bounded wait or bounds check inside a kernel gave up      */
+};
+
+enum { BMA_DTYPE_F32 = 0, BMA_DTYPE_BF16 = 1 };
+
+/* ---- mask description ----------------------------------------------------------------
+ * Device-evaluable form of the reference's mask_fn(b, h, q, k) (jaxmodules/attention.py:
+ * 368-372, 404-419, 437).  The predicate is the AND of every enabled term; with flags == 0
+ * every (q, k) inside the valid box is allowed.
+ *   gq = q + q_offset, gk = k + k_offset          (offsets are 0 except for sequence shards)
+ *   always      : q < q_valid  &&  k < k_valid                       (attention.py:437)
+ *   CAUSAL      : gk <= gq                                           (attention.py:414)
+ *   BAND        : gq - band_left <= gk <= gq + band_right
+ *   BLOCK_WINDOW: the key-block window of window_size (attention.py:161-167, 199-204):
+ *                 i = gq / win_block, s = min(max(0, i - win_left), win_nblk - win_left - win_right),
+ *                 s*win_block <= gk < (s + win_left + win_right)*win_block
+ *   SEGMENT     : seg_q[b*seg_q_stride + gq] == seg_k[b*seg_k_stride + gk]
+ *   BITMAP      : bit (gk & 31) of bitmap[((b%bitmap_B)*bitmap_H + h%bitmap_H)*bitmap_q + gq)*bitmap_words + gk/32]
+ *                 (an arbitrary host-evaluated mask_fn; h is the QUERY head, attention.py:72-73)
+ */
+enum {
+  BMA_MASK_CAUSAL = 1,
+  BMA_MASK_BAND = 2,
+  BMA_MASK_BLOCK_WINDOW = 4,
+  BMA_MASK_SEGMENT = 8,
+  BMA_MASK_BITMAP = 16
+};
+
+typedef struct bma_mask_spec {
+  int32_t flags;
+  int32_t q_valid, k_valid;
+  int32_t q_offset, k_offset;
+  int32_t band_left, band_right;
+  int32_t win_block, win_left, win_right, win_nblk;
+  int32_t bitmap_B, bitmap_H, bitmap_q, bitmap_words;
+  int32_t reserved_;
+  const int32_t* seg_q;
+  const int32_t* seg_k;
+  int64_t seg_q_stride, seg_k_stride;
+  const uint32_t* bitmap;
+} bma_mask_spec;
+
+/* ---- block lists ---------------------------------------------------------------------
+ * The arrays of the reference's BlockMask (jaxmodules/block_mask.py:17-42): per q-block row
+ * the number and the indices of PARTIAL kv blocks (kv_*), of FULL kv blocks (full_kv_*), and
+ * the same per kv-block column (q_*, full_q_*).  Index rows have full width (NKV resp. NQ):
+ * set blocks ascending, then unset blocks ascending, exactly what
+ * argsort(-blocks) yields (block_mask.py:428-430).  B and H may be 1 to broadcast
+ * (attention.py:521-522).  All int32.
+ */
+typedef struct bma_block_lists {
+  int32_t B, H, NQ, NKV;
+  int32_t q_block, kv_block;
+  int32_t* kv_num;       /* [B,H,NQ]      */
+  int32_t* kv_idx;       /* [B,H,NQ,NKV]  */
+  int32_t* full_kv_num;  /* [B,H,NQ]      */
+  int32_t* full_kv_idx;  /* [B,H,NQ,NKV]  */
+  int32_t* q_num;        /* [B,H,NKV]     may be NULL together with the next three */
+  int32_t* q_idx;        /* [B,H,NKV,NQ]  */
+  int32_t* full_q_num;   /* [B,H,NKV]     */
+  int32_t* full_q_idx;   /* [B,H,NKV,NQ]  */
+} bma_block_lists;
+
+/* ---- tensors ------------------------------------------------------------------------- */
+typedef struct bma_tensor {
+  void* ptr;
+  int64_t stride_b, stride_l, stride_h; /* in elements; innermost (d) stride is 1 */
+  int32_t dtype;                        /* BMA_DTYPE_* */
+  int32_t reserved_;
+} bma_tensor;
+
+typedef struct bma_attn_args {
+  int32_t B, N, L, Hq, Hkv, d;
+  float scale;      /* 1/sqrt(d) for default_kernel, jaxmodules/attention.py:50 */
+  int32_t backend;  /* BMA_BACKEND_AUTO or a forced backend (tests) */
+  bma_tensor q, k, v;      /* inputs                                             */
+  bma_tensor o;            /* [B,N,Hq,d] output (fwd) / input (bwd)               */
+  float* lse;              /* [B,Hq,N] natural-log sum of exp; -inf for empty rows */
+  bma_tensor d_o;          /* cotangent of o (bwd)                               */
+  float* delta;            /* [B,Hq,N] rowsum(dO*O) (bwd)                        */
+  bma_tensor dq, dk, dv;   /* outputs (bwd), dtype of q/k/v                      */
+} bma_attn_args;
+
+enum { BMA_BACKEND_AUTO = 0, BMA_BACKEND_SIMT = 1, BMA_BACKEND_TCGEN05 = 2 };
+
+/* ---- entry points -------------------------------------------------------------------- */
+
+/* Library / ABI version (major*1000 + minor). */
+int bma_version(void);
+
+/* Number of CUDA kernels this library has launched in the calling process (diagnostics for
+ * benchmarks; no counterpart in the reference). */
+unsigned long long bma_launch_count(void);
+
+/* Static text for a status code; for BMA_ERR_CUDA the text of the last CUDA error seen by
+ * the calling thread is appended. */
+const char* bma_error_string(int status);
+
+/* Scratch bytes bma_mask_compile needs for a mask of B x H x NQ x NKV blocks. */
+size_t bma_mask_compile_workspace_bytes(const bma_mask_spec* spec, int32_t B, int32_t H,
+                                        int32_t NQ, int32_t NKV);
+
+/* Block-mask compilation: classifies every (q-block, kv-block) of the mask as empty /
+ * partial / full (partial = any ^ all, full = all) and writes the BlockMask arrays.
+ * Replaces create_block_mask + BlockMask.from_blocks + get_sparse_{kv,q}_data_from_blocks,
+ * jaxmodules/block_mask.py:454-498, 227-275, 411-451.  `B`,`H` are the mask's logical batch
+ * and query-head counts; lists->B / lists->H are the extents actually written (1 only if
+ * the spec does not depend on that index).  NQ = ceil(q_valid / q_block) etc. are taken
+ * from `lists`; elements outside the valid box count as masked. */
+int bma_mask_compile(const bma_mask_spec* spec, int32_t B, int32_t H,
+                     const bma_block_lists* lists, void* workspace, size_t workspace_bytes,
+                     bma_stream_t stream);
+
+/* Which backend and tile sizes bma_attn_fwd / bma_attn_bwd will use for these arguments;
+ * the block lists passed to them must be compiled at exactly these block sizes. */
+int bma_attn_plan(const bma_attn_args* args, int32_t* backend, int32_t* q_tile, int32_t* kv_tile);
+
+/* Forward: O = softmax_masked(Q K^T * scale) V and lse, visiting only listed blocks and
+ * applying the element predicate only on partial ones.  Replaces the lax.map/lax.scan
+ * nest of jaxmodules/attention.py:52-177, 219-241. */
+int bma_attn_fwd(const bma_attn_args* args, const bma_mask_spec* spec,
+                 const bma_block_lists* lists, bma_stream_t stream);
+
+/* Backward preprocess: delta = rowsum(dO * O); when d_o_bf16 is non-NULL also writes a
+ * bf16 copy of dO with the layout/strides of args->o (the cotangent arrives in float32
+ * because the reference returns O in float32, jaxmodules/attention.py:173).  Part of what
+ * jax.vjp derives at jaxmodules/attention.py:320-321. */
+int bma_attn_bwd_preprocess(const bma_attn_args* args, void* d_o_bf16, bma_stream_t stream);
+
+/* Scratch bytes bma_attn_bwd needs (float32 dQ accumulator when the tensor-core backend
+ * accumulates dQ with atomics; 0 for the SIMT backend). */
+size_t bma_attn_bwd_workspace_bytes(const bma_attn_args* args);
+
+/* Backward: dQ, dK, dV from (Q, K, V, O, dO, lse, delta).  Replaces
+ * _masked_attention_via_map_bwd, jaxmodules/attention.py:266-342.  `lists` must carry the
+ * q-side arrays. */
+int bma_attn_bwd(const bma_attn_args* args, const bma_mask_spec* spec,
+                 const bma_block_lists* lists, void* workspace, size_t workspace_bytes,
+                 bma_stream_t stream);
+
+/* Merge of two partial attention results over disjoint key sets (sequence-sharded
+ * execution; no counterpart in the reference, which is single-device):
+ *   lse = log(exp(lse_a) + exp(lse_b)),  o = exp(lse_a - lse) o_a + exp(lse_b - lse) o_b,
+ * written in place into (o_a, lse_a).  o_* are float32 [B,N,Hq,d] described by args->o
+ * (a) and args->d_o (b); lse_* by args->lse (a) and args->delta (b). */
+int bma_attn_merge(const bma_attn_args* args, bma_stream_t stream);
+
+/* Reads and clears the device-side status word that bounded waits / bounds checks write.
+ * Synchronises `stream`.  Returns BMA_OK or BMA_ERR_DEVICE_CHECK; *detail gets the code. */
+int bma_device_status(bma_stream_t stream, int32_t* detail);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BMA_H_ */

@@ -1,0 +1,266 @@
+"""``masked_attention_via_map`` with the reference's signature and error behaviour
+(jaxmodules/attention.py:347-455), executing on sm_100a CUDA kernels through the C ABI.
+
+Inputs are CUDA torch tensors ``[B, L, H, d]`` (or 3-D without the batch axis).  The result is
+differentiable (torch autograd) — the counterpart of the reference's ``jax.custom_vjp``
+(jaxmodules/attention.py:180, 244-345); the backward saves ``(Q, K, V, O, lse)`` instead of
+recomputing the forward.  There is no CPU or eager-PyTorch path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Callable, Optional, Tuple
+
+import torch
+
+from . import _native as nat
+from . import masks as _masks
+from .block_mask import compile_block_lists
+
+
+def default_kernel(q, k):
+    """Marker for the reference's default score ``exp(q.k / sqrt(d))``
+    (jaxmodules/attention.py:39-50).  The CUDA kernels implement exactly this kernel; the
+    function itself also evaluates it for host-side use."""
+    q, k = torch.as_tensor(q), torch.as_tensor(k)
+    return torch.exp(torch.dot(q, k) / math.sqrt(k.shape[-1]))
+
+
+def threshold_kernel(threshold: Optional[float] = None):
+    """jaxmodules/attention.py:18-36.  Not available on the CUDA path yet; passing the result
+    as ``kernel_fn`` raises NotImplementedError."""
+    def kernel_fn(q, k):
+        q, k = torch.as_tensor(q), torch.as_tensor(k)
+        dotp = torch.dot(q, k)
+        if threshold is not None:
+            dotp = dotp - threshold / math.sqrt(q.shape[0])
+        return torch.exp(dotp)
+    return kernel_fn
+
+
+_DTYPES = {torch.float32: nat.BMA_DTYPE_F32, torch.bfloat16: nat.BMA_DTYPE_BF16}
+
+
+def _tensor(t: Optional[torch.Tensor]) -> nat.Tensor:
+    out = nat.Tensor()
+    if t is None:
+        return out
+    if t.stride(-1) != 1:
+        raise ValueError("innermost dimension must be contiguous")
+    out.ptr = t.data_ptr()
+    out.stride_b, out.stride_l, out.stride_h = t.stride(0), t.stride(1), t.stride(2)
+    out.dtype = _DTYPES[t.dtype]
+    return out
+
+
+def _make_args(Q, K, V, backend=nat.BMA_BACKEND_AUTO) -> nat.AttnArgs:
+    a = nat.AttnArgs()
+    a.B, a.N, a.Hq, a.d = Q.shape
+    a.L, a.Hkv = K.shape[1], K.shape[2]
+    a.scale = 1.0 / math.sqrt(K.shape[-1])
+    a.backend = backend
+    a.q, a.k, a.v = _tensor(Q), _tensor(K), _tensor(V)
+    return a
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def plan(Q, K, V, backend=nat.BMA_BACKEND_AUTO):
+    """(backend, q_tile, kv_tile) the library will use for these tensors."""
+    a = _make_args(Q, K, V, backend)
+    be, tq, tk = C.c_int32(), C.c_int32(), C.c_int32()
+    nat.check(nat.lib().bma_attn_plan(C.byref(a), C.byref(be), C.byref(tq), C.byref(tk)), "bma_attn_plan")
+    return be.value, tq.value, tk.value
+
+
+class _Span:
+    """Optional CUDA-event bracket around one launch (used by the benchmark to time a single
+    kernel on the launching stream); a no-op when ``sink`` is None."""
+
+    def __init__(self, sink, key, device):
+        self.sink, self.key, self.device = sink, key, device
+
+    def __enter__(self):
+        if self.sink is not None:
+            self.t0 = torch.cuda.Event(enable_timing=True)
+            self.t1 = torch.cuda.Event(enable_timing=True)
+            self.t0.record(torch.cuda.current_stream(self.device))
+        return self
+
+    def __exit__(self, *exc):
+        if self.sink is not None:
+            self.t1.record(torch.cuda.current_stream(self.device))
+            self.sink.setdefault(self.key, []).append((self.t0, self.t1))
+        return False
+
+
+_profile_sink = None
+
+
+def set_profile_sink(sink):
+    """Install (or remove with None) a dict that collects (start, end) CUDA event pairs per
+    launch group: 'mask_compile', 'fwd', 'bwd_preprocess', 'bwd'."""
+    global _profile_sink
+    _profile_sink = sink
+
+
+def attention_forward(Q, K, V, terms: _masks.MaskTerms, *, out_dtype=torch.float32, backend=nat.BMA_BACKEND_AUTO,
+                      need_q_side: bool = False):
+    """One forward launch sequence: mask compile at the kernel's tile size, then attention.
+    Returns (O, lse, ctx) where ctx carries what the backward needs."""
+    lib = nat.lib()
+    dev = Q.device
+    B, N, Hq, d = Q.shape
+    L = K.shape[1]
+    with torch.cuda.device(dev):
+        a = _make_args(Q, K, V, backend)
+        be, tq, tk = plan(Q, K, V, backend)
+        dmask = _masks.to_device_mask(terms, N, L, dev)
+        with _Span(_profile_sink, "mask_compile", dev):
+            lists, lt = compile_block_lists(dmask, B, Hq, N, L, tq, tk, dev, q_side=need_q_side)
+        O = torch.empty((B, N, Hq, d), dtype=out_dtype, device=dev)
+        lse = torch.empty((B, Hq, N), dtype=torch.float32, device=dev)
+        a.o, a.lse = _tensor(O), lse.data_ptr()
+        with _Span(_profile_sink, "fwd", dev):
+            nat.check(lib.bma_attn_fwd(C.byref(a), C.byref(dmask.spec), C.byref(lists), _stream(dev)), "bma_attn_fwd")
+    ctx = dict(dmask=dmask, lists=lists, list_tensors=lt, backend=be)
+    return O, lse, ctx
+
+
+def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
+    """dQ, dK, dV through ``bma_attn_bwd_preprocess`` + ``bma_attn_bwd``."""
+    lib = nat.lib()
+    dev = Q.device
+    B, N, Hq, d = Q.shape
+    with torch.cuda.device(dev):
+        a = _make_args(Q, K, V, backend)
+        if dO.stride(-1) != 1:
+            dO = dO.contiguous()
+        delta = torch.empty((B, Hq, N), dtype=torch.float32, device=dev)
+        dQ, dK, dV = torch.empty_like(Q), torch.empty_like(K), torch.empty_like(V)
+        a.o, a.lse, a.d_o, a.delta = _tensor(O), lse.data_ptr(), _tensor(dO), delta.data_ptr()
+        a.dq, a.dk, a.dv = _tensor(dQ), _tensor(dK), _tensor(dV)
+        st = _stream(dev)
+        do_bf16 = None
+        if ctx["backend"] == nat.BMA_BACKEND_TCGEN05 and dO.dtype != torch.bfloat16:
+            do_bf16 = torch.empty((B, N, Hq, d), dtype=torch.bfloat16, device=dev)
+        with _Span(_profile_sink, "bwd_preprocess", dev):
+            nat.check(lib.bma_attn_bwd_preprocess(C.byref(a), do_bf16.data_ptr() if do_bf16 is not None else None, st),
+                      "bma_attn_bwd_preprocess")
+        if do_bf16 is not None:
+            a.d_o = _tensor(do_bf16)
+        ws_bytes = lib.bma_attn_bwd_workspace_bytes(C.byref(a))
+        ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=dev)
+        with _Span(_profile_sink, "bwd", dev):
+            nat.check(lib.bma_attn_bwd(C.byref(a), C.byref(ctx["dmask"].spec), C.byref(ctx["lists"]), ws.data_ptr(), ws_bytes, st),
+                      "bma_attn_bwd")
+    return dQ, dK, dV
+
+
+class _MaskedAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, Q, K, V, terms, out_dtype, backend):
+        need_grad = any(ctx.needs_input_grad[:3])
+        O, lse, fctx = attention_forward(Q, K, V, terms, out_dtype=out_dtype, backend=backend, need_q_side=need_grad)
+        ctx.save_for_backward(Q, K, V, O, lse)
+        ctx.fctx, ctx.backend = fctx, backend
+        ctx.mark_non_differentiable(lse)
+        return O, lse
+
+    @staticmethod
+    def backward(ctx, dO, _dlse):
+        Q, K, V, O, lse = ctx.saved_tensors
+        dQ, dK, dV = attention_backward(Q, K, V, O, lse, dO, ctx.fctx, ctx.backend)
+        return dQ, dK, dV, None, None, None
+
+
+def masked_attention_via_map(
+    Q: torch.Tensor,
+    K: torch.Tensor,
+    V: torch.Tensor,
+    *,
+    is_causal: bool = False,
+    kernel_fn: Callable = default_kernel,
+    mask_fn: Optional[Callable] = None,
+    block_size: Optional[int] = None,
+    window_size: Optional[Tuple[int, int]] = None,
+    out_dtype: Optional[torch.dtype] = None,
+    return_lse: bool = False,
+    backend: int = nat.BMA_BACKEND_AUTO,
+):
+    """Drop-in for jaxmodules/attention.py:347-455.
+
+    K, V: ``[B, L, Hkv, d]`` or ``[L, Hkv, d]``; Q: ``[B, N, Hq, d]`` or ``[N, Hq, d]``.
+    ``mask_fn(b, h, q, k)`` or ``mask_fn(h, q, k)``; ``is_causal`` excludes ``mask_fn``.
+    ``block_size`` / ``window_size`` keep the reference's meaning: the key window is a whole
+    number of ``block_size`` blocks, clamped at the sequence ends, applied on top of the mask
+    (jaxmodules/attention.py:161-167, 199-204); without ``window_size`` the result does not
+    depend on ``block_size``.  Rows without any allowed key return 0.
+
+    Extras (keyword-only, defaulting to the reference's behaviour): ``out_dtype`` — the
+    reference returns float32 for every input dtype, pass ``torch.bfloat16`` to halve the
+    output traffic; ``return_lse`` — also return the log-sum-exp ``[B, Hq, N]``.
+    """
+    if K.ndim not in (3, 4):
+        raise ValueError("K must have 3 or 4 dimensions")
+    if Q.ndim not in (3, 4):
+        raise ValueError("Q must have 3 or 4 dimensions")
+    if V.ndim not in (3, 4):
+        raise ValueError("V must have 3 or 4 dimensions")
+    assert K.ndim == Q.ndim and V.ndim == Q.ndim, "Q, K, and V must have the same number of dimensions"
+
+    added_batch_dim = Q.ndim == 3
+    if added_batch_dim:
+        Q, K, V = Q[None], K[None], V[None]
+
+    if is_causal and mask_fn is not None:
+        raise ValueError("cannot specify both 'is_causal' and 'mask_fn'!")
+    if kernel_fn is not default_kernel:
+        raise NotImplementedError("only default_kernel (exp(q.k/sqrt(d))) is implemented on the CUDA path")
+
+    assert K.shape[0] == Q.shape[0] == V.shape[0], "Q, K, and V must have the same batch dimension"
+    B, N, Hq, dq = Q.shape
+    _, L, Hk, d = K.shape
+    _, Lv, Hv, dv = V.shape
+    assert d == dq and Lv == L and dv == d, f"shape mismatch in K {tuple(K.shape)}, Q {tuple(Q.shape)} and V {tuple(V.shape)}"
+    assert Hq % Hk == 0, "Hq must be divisible by Hk"
+    assert Hv == Hk, "Hv must be equal to Hk"
+    if not (Q.is_cuda and K.is_cuda and V.is_cuda):
+        raise RuntimeError("masked_attention_via_map needs CUDA tensors; there is no CPU path")
+    if Q.dtype not in _DTYPES or K.dtype != Q.dtype or V.dtype != Q.dtype:
+        raise TypeError("Q, K, V must share dtype float32 or bfloat16")
+
+    if is_causal:
+        terms = _masks.MaskTerms(causal=True)
+    else:
+        terms = _masks.terms_from_mask_fn(mask_fn, B, Hq, N, L)
+
+    # Block geometry exactly as the reference derives it: padding only when N is not a
+    # multiple of block_size (jaxmodules/attention.py:426-434), kv blocks sized like q blocks
+    # (:155-158).  Nothing is physically padded; the kernels bound-check instead.
+    bs = N if block_size is None else int(block_size)
+    if bs <= 0:
+        raise ValueError("block_size must be positive")
+    if N % bs != 0:
+        Lp = L + bs - (L % bs)
+    else:
+        Lp = L
+        if L % bs != 0:
+            raise ValueError("number of keys must be a multiple of block_size when the number of queries is")
+    if window_size is not None:
+        left, right = window_size
+        lb = (left + bs - 1) // bs
+        rb = 1 + (right + bs - 1) // bs
+        nkb = Lp // bs
+        if lb + rb > nkb:
+            raise ValueError("window_size covers more blocks than there are key blocks")
+        terms = terms.merged(_masks.MaskTerms(window=(bs, lb, rb, nkb)))
+
+    fix = lambda t: t if t.stride(-1) == 1 else t.contiguous()
+    O, lse = _MaskedAttention.apply(fix(Q), fix(K), fix(V), terms, out_dtype or torch.float32, backend)
+    if added_batch_dim:
+        O, lse = O[0], lse[0]
+    return (O, lse) if return_lse else O

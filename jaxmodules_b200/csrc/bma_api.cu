@@ -1,0 +1,283 @@
+// extern "C" entry points of libbma.so: argument validation, backend choice, and the two
+// small HBM-bound kernels (backward preprocess, partial-result merge).
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <atomic>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace bma {
+
+// implemented in mask_compile.cu
+size_t mask_compile_workspace_bytes(const bma_mask_spec& spec, int B, int H, int NQ, int NKV);
+int mask_compile_validate(const bma_mask_spec& s, int B, int H, const bma_block_lists& l);
+int mask_compile_launch(const bma_mask_spec& spec, int B, int H, const bma_block_lists& l, void* workspace,
+                        cudaStream_t st);
+
+namespace {
+thread_local char g_err_text[512] = "";
+__device__ int g_device_status_word = 0;
+constexpr int kMaxDevices = 64;
+int* g_status_ptr[kMaxDevices] = {};
+std::mutex g_status_mutex;
+std::atomic<unsigned long long> g_launches{0};
+}  // namespace
+
+void count_launches(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+
+void set_last_cuda_error(cudaError_t e, const char* where) {
+  std::snprintf(g_err_text, sizeof(g_err_text), "CUDA error %d (%s) at %s", (int)e, cudaGetErrorString(e), where);
+  (void)cudaGetLastError();  // clear the sticky-less error so that later calls start clean
+}
+
+int* device_status_ptr() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  if (!g_status_ptr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_device_status_word);
+    if (e != cudaSuccess) { set_last_cuda_error(e, "cudaGetSymbolAddress(status)"); return nullptr; }
+    g_status_ptr[dev] = static_cast<int*>(p);
+  }
+  return g_status_ptr[dev];
+}
+
+namespace {
+
+// ---- backward preprocess: delta = rowsum(dO * O), optional bf16 copy of dO ---------------
+template <typename TO, typename TDO>
+__global__ void bwd_preprocess_kernel(bma_attn_args a, __nv_bfloat16* __restrict__ do_bf16) {
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = (int64_t)a.B * a.N * a.Hq;
+  const int warps = (blockDim.x >> 5);
+  for (int64_t r = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5); r < rows; r += (int64_t)gridDim.x * warps) {
+    const int h = (int)(r % a.Hq);
+    const int q = (int)((r / a.Hq) % a.N);
+    const int b = (int)(r / ((int64_t)a.Hq * a.N));
+    const TO* o = static_cast<const TO*>(a.o.ptr) + (int64_t)b * a.o.stride_b + (int64_t)q * a.o.stride_l + (int64_t)h * a.o.stride_h;
+    const TDO* g = static_cast<const TDO*>(a.d_o.ptr) + (int64_t)b * a.d_o.stride_b + (int64_t)q * a.d_o.stride_l + (int64_t)h * a.d_o.stride_h;
+    float acc = 0.f;
+    for (int c = lane; c < a.d; c += 32) {
+      const float gv = to_float(g[c]);
+      acc = fmaf(gv, to_float(o[c]), acc);
+      if (do_bf16) do_bf16[r * a.d + c] = __float2bfloat16_rn(gv);
+    }
+    for (int off = 16; off; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) a.delta[((int64_t)b * a.Hq + h) * a.N + q] = acc;
+  }
+}
+
+// ---- merge of two partial results over disjoint key sets ---------------------------------
+__global__ void merge_kernel(bma_attn_args a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = (int64_t)a.B * a.N * a.Hq;
+  const int warps = (blockDim.x >> 5);
+  for (int64_t r = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5); r < rows; r += (int64_t)gridDim.x * warps) {
+    const int h = (int)(r % a.Hq);
+    const int q = (int)((r / a.Hq) % a.N);
+    const int b = (int)(r / ((int64_t)a.Hq * a.N));
+    float* oa = static_cast<float*>(a.o.ptr) + (int64_t)b * a.o.stride_b + (int64_t)q * a.o.stride_l + (int64_t)h * a.o.stride_h;
+    const float* ob = static_cast<const float*>(a.d_o.ptr) + (int64_t)b * a.d_o.stride_b + (int64_t)q * a.d_o.stride_l + (int64_t)h * a.d_o.stride_h;
+    const int64_t li = ((int64_t)b * a.Hq + h) * a.N + q;
+    const float la = a.lse[li], lb = a.delta[li];
+    const float mx = fmaxf(la, lb);
+    float wa = 0.f, wb = 0.f, l = -INFINITY;
+    if (mx != -INFINITY) {
+      const float ea = expf(la - mx), eb = expf(lb - mx);
+      l = mx + logf(ea + eb);
+      wa = ea / (ea + eb);
+      wb = eb / (ea + eb);
+    }
+    for (int c = lane; c < a.d; c += 32) oa[c] = wa * oa[c] + wb * ob[c];
+    if (lane == 0) a.lse[li] = l;
+  }
+}
+
+int validate_tensor(const bma_tensor& t, bool required) {
+  if (!t.ptr) return required ? BMA_ERR_ARG : BMA_OK;
+  BMA_REQUIRE(t.dtype == BMA_DTYPE_F32 || t.dtype == BMA_DTYPE_BF16, BMA_ERR_UNSUPPORTED);
+  return BMA_OK;
+}
+
+int validate_common(const bma_attn_args* a) {
+  BMA_REQUIRE(a != nullptr, BMA_ERR_ARG);
+  BMA_REQUIRE(a->B > 0 && a->N > 0 && a->L > 0 && a->Hq > 0 && a->Hkv > 0 && a->d > 0, BMA_ERR_ARG);
+  BMA_REQUIRE(a->Hq % a->Hkv == 0, BMA_ERR_ARG);
+  BMA_REQUIRE(a->d <= 128, BMA_ERR_UNSUPPORTED);
+  BMA_REQUIRE(a->Hq <= 65535 && a->B <= 65535, BMA_ERR_LIMIT);
+  return BMA_OK;
+}
+
+int validate_lists(const bma_attn_args* a, const bma_block_lists* l, int tile, bool need_q_side) {
+  BMA_REQUIRE(l != nullptr, BMA_ERR_ARG);
+  BMA_REQUIRE(l->kv_num && l->kv_idx && l->full_kv_num && l->full_kv_idx, BMA_ERR_ARG);
+  BMA_REQUIRE(!need_q_side || (l->q_num && l->q_idx && l->full_q_num && l->full_q_idx), BMA_ERR_ARG);
+  BMA_REQUIRE(l->q_block == tile && l->kv_block == tile, BMA_ERR_ARG);
+  BMA_REQUIRE(l->NQ == ceil_div(a->N, tile) && l->NKV == ceil_div(a->L, tile), BMA_ERR_ARG);
+  BMA_REQUIRE((l->B == 1 || l->B == a->B) && (l->H == 1 || l->H == a->Hq), BMA_ERR_ARG);
+  return BMA_OK;
+}
+
+int pick_backend(const bma_attn_args* a) {
+  if (a->backend == BMA_BACKEND_SIMT) return BMA_BACKEND_SIMT;
+  if (sm100_supported(*a)) return BMA_BACKEND_TCGEN05;
+  if (a->backend == BMA_BACKEND_TCGEN05) return -1;
+  return BMA_BACKEND_SIMT;
+}
+
+int sm_count() {
+  int dev = 0, n = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n;
+}
+
+}  // namespace
+}  // namespace bma
+
+using namespace bma;
+
+extern "C" {
+
+int bma_version(void) { return 1000; }
+
+unsigned long long bma_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* bma_error_string(int status) {
+  switch (status) {
+    case BMA_OK: return "ok";
+    case BMA_ERR_ARG: return "invalid argument (null pointer, bad size or inconsistent shapes)";
+    case BMA_ERR_UNSUPPORTED: return "request not covered by any kernel (dtype / head dim / backend)";
+    case BMA_ERR_WORKSPACE: return "workspace missing or too small";
+    case BMA_ERR_CUDA: return g_err_text[0] ? g_err_text : "CUDA call failed";
+    case BMA_ERR_LIMIT: return "size beyond a fixed limit of the library";
+    case BMA_ERR_DEVICE_CHECK: return "a device-side bounded wait or bounds check gave up";
+    default: return "unknown status";
+  }
+}
+
+size_t bma_mask_compile_workspace_bytes(const bma_mask_spec* spec, int32_t B, int32_t H, int32_t NQ, int32_t NKV) {
+  if (!spec || B <= 0 || H <= 0 || NQ <= 0 || NKV <= 0) return 0;
+  return mask_compile_workspace_bytes(*spec, B, H, NQ, NKV);
+}
+
+int bma_mask_compile(const bma_mask_spec* spec, int32_t B, int32_t H, const bma_block_lists* lists, void* workspace,
+                     size_t workspace_bytes, bma_stream_t stream) {
+  BMA_REQUIRE(spec && lists, BMA_ERR_ARG);
+  int rc = mask_compile_validate(*spec, B, H, *lists);
+  if (rc != BMA_OK) return rc;
+  const size_t need = mask_compile_workspace_bytes(*spec, B, H, lists->NQ, lists->NKV);
+  BMA_REQUIRE(workspace != nullptr && workspace_bytes >= need, BMA_ERR_WORKSPACE);
+  return mask_compile_launch(*spec, B, H, *lists, workspace, static_cast<cudaStream_t>(stream));
+}
+
+int bma_attn_plan(const bma_attn_args* args, int32_t* backend, int32_t* q_tile, int32_t* kv_tile) {
+  int rc = validate_common(args);
+  if (rc != BMA_OK) return rc;
+  const int be = pick_backend(args);
+  BMA_REQUIRE(be > 0, BMA_ERR_UNSUPPORTED);
+  const int tile = be == BMA_BACKEND_TCGEN05 ? kSm100Tile : kSimtTile;
+  if (backend) *backend = be;
+  if (q_tile) *q_tile = tile;
+  if (kv_tile) *kv_tile = tile;
+  return BMA_OK;
+}
+
+int bma_attn_fwd(const bma_attn_args* args, const bma_mask_spec* spec, const bma_block_lists* lists,
+                 bma_stream_t stream) {
+  int rc = validate_common(args);
+  if (rc != BMA_OK) return rc;
+  BMA_REQUIRE(spec != nullptr, BMA_ERR_ARG);
+  if ((rc = validate_tensor(args->q, true)) || (rc = validate_tensor(args->k, true)) ||
+      (rc = validate_tensor(args->v, true)) || (rc = validate_tensor(args->o, true)))
+    return rc;
+  BMA_REQUIRE(args->q.dtype == args->k.dtype && args->k.dtype == args->v.dtype, BMA_ERR_UNSUPPORTED);
+  const int be = pick_backend(args);
+  BMA_REQUIRE(be > 0, BMA_ERR_UNSUPPORTED);
+  const int tile = be == BMA_BACKEND_TCGEN05 ? kSm100Tile : kSimtTile;
+  if ((rc = validate_lists(args, lists, tile, false))) return rc;
+  BMA_REQUIRE(spec->q_valid <= args->N && spec->k_valid <= args->L, BMA_ERR_ARG);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return be == BMA_BACKEND_TCGEN05 ? sm100_fwd(*args, *spec, *lists, st) : simt_fwd(*args, *spec, *lists, st);
+}
+
+int bma_attn_bwd_preprocess(const bma_attn_args* args, void* d_o_bf16, bma_stream_t stream) {
+  int rc = validate_common(args);
+  if (rc != BMA_OK) return rc;
+  if ((rc = validate_tensor(args->o, true)) || (rc = validate_tensor(args->d_o, true))) return rc;
+  BMA_REQUIRE(args->delta != nullptr, BMA_ERR_ARG);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t rows = (int64_t)args->B * args->N * args->Hq;
+  const int grid = (int)std::min<int64_t>((rows + 7) / 8, (int64_t)sm_count() * 16);
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(d_o_bf16);
+  const bool of = args->o.dtype == BMA_DTYPE_F32, gf = args->d_o.dtype == BMA_DTYPE_F32;
+  if (of && gf) bwd_preprocess_kernel<float, float><<<grid, 256, 0, st>>>(*args, out);
+  else if (of) bwd_preprocess_kernel<float, __nv_bfloat16><<<grid, 256, 0, st>>>(*args, out);
+  else if (gf) bwd_preprocess_kernel<__nv_bfloat16, float><<<grid, 256, 0, st>>>(*args, out);
+  else bwd_preprocess_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>(*args, out);
+  count_launches(1);
+  BMA_CUDA_TRY(cudaGetLastError());
+  return BMA_OK;
+}
+
+size_t bma_attn_bwd_workspace_bytes(const bma_attn_args* args) {
+  if (validate_common(args) != BMA_OK) return 0;
+  return pick_backend(args) == BMA_BACKEND_TCGEN05 ? sm100_bwd_workspace_bytes(*args) : 0;
+}
+
+int bma_attn_bwd(const bma_attn_args* args, const bma_mask_spec* spec, const bma_block_lists* lists, void* workspace,
+                 size_t workspace_bytes, bma_stream_t stream) {
+  int rc = validate_common(args);
+  if (rc != BMA_OK) return rc;
+  BMA_REQUIRE(spec != nullptr, BMA_ERR_ARG);
+  if ((rc = validate_tensor(args->q, true)) || (rc = validate_tensor(args->k, true)) ||
+      (rc = validate_tensor(args->v, true)) || (rc = validate_tensor(args->d_o, true)) ||
+      (rc = validate_tensor(args->dq, true)) || (rc = validate_tensor(args->dk, true)) ||
+      (rc = validate_tensor(args->dv, true)))
+    return rc;
+  BMA_REQUIRE(args->lse && args->delta, BMA_ERR_ARG);
+  BMA_REQUIRE(args->q.dtype == args->k.dtype && args->k.dtype == args->v.dtype, BMA_ERR_UNSUPPORTED);
+  BMA_REQUIRE(args->dq.dtype == args->q.dtype && args->dk.dtype == args->q.dtype && args->dv.dtype == args->q.dtype,
+              BMA_ERR_UNSUPPORTED);
+  const int be = pick_backend(args);
+  BMA_REQUIRE(be > 0, BMA_ERR_UNSUPPORTED);
+  const int tile = be == BMA_BACKEND_TCGEN05 ? kSm100Tile : kSimtTile;
+  if ((rc = validate_lists(args, lists, tile, true))) return rc;
+  BMA_REQUIRE(spec->q_valid <= args->N && spec->k_valid <= args->L, BMA_ERR_ARG);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (be == BMA_BACKEND_TCGEN05) {
+    const size_t need = sm100_bwd_workspace_bytes(*args);
+    BMA_REQUIRE(need == 0 || (workspace && workspace_bytes >= need), BMA_ERR_WORKSPACE);
+    return sm100_bwd(*args, *spec, *lists, workspace, workspace_bytes, st);
+  }
+  return simt_bwd(*args, *spec, *lists, st);
+}
+
+int bma_attn_merge(const bma_attn_args* args, bma_stream_t stream) {
+  int rc = validate_common(args);
+  if (rc != BMA_OK) return rc;
+  BMA_REQUIRE(args->o.ptr && args->d_o.ptr && args->lse && args->delta, BMA_ERR_ARG);
+  BMA_REQUIRE(args->o.dtype == BMA_DTYPE_F32 && args->d_o.dtype == BMA_DTYPE_F32, BMA_ERR_UNSUPPORTED);
+  const int64_t rows = (int64_t)args->B * args->N * args->Hq;
+  const int grid = (int)std::min<int64_t>((rows + 7) / 8, (int64_t)sm_count() * 16);
+  merge_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(*args);
+  count_launches(1);
+  BMA_CUDA_TRY(cudaGetLastError());
+  return BMA_OK;
+}
+
+int bma_device_status(bma_stream_t stream, int32_t* detail) {
+  int* p = device_status_ptr();
+  BMA_REQUIRE(p != nullptr, BMA_ERR_CUDA);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int v = 0;
+  BMA_CUDA_TRY(cudaMemcpyAsync(&v, p, sizeof(int), cudaMemcpyDeviceToHost, st));
+  BMA_CUDA_TRY(cudaStreamSynchronize(st));
+  if (v != 0) BMA_CUDA_TRY(cudaMemsetAsync(p, 0, sizeof(int), st));
+  if (detail) *detail = v;
+  return v == 0 ? BMA_OK : BMA_ERR_DEVICE_CHECK;
+}
+
+}  // extern "C"

@@ -1,0 +1,124 @@
+// Shared helpers for the blockwise masked attention kernels: status handling, the device
+// form of the mask predicate, and small numeric utilities.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/bma.h"
+
+namespace bma {
+
+// ---- host-side error plumbing ----------------------------------------------------------
+void set_last_cuda_error(cudaError_t e, const char* where);
+
+#define BMA_CUDA_TRY(expr)                                   \
+  do {                                                       \
+    cudaError_t _e = (expr);                                 \
+    if (_e != cudaSuccess) {                                 \
+      ::bma::set_last_cuda_error(_e, #expr);                 \
+      return BMA_ERR_CUDA;                                   \
+    }                                                        \
+  } while (0)
+
+#define BMA_REQUIRE(cond, code) \
+  do {                          \
+    if (!(cond)) return (code); \
+  } while (0)
+
+// Device-side status word (one per device, lives for the lifetime of the module).  Kernels
+// get its address as an argument and record a non-zero code with atomicCAS when a bounded
+// wait or a bounds check gives up.  Returns nullptr (and records the CUDA error) on failure.
+int* device_status_ptr();
+
+// Host-side count of kernels launched by this library in this process (diagnostics).
+void count_launches(int n);
+
+__device__ __forceinline__ void report_device_error(int* status, int code) { atomicCAS(status, 0, code); }
+
+// ---- mask predicate --------------------------------------------------------------------
+// Device copy of bma_mask_spec with the per-(b,h) row pointers resolved once per CTA.
+struct MaskView {
+  int flags;
+  int q_valid, k_valid;
+  int q_offset, k_offset;
+  int band_left, band_right;
+  int win_block, win_left, win_right, win_nblk;
+  const int32_t* seg_q_row;     // &seg_q[b*stride]
+  const int32_t* seg_k_row;
+  const uint32_t* bitmap_bh;    // &bitmap[((b%BB)*BH + h%BH) * bitmap_q * words]
+  int bitmap_words;
+};
+
+__device__ __forceinline__ MaskView make_mask_view(const bma_mask_spec& s, int b, int h) {
+  MaskView m;
+  m.flags = s.flags;
+  m.q_valid = s.q_valid; m.k_valid = s.k_valid;
+  m.q_offset = s.q_offset; m.k_offset = s.k_offset;
+  m.band_left = s.band_left; m.band_right = s.band_right;
+  m.win_block = s.win_block; m.win_left = s.win_left; m.win_right = s.win_right; m.win_nblk = s.win_nblk;
+  m.seg_q_row = (s.flags & BMA_MASK_SEGMENT) ? s.seg_q + (int64_t)b * s.seg_q_stride : nullptr;
+  m.seg_k_row = (s.flags & BMA_MASK_SEGMENT) ? s.seg_k + (int64_t)b * s.seg_k_stride : nullptr;
+  m.bitmap_words = s.bitmap_words;
+  m.bitmap_bh = nullptr;
+  if (s.flags & BMA_MASK_BITMAP) {
+    int64_t bh = (int64_t)(b % s.bitmap_B) * s.bitmap_H + (h % s.bitmap_H);
+    m.bitmap_bh = s.bitmap + bh * (int64_t)s.bitmap_q * s.bitmap_words;
+  }
+  return m;
+}
+
+// First key index and one-past-last key index of the reference's block window for the
+// query at global index gq (start clamped like XLA's dynamic_slice).
+__device__ __forceinline__ void block_window_range(const MaskView& m, int gq, int& k_lo, int& k_hi) {
+  int i = gq / m.win_block;
+  int total = m.win_left + m.win_right;
+  int s = max(0, i - m.win_left);
+  s = min(s, m.win_nblk - total);
+  k_lo = s * m.win_block;
+  k_hi = (s + total) * m.win_block;
+}
+
+// mask_fn(b, h, q, k) for local indices q, k (tile offset + lane offset).
+__device__ __forceinline__ bool mask_allowed(const MaskView& m, int q, int k) {
+  bool ok = (q < m.q_valid) & (k < m.k_valid);
+  const int gq = q + m.q_offset, gk = k + m.k_offset;
+  if (m.flags & BMA_MASK_CAUSAL) ok &= (gk <= gq);
+  if (m.flags & BMA_MASK_BAND) ok &= (gk >= gq - m.band_left) & (gk <= gq + m.band_right);
+  if (m.flags & BMA_MASK_BLOCK_WINDOW) {
+    int lo, hi;
+    block_window_range(m, gq, lo, hi);
+    ok &= (gk >= lo) & (gk < hi);
+  }
+  if ((m.flags & BMA_MASK_SEGMENT) && ok) ok = (__ldg(m.seg_q_row + gq) == __ldg(m.seg_k_row + gk));
+  if ((m.flags & BMA_MASK_BITMAP) && ok)
+    ok = (__ldg(m.bitmap_bh + (int64_t)gq * m.bitmap_words + (gk >> 5)) >> (gk & 31)) & 1u;
+  return ok;
+}
+
+// ---- numeric helpers -------------------------------------------------------------------
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Host-side dispatchers implemented in the individual .cu files.
+int simt_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, cudaStream_t st);
+int simt_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, cudaStream_t st);
+int sm100_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, cudaStream_t st);
+int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, void* ws,
+              size_t ws_bytes, cudaStream_t st);
+size_t sm100_bwd_workspace_bytes(const bma_attn_args& a);
+bool sm100_supported(const bma_attn_args& a);
+
+constexpr int kSimtTile = 64;
+constexpr int kSm100Tile = 128;
+
+}  // namespace bma

@@ -1,0 +1,233 @@
+"""Device-evaluable mask descriptions for ``mask_fn(b, h, q, k)``.
+
+The reference accepts an arbitrary Python callable (jaxmodules/attention.py:354, 368-372)
+and traces it with vmap.  A CUDA kernel cannot call Python, so a mask reaches the device in
+one of two forms:
+
+* a *structured* mask built by the factories below (``causal_mask``, ``sliding_window_mask``,
+  ``document_mask``, ``and_masks``).  They are ordinary callables with the reference's
+  ``(b, h, q, k)`` signature — usable anywhere a ``mask_fn`` is — that also carry the terms
+  the kernels evaluate in registers;
+* any other callable is evaluated once on the host over the full index grid and shipped as a
+  bit-packed table (1 bit per (b, h, q, k); a 3-argument ``(h, q, k)`` callable gives a
+  batch-independent table).  Only sensible up to a few thousand positions.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field, replace
+from typing import Callable, Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _native as nat
+
+_BIG = 1 << 30
+MAX_BITMAP_BITS = 1 << 34  # 2 GiB of table; beyond this a structured mask is required
+
+
+@dataclass(frozen=True)
+class MaskTerms:
+    """AND of the enabled terms; see ``bma_mask_spec`` in include/bma.h."""
+    causal: bool = False
+    band: Optional[Tuple[int, int]] = None           # (left, right): q-left <= k <= q+right
+    seg_q: Optional[torch.Tensor] = None             # [B, >=N] int32
+    seg_k: Optional[torch.Tensor] = None             # [B, >=L] int32
+    window: Optional[Tuple[int, int, int, int]] = None   # (block, left_blocks, right_blocks, num_kv_blocks)
+    bitmap: Optional[torch.Tensor] = None            # [Bm, Hm, Q, words] int32 (bit pattern of uint32)
+    q_offset: int = 0
+    k_offset: int = 0
+
+    def merged(self, other: "MaskTerms") -> "MaskTerms":
+        band = self.band
+        if other.band is not None:
+            band = other.band if band is None else (min(band[0], other.band[0]), min(band[1], other.band[1]))
+        if self.seg_q is not None and other.seg_q is not None:
+            raise NotImplementedError("and_masks: only one document_mask term is supported")
+        if self.bitmap is not None and other.bitmap is not None:
+            raise NotImplementedError("and_masks: only one table-backed term is supported")
+        return MaskTerms(
+            causal=self.causal or other.causal, band=band,
+            seg_q=self.seg_q if self.seg_q is not None else other.seg_q,
+            seg_k=self.seg_k if self.seg_k is not None else other.seg_k,
+            window=self.window or other.window,
+            bitmap=self.bitmap if self.bitmap is not None else other.bitmap,
+            q_offset=self.q_offset or other.q_offset, k_offset=self.k_offset or other.k_offset)
+
+
+class StructuredMask:
+    """A ``mask_fn`` that the kernels can evaluate: callable as ``m(b, h, q, k)`` on ints or
+    broadcastable NumPy arrays, with the device terms in ``m.terms``."""
+
+    def __init__(self, terms: MaskTerms, fn: Callable, name: str):
+        self.terms = terms
+        self._fn = fn
+        self.__name__ = name
+
+    def __call__(self, b, h, q, k):
+        return self._fn(b, h, q, k)
+
+    def __repr__(self):
+        return f"StructuredMask({self.__name__})"
+
+
+def causal_mask() -> StructuredMask:
+    """``q >= k`` — what ``is_causal=True`` installs (jaxmodules/attention.py:412-415)."""
+    return StructuredMask(MaskTerms(causal=True), lambda b, h, q, k: q >= k, "causal")
+
+
+def full_mask() -> StructuredMask:
+    """Everything allowed — the default when no mask is given (jaxmodules/attention.py:417-419)."""
+    return StructuredMask(MaskTerms(), lambda b, h, q, k: (q == q) & (k == k), "full")
+
+
+def sliding_window_mask(left: int, right: int) -> StructuredMask:
+    """``q - left <= k <= q + right`` (the explicit-window mask the reference's docstring
+    recommends, jaxmodules/attention.py:378-382)."""
+    left, right = int(left), int(right)
+    if left < 0 or right < 0:
+        raise ValueError("window extents must be non-negative")
+    return StructuredMask(MaskTerms(band=(min(left, _BIG), min(right, _BIG))),
+                          lambda b, h, q, k: (k >= q - left) & (k <= q + right), f"sliding({left},{right})")
+
+
+def document_mask(seg_q, seg_k=None, causal: bool = False) -> StructuredMask:
+    """``seg_q[b, q] == seg_k[b, k]`` (packed documents), optionally AND ``k <= q``.
+
+    ``seg_q``/``seg_k``: integer arrays [B, N] / [B, L] (tensor or ndarray); ``seg_k``
+    defaults to ``seg_q``."""
+    sq = torch.as_tensor(np.asarray(seg_q.cpu()) if isinstance(seg_q, torch.Tensor) else np.asarray(seg_q))
+    sk = sq if seg_k is None else torch.as_tensor(np.asarray(seg_k.cpu()) if isinstance(seg_k, torch.Tensor) else np.asarray(seg_k))
+    if sq.ndim != 2 or sk.ndim != 2 or sq.shape[0] != sk.shape[0]:
+        raise ValueError("segment ids must be [B, N] and [B, L]")
+    sq = sq.to(torch.int32).contiguous()
+    sk = sk.to(torch.int32).contiguous()
+    sq_np, sk_np = sq.numpy(), sk.numpy()
+
+    def fn(b, h, q, k):
+        same = sq_np[b, q] == sk_np[b, k]
+        return (same & (k <= q)) if causal else same
+
+    return StructuredMask(MaskTerms(causal=causal, seg_q=sq, seg_k=sk), fn,
+                          "document_causal" if causal else "document")
+
+
+def and_masks(*masks) -> StructuredMask:
+    """Conjunction of structured masks."""
+    if not masks or not all(isinstance(m, StructuredMask) for m in masks):
+        raise TypeError("and_masks takes StructuredMask arguments")
+    terms = masks[0].terms
+    for m in masks[1:]:
+        terms = terms.merged(m.terms)
+
+    def fn(b, h, q, k):
+        out = masks[0](b, h, q, k)
+        for m in masks[1:]:
+            out = out & m(b, h, q, k)
+        return out
+
+    return StructuredMask(terms, fn, "&".join(m.__name__ for m in masks))
+
+
+def argcount(fn) -> int:
+    """Positional-argument count the way the reference reads it
+    (``mask_fn.__code__.co_argcount``, jaxmodules/attention.py:405)."""
+    if isinstance(fn, StructuredMask):
+        return 4
+    code = getattr(fn, "__code__", None)
+    if code is not None:
+        return code.co_argcount
+    return fn.__call__.__code__.co_argcount - 1
+
+
+def bitmap_from_callable(mask_fn, B: int, H: int, N: int, L: int, batch_dependent: bool) -> torch.Tensor:
+    """Evaluate ``mask_fn(b, h, q, k)`` over the whole grid on the host and bit-pack it along k
+    (bit k%32 of word k//32).  Returns an int32 CPU tensor [Bm, H, N, ceil(L/32)]."""
+    Bm = B if batch_dependent else 1
+    if Bm * H * N * L > MAX_BITMAP_BITS:
+        raise NotImplementedError(
+            "mask_fn is an arbitrary callable and its table would exceed 2 GiB; build the mask with "
+            "jaxmodules_b200.masks (causal_mask, sliding_window_mask, document_mask, and_masks)")
+    b = np.arange(Bm, dtype=np.int64)[:, None, None, None]
+    h = np.arange(H, dtype=np.int64)[None, :, None, None]
+    q = np.arange(N, dtype=np.int64)[None, None, :, None]
+    k = np.arange(L, dtype=np.int64)[None, None, None, :]
+    try:
+        dense = np.broadcast_to(np.asarray(mask_fn(b, h, q, k)), (Bm, H, N, L)).astype(bool)
+    except Exception:
+        dense = np.zeros((Bm, H, N, L), dtype=bool)
+        for bi in range(Bm):
+            for hi in range(H):
+                for qi in range(N):
+                    for ki in range(L):
+                        dense[bi, hi, qi, ki] = bool(mask_fn(bi, hi, qi, ki))
+    words = (L + 31) // 32
+    padded = np.zeros((Bm, H, N, words * 32), dtype=bool)
+    padded[..., :L] = dense
+    packed = np.packbits(padded, axis=-1, bitorder="little")        # uint8, little bit order
+    packed = packed.reshape(Bm, H, N, words, 4).copy().view("<u4").reshape(Bm, H, N, words)
+    return torch.from_numpy(packed.view(np.int32).copy())
+
+
+@dataclass
+class DeviceMask:
+    """A MaskTerms resolved for one call: owns the device copies that the C struct points at."""
+    spec: nat.MaskSpec
+    keep: tuple = field(default_factory=tuple)
+    depends_b: bool = False
+    depends_h: bool = False
+
+
+def to_device_mask(terms: MaskTerms, N: int, L: int, device) -> DeviceMask:
+    s = nat.MaskSpec()
+    keep = []
+    flags = 0
+    s.q_valid, s.k_valid = N, L
+    s.q_offset, s.k_offset = terms.q_offset, terms.k_offset
+    if terms.causal:
+        flags |= nat.BMA_MASK_CAUSAL
+    if terms.band is not None:
+        flags |= nat.BMA_MASK_BAND
+        s.band_left, s.band_right = min(terms.band[0], _BIG), min(terms.band[1], _BIG)
+    if terms.window is not None:
+        flags |= nat.BMA_MASK_BLOCK_WINDOW
+        s.win_block, s.win_left, s.win_right, s.win_nblk = terms.window
+    depends_b = depends_h = False
+    if terms.seg_q is not None:
+        flags |= nat.BMA_MASK_SEGMENT
+        sq = terms.seg_q.to(device=device, dtype=torch.int32).contiguous()
+        sk = sq if terms.seg_k is terms.seg_q else terms.seg_k.to(device=device, dtype=torch.int32).contiguous()
+        if sq.shape[1] < N + terms.q_offset or sk.shape[1] < L + terms.k_offset:
+            raise ValueError("segment id arrays are shorter than the sequences")
+        keep += [sq, sk]
+        s.seg_q, s.seg_k = sq.data_ptr(), sk.data_ptr()
+        s.seg_q_stride, s.seg_k_stride = sq.stride(0), sk.stride(0)
+        depends_b = True
+    if terms.bitmap is not None:
+        flags |= nat.BMA_MASK_BITMAP
+        bm = terms.bitmap.to(device=device).contiguous()
+        keep.append(bm)
+        s.bitmap = bm.data_ptr()
+        s.bitmap_B, s.bitmap_H, s.bitmap_q, s.bitmap_words = bm.shape
+        depends_b = depends_b or bm.shape[0] > 1
+        depends_h = bm.shape[1] > 1
+    s.flags = flags
+    return DeviceMask(spec=s, keep=tuple(keep), depends_b=depends_b, depends_h=depends_h)
+
+
+def terms_from_mask_fn(mask_fn, B: int, Hq: int, N: int, L: int) -> MaskTerms:
+    """Structured masks pass through; any other callable becomes a bit table."""
+    if mask_fn is None:
+        return MaskTerms()
+    if isinstance(mask_fn, StructuredMask):
+        t = mask_fn.terms
+        if t.seg_q is not None and t.seg_q.shape[0] != B:
+            raise ValueError("document_mask batch size differs from the batch size of Q")
+        return t
+    n = argcount(mask_fn)
+    if n == 3:
+        fn = lambda b, h, q, k: mask_fn(h, q, k)
+        return MaskTerms(bitmap=bitmap_from_callable(fn, B, Hq, N, L, batch_dependent=False))
+    if n == 4:
+        return MaskTerms(bitmap=bitmap_from_callable(mask_fn, B, Hq, N, L, batch_dependent=True))
+    raise TypeError("mask_fn must take (b, h, q, k) or (h, q, k)")

@@ -1,0 +1,200 @@
+"""Parity of the CUDA attention path (package -> ctypes -> C ABI -> kernels) with the float64
+dense oracle, on the reference's test shapes, the benchmark configurations (reduced where the
+oracle would take minutes) and size-independent properties at full size.
+
+Tolerances (max-abs / mean-abs against the oracle): float32 I/O 1e-4 / 1e-5; bfloat16 I/O
+2e-2 / 2e-3 on O, dQ, dK and dV."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import jaxmodules_b200 as jm
+from jaxmodules_b200 import masks as M
+from jaxmodules_b200 import _native as nat
+from oracle import attention_oracle as ao
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: (1e-4, 1e-5), torch.bfloat16: (2e-2, 2e-3)}
+
+
+def gen(shape, seed, dtype, scale=1.0):
+    x = np.random.Generator(np.random.PCG64(seed)).standard_normal(shape, dtype=np.float32) * scale
+    return torch.from_numpy(x).to(dtype)
+
+
+def run(Q, K, V, dO, **kw):
+    Qc, Kc, Vc = (x.cuda().requires_grad_(True) for x in (Q, K, V))
+    O = jm.masked_attention_via_map(Qc, Kc, Vc, **kw)
+    O.backward(dO.cuda().to(O.dtype))
+    torch.cuda.synchronize()
+    return O.detach().cpu(), Qc.grad.cpu(), Kc.grad.cpu(), Vc.grad.cpu()
+
+
+def check(got, ref, dtype, what):
+    max_tol, mean_tol = TOL[dtype]
+    for name, g in zip(("O", "dQ", "dK", "dV"), got):
+        r = ref[name]
+        err = np.abs(g.float().numpy().astype(np.float64) - r)
+        assert np.isfinite(g.float().numpy()).all(), f"{what}: {name} has non-finite values"
+        assert err.max() <= max_tol and err.mean() <= mean_tol, f"{what}: {name} max {err.max():.3e} mean {err.mean():.3e}"
+
+
+def oracle(Q, K, V, dO, **kw):
+    kw = dict(kw)
+    kw.pop("backend", None)
+    kw.pop("out_dtype", None)
+    return ao.masked_attention_dense(Q.float().numpy(), K.float().numpy(), V.float().numpy(), dO=dO.float().numpy(), **kw)
+
+
+SMALL_MASKS = {
+    "causal": dict(is_causal=True),
+    "none": dict(),
+    "sliding": dict(mask_fn=lambda h, q, k: (q - 2 <= k) & (k <= q + 2)),
+    "alternating": dict(mask_fn=lambda h, q, k: (q + k) % 2 == 0),
+    "head_specific": dict(mask_fn=lambda h, q, k: np.where(h % 2 == 0, q >= k, (q + k) % 2 == 0)),
+    "batch_dependent": dict(mask_fn=lambda b, h, q, k: q + b >= k),
+    "empty_rows": dict(mask_fn=lambda h, q, k: k < q),
+}
+
+
+@pytest.mark.parametrize("mask", list(SMALL_MASKS))
+@pytest.mark.parametrize("block_size", [None, 4])
+def test_reference_small_shapes_f32(mask, block_size):
+    # shapes of the reference's tests/test_mapped_attention.py:303-430: N=L=8, H=4, d=16
+    B, N, L, H, d = 2, 8, 8, 4, 16
+    Q, K, V, dO = (gen((B, N if i in (0, 3) else L, H, d), i, torch.float32) for i in range(4))
+    kw = dict(SMALL_MASKS[mask], block_size=block_size)
+    check(run(Q, K, V, dO, **kw), oracle(Q, K, V, dO, **kw), torch.float32, mask)
+
+
+def test_3d_inputs_gqa_and_rectangular():
+    # tests/test_mapped_attention.py:564-605: N=32, L=64, Hq=8, Hkv=4, d=64, causal, no batch axis
+    Q, K, V, dO = gen((32, 8, 64), 0, torch.float32), gen((64, 4, 64), 1, torch.float32), gen((64, 4, 64), 2, torch.float32), gen((32, 8, 64), 3, torch.float32)
+    got = run(Q, K, V, dO, is_causal=True)
+    assert got[0].shape == (32, 8, 64) and got[2].shape == (64, 4, 64)
+    check(got, oracle(Q, K, V, dO, is_causal=True), torch.float32, "gqa")
+
+
+def test_padding_path():
+    # tests/test_mapped_attention.py:1076-1112: N=10, L=13, block 4
+    Q, K, V, dO = gen((2, 10, 4, 16), 0, torch.float32), gen((2, 13, 4, 16), 1, torch.float32), gen((2, 13, 4, 16), 2, torch.float32), gen((2, 10, 4, 16), 3, torch.float32)
+    for kw in (dict(is_causal=True, block_size=4), dict(block_size=4, window_size=(3, 2)),
+               dict(mask_fn=lambda b, h, q, k: (q + k + b) % 3 != 0, block_size=4)):
+        check(run(Q, K, V, dO, **kw), oracle(Q, K, V, dO, **kw), torch.float32, str(kw))
+
+
+@pytest.mark.parametrize("window", [(1, 1), (16, 1), (17, 1), (40, 40)])
+def test_window_size_semantics(window):
+    # tests/test_mapped_attention.py:1593-1648: the block window restricts even a permissive mask
+    N = L = 128
+    Q, K, V, dO = (gen((1, N, 2, 32), i, torch.float32) for i in range(4))
+    kw = dict(block_size=16, window_size=window)
+    check(run(Q, K, V, dO, **kw), oracle(Q, K, V, dO, **kw), torch.float32, f"window{window}")
+    kw = dict(block_size=16, window_size=window, is_causal=True)
+    check(run(Q, K, V, dO, **kw), oracle(Q, K, V, dO, **kw), torch.float32, f"causal window{window}")
+
+
+def test_window_larger_than_sequence_raises():
+    Q = torch.randn(1, 32, 2, 16, device="cuda")
+    with pytest.raises(ValueError):
+        jm.masked_attention_via_map(Q, Q, Q, block_size=8, window_size=(30, 30))
+
+
+def test_block_size_invariance_and_zero_inputs():
+    Q, K, V, dO = (gen((1, 64, 2, 32), i, torch.float32) for i in range(4))
+    outs = [run(Q, K, V, dO, is_causal=True, block_size=bs)[0] for bs in (4, 8, 16, None)]
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])          # block_size only matters through window_size
+    z = torch.zeros(1, 16, 2, 32, device="cuda")
+    assert torch.count_nonzero(jm.masked_attention_via_map(z, z, z, is_causal=True)) == 0
+    big = jm.masked_attention_via_map(Q.cuda() * 100, K.cuda() * 100, V.cuda(), is_causal=True)
+    assert torch.isfinite(big).all()            # max-subtracted softmax does not overflow
+
+
+def test_config1_causal_f32_full():
+    # BASELINE config 1: fp32, B=2, L=128, H=8, d=64, block_size=32, causal
+    Q, K, V, dO = (gen((2, 128, 8, 64), i, torch.float32) for i in range(4))
+    kw = dict(is_causal=True, block_size=32)
+    got = run(Q, K, V, dO, **kw)
+    check(got, oracle(Q, K, V, dO, **kw), torch.float32, "config1")
+    port = ao.masked_attention_via_map(Q, K, V, dO=dO, **kw)     # the faithful blockwise port agrees too
+    for g, p in zip(got, port):
+        assert (g - p).abs().max() < 1e-4
+
+
+def document_segments(B, L, lo, hi, seed):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    seg = np.zeros((B, L), dtype=np.int32)
+    for b in range(B):
+        pos, sid = 0, 0
+        while pos < L:
+            n = int(rng.integers(lo, hi + 1))
+            seg[b, pos:pos + n] = sid
+            pos += n
+            sid += 1
+    return seg
+
+
+BF16_CASES = {
+    # reduced copies of BASELINE configs 2-4 (same d, block size, mask family, value scales)
+    "config2_causal": dict(B=1, L=1024, H=2, d=128, scale=1 / math.sqrt(128), kw=lambda L: dict(is_causal=True, block_size=128)),
+    "config3_sliding": dict(B=1, L=2048, H=2, d=128, scale=1.0,
+                            kw=lambda L: dict(mask_fn=M.sliding_window_mask(256, 256), window_size=(256, 256), block_size=128)),
+    "config4_documents": dict(B=2, L=2048, H=2, d=128, scale=1.0,
+                              kw=lambda L: dict(mask_fn=M.document_mask(document_segments(2, L, 64, 700, 4), causal=True), block_size=128)),
+    "ragged_gqa": dict(B=1, L=300, H=4, d=128, scale=1.0, kw=lambda L: dict(is_causal=True), Hkv=2, N=200),
+    "d64": dict(B=1, L=512, H=2, d=64, scale=1.0, kw=lambda L: dict(is_causal=True, block_size=128)),
+}
+
+
+@pytest.mark.parametrize("name", list(BF16_CASES))
+def test_bf16_configs(name):
+    c = BF16_CASES[name]
+    N, Hkv = c.get("N", c["L"]), c.get("Hkv", c["H"])
+    Q = gen((c["B"], N, c["H"], c["d"]), 0, torch.bfloat16, c["scale"])
+    K = gen((c["B"], c["L"], Hkv, c["d"]), 1, torch.bfloat16, c["scale"])
+    V = gen((c["B"], c["L"], Hkv, c["d"]), 2, torch.bfloat16, c["scale"])
+    dO = gen((c["B"], N, c["H"], c["d"]), 3, torch.float32)
+    kw = c["kw"](c["L"])
+    got = run(Q, K, V, dO, **kw)
+    assert got[0].dtype == torch.float32 and got[1].dtype == torch.bfloat16   # O float32 like the reference
+    check(got, oracle(Q, K, V, dO, **kw), torch.bfloat16, name)
+
+
+def test_simt_and_auto_backends_agree_bf16():
+    """The exact-FP32 SIMT kernels cross-check whatever backend AUTO selects."""
+    Q, K, V = (gen((1, 512, 2, 128), i, torch.bfloat16) for i in range(3))
+    dO = gen((1, 512, 2, 128), 3, torch.float32)
+    a = run(Q, K, V, dO, is_causal=True)
+    b = run(Q, K, V, dO, is_causal=True, backend=nat.BMA_BACKEND_SIMT)
+    for x, y in zip(a, b):
+        assert (x.float() - y.float()).abs().max() <= 2e-2
+
+
+def test_full_size_properties_config2():
+    """BASELINE config 2 at full size (B=8, L=4096, H=32, d=128, bf16 causal): properties that do
+    not need the oracle — row 0 attends only key 0 so O[:,0] == V[:,0]; the output is a convex
+    combination of values; a (b,h) slice recomputed alone is bit-identical; dV column sums equal
+    dO column sums (softmax rows sum to 1)."""
+    B, L, H, d = 8, 4096, 32, 128
+    g = torch.Generator(device="cuda").manual_seed(0)
+    Q, K, V = (torch.randn(B, L, H, d, device="cuda", generator=g).mul_(1 / math.sqrt(d)).to(torch.bfloat16) for _ in range(3))
+    Q.requires_grad_(True); K.requires_grad_(True); V.requires_grad_(True)
+    O = jm.masked_attention_via_map(Q, K, V, is_causal=True, block_size=128)
+    assert torch.isfinite(O).all()
+    assert (O[:, 0] - V[:, 0].float()).abs().max() < 1e-6
+    vmax = V.float().abs().amax(dim=1, keepdim=True)
+    assert (O.abs() <= vmax + 1e-3).all()
+    sl = jm.masked_attention_via_map(Q[3:4, :, 5:6].detach().contiguous(), K[3:4, :, 5:6].detach().contiguous(),
+                                     V[3:4, :, 5:6].detach().contiguous(), is_causal=True, block_size=128)
+    assert torch.equal(sl, O[3:4, :, 5:6])
+    dO = torch.randn(B, L, H, d, device="cuda", generator=g)
+    O.backward(dO)
+    for t in (Q.grad, K.grad, V.grad):
+        assert torch.isfinite(t).all()
+    lhs = V.grad.float().sum(dim=1)
+    rhs = dO.to(torch.bfloat16).float().sum(dim=1) if False else dO.sum(dim=1)
+    assert (lhs - rhs).abs().max() / rhs.abs().max() < 2e-2

@@ -1,0 +1,117 @@
+"""Host-side mirror of the reference interface: BlockMask constructors/converters against the
+reference's known answers, mask factories, bit-table packing, and the argument checks of
+masked_attention_via_map that fire before any CUDA work."""
+import numpy as np
+import pytest
+import torch
+
+import jaxmodules_b200 as jm
+from jaxmodules_b200 import masks as M
+
+
+def test_constructors_match_known_answers(golden_block_mask, named_masks):
+    g = golden_block_mask["classmethod_causal"]
+    bm = jm.BlockMask.causal_mask(g["B"], g["H"], g["Q_LEN"], g["KV_LEN"], g["BLOCK_SIZE"])
+    assert (bm.B, bm.H, bm.Q_LEN, bm.KV_LEN, bm.Q_BLOCK_SIZE, bm.KV_BLOCK_SIZE) == (2, 2, 8, 8, 4, 4)
+    assert torch.equal(bm.materialize_mask(), torch.tensor(g["dense_mask_bh"], dtype=torch.int32).expand(2, 2, 8, 8))
+    g = golden_block_mask["classmethod_full"]
+    bm = jm.BlockMask.full_mask(g["B"], g["H"], g["Q_LEN"], g["KV_LEN"], g["BLOCK_SIZE"])
+    assert torch.equal(bm.materialize_mask(), torch.ones(2, 2, 8, 8, dtype=torch.int32))
+    assert bm.kv_indices.shape == (2, 2, 2, 1) and bm.q_num_blocks is None
+
+
+def test_from_kv_blocks(golden_block_mask, named_masks):
+    g = golden_block_mask["from_kv_blocks_banded"]
+    bm = jm.BlockMask.from_kv_blocks(torch.tensor(g["kv_num_blocks"]), torch.tensor(g["kv_indices"]),
+                                     torch.tensor(g["full_kv_num_blocks"]), torch.tensor(g["full_kv_indices"]),
+                                     BLOCK_SIZE=g["BLOCK_SIZE"], mask_mod=named_masks[g["mask"]], seq_lengths=tuple(g["seq_lengths"]))
+    assert torch.equal(bm.materialize_mask()[0, 0], torch.tensor(g["dense_mask_bh"], dtype=torch.int32))
+    g = golden_block_mask["from_kv_blocks_inferred"]
+    bm = jm.BlockMask.from_kv_blocks(torch.tensor(g["kv_num_blocks"]), torch.tensor(g["kv_indices"]),
+                                     torch.tensor(g["full_kv_num_blocks"]), torch.tensor(g["full_kv_indices"]),
+                                     BLOCK_SIZE=g["BLOCK_SIZE"], mask_mod=named_masks[g["mask"]])
+    assert (bm.Q_LEN, bm.KV_LEN, bm.B, bm.H) == (g["expected_Q_LEN"], g["expected_KV_LEN"], 1, 1)
+    dense = bm.materialize_mask()
+    assert dense.shape == (1, 1, 6, 8) and dense.min() >= 0 and dense.max() <= 1
+    # rank lifting and q-side generation
+    bm2 = jm.BlockMask.from_kv_blocks(torch.tensor([1, 2]), torch.tensor([[0, 0], [0, 1]]), torch.tensor([0, 0]),
+                                      torch.tensor([[0, 0], [0, 0]]), BLOCK_SIZE=2, mask_mod=named_masks["parity"],
+                                      seq_lengths=(4, 4), generate_q_blocks=True)
+    assert bm2.q_num_blocks.tolist() == [[[2, 1]]] and bm2.kv_num_blocks.shape == (1, 1, 2)
+
+
+def test_sparse_dense_converters(golden_block_mask, named_masks):
+    for name, fn in (("sparse_kv", jm.get_sparse_kv_data_from_blocks), ("sparse_q", jm.get_sparse_q_data_from_blocks)):
+        g = golden_block_mask[name]
+        num, idx = fn(torch.tensor(g["blocks"]))
+        rel = torch.tensor(g["relevant"])
+        assert num.dtype == torch.int32 and idx.dtype == torch.int32
+        assert num.tolist() == g["expected_num_blocks"]
+        assert torch.equal(idx * rel, torch.tensor(g["expected_indices"], dtype=torch.int32) * rel)
+    g = golden_block_mask["dense_from_kv"]
+    dense = jm.get_dense_from_kv_blocks(1, 1, 2, 2, torch.tensor(g["kv_num_blocks"]), torch.tensor(g["kv_indices"]))
+    assert dense.int().tolist() == g["expected"]
+    g = golden_block_mask["get_partial_block_checkerboard"]
+    blk = jm.get_partial_block(named_masks["parity"], 0, 0, 0, 0, 4, 4, 1, 1)
+    assert blk.int().tolist() == g["expected"]
+    assert jm.extract_block_size(4) == (4, 4) and jm.extract_block_size((2, 8)) == (2, 8)
+
+
+def test_from_blocks_removes_full_from_partial():
+    partial = torch.tensor([[[[1, 1], [0, 1]]]])
+    full = torch.tensor([[[[0, 1], [0, 0]]]])
+    bm = jm.BlockMask.from_blocks(partial, full, 4, lambda b, h, q, k: True)
+    assert bm.kv_num_blocks.tolist() == [[[1, 1]]] and bm.full_kv_num_blocks.tolist() == [[[1, 0]]]
+    assert bm.to_dense().int().tolist() == [[[[1, 1], [0, 1]]]]
+    assert (bm.Q_LEN, bm.KV_LEN) == (8, 8)
+
+
+def test_mask_factories_agree_with_plain_predicates():
+    q = np.arange(12)[:, None]
+    k = np.arange(12)[None, :]
+    assert np.array_equal(M.causal_mask()(0, 0, q, k), q >= k)
+    assert np.array_equal(M.sliding_window_mask(3, 2)(0, 0, q, k), (k >= q - 3) & (k <= q + 2))
+    seg = np.array([[0, 0, 0, 1, 1, 2, 2, 2, 2, 3, 3, 3]])
+    got = M.document_mask(seg, causal=True)(0, 0, q, k)
+    assert np.array_equal(got, (seg[0][q] == seg[0][k]) & (k <= q))
+    both = M.and_masks(M.causal_mask(), M.sliding_window_mask(4, 0))
+    assert both.terms.causal and both.terms.band == (4, 0)
+    assert np.array_equal(both(0, 0, q, k), (q >= k) & (k >= q - 4))
+    assert M.argcount(lambda h, q, k: True) == 3 and M.argcount(both) == 4
+
+
+def test_bitmap_packing():
+    fn = lambda b, h, q, k: (q * 7 + k * 3 + h + b) % 5 < 2
+    bm = M.bitmap_from_callable(fn, 2, 3, 5, 70, batch_dependent=True)
+    assert bm.shape == (2, 3, 5, 3) and bm.dtype == torch.int32
+    words = bm.numpy().view(np.uint32)
+    for (b, h, q, k) in [(0, 0, 0, 0), (1, 2, 4, 69), (1, 1, 3, 31), (0, 2, 2, 32), (1, 0, 1, 64)]:
+        assert ((words[b, h, q, k // 32] >> (k % 32)) & 1) == int(fn(b, h, q, k))
+    assert (words[..., 2] >> 6).max() == 0  # bits past L are clear
+    t = M.terms_from_mask_fn(lambda h, q, k: q >= k, 4, 2, 8, 8)
+    assert t.bitmap.shape[0] == 1  # 3-argument masks are batch independent
+
+
+def test_argument_errors_precede_cuda():
+    Q, K, V = torch.randn(8, 2, 16), torch.randn(8, 2, 16), torch.randn(8, 2, 16)
+    with pytest.raises(ValueError):
+        jm.masked_attention_via_map(Q, K, V, is_causal=True, mask_fn=lambda h, q, k: True)
+    with pytest.raises(AssertionError):
+        jm.masked_attention_via_map(Q, torch.randn(8, 2, 32), V)
+    with pytest.raises(ValueError):
+        jm.masked_attention_via_map(torch.randn(8, 16), K, V)
+    with pytest.raises(AssertionError):
+        jm.masked_attention_via_map(Q[None], K, V)
+    with pytest.raises(AssertionError):
+        jm.masked_attention_via_map(torch.randn(8, 3, 16), K, V)   # Hq % Hkv != 0
+    with pytest.raises(NotImplementedError):
+        jm.masked_attention_via_map(Q, K, V, kernel_fn=jm.threshold_kernel(1.0))
+    with pytest.raises(RuntimeError):   # CPU tensors: there is no CPU path
+        jm.masked_attention_via_map(Q, K, V)
+
+
+def test_no_cpu_path_for_create_block_mask():
+    if torch.cuda.is_available():
+        pytest.skip("CUDA present")
+    with pytest.raises(RuntimeError):
+        jm.create_block_mask(lambda b, h, q, k: q >= k, 1, 1, 8, 8, 4)
