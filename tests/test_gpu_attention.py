@@ -145,7 +145,7 @@ BF16_CASES = {
                             kw=lambda L: dict(mask_fn=M.sliding_window_mask(256, 256), window_size=(256, 256), block_size=128)),
     "config4_documents": dict(B=2, L=2048, H=2, d=128, scale=1.0,
                               kw=lambda L: dict(mask_fn=M.document_mask(document_segments(2, L, 64, 700, 4), causal=True), block_size=128)),
-    "ragged_gqa": dict(B=1, L=300, H=4, d=128, scale=1.0, kw=lambda L: dict(is_causal=True), Hkv=2, N=200),
+    "ragged_gqa": dict(B=1, L=300, H=4, d=128, scale=1.0, kw=lambda L: dict(is_causal=True, block_size=64), Hkv=2, N=200),
     "d64": dict(B=1, L=512, H=2, d=64, scale=1.0, kw=lambda L: dict(is_causal=True, block_size=128)),
 }
 
