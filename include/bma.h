@@ -152,9 +152,12 @@ int bma_mask_compile(const bma_mask_spec* spec, int32_t B, int32_t H,
                      const bma_block_lists* lists, void* workspace, size_t workspace_bytes,
                      bma_stream_t stream);
 
-/* Which backend and tile sizes bma_attn_fwd / bma_attn_bwd will use for these arguments;
- * the block lists passed to them must be compiled at exactly these block sizes. */
+/* Which backend and tile sizes bma_attn_fwd (bma_attn_plan) and bma_attn_bwd
+ * (bma_attn_bwd_plan) will use for these arguments; the block lists passed to each must be
+ * compiled at exactly those block sizes.  (The reference has one block_size for both passes,
+ * jaxmodules/attention.py:195-196, 280-281; results do not depend on it.) */
 int bma_attn_plan(const bma_attn_args* args, int32_t* backend, int32_t* q_tile, int32_t* kv_tile);
+int bma_attn_bwd_plan(const bma_attn_args* args, int32_t* backend, int32_t* q_tile, int32_t* kv_tile);
 
 /* Forward: O = softmax_masked(Q K^T * scale) V and lse, visiting only listed blocks and
  * applying the element predicate only on partial ones.  Replaces the lax.map/lax.scan

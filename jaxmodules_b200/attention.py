@@ -68,11 +68,12 @@ def _stream(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def plan(Q, K, V, backend=nat.BMA_BACKEND_AUTO):
-    """(backend, q_tile, kv_tile) the library will use for these tensors."""
+def plan(Q, K, V, backend=nat.BMA_BACKEND_AUTO, backward: bool = False):
+    """(backend, q_tile, kv_tile) the library will use for the forward (or backward) pass."""
     a = _make_args(Q, K, V, backend)
     be, tq, tk = C.c_int32(), C.c_int32(), C.c_int32()
-    nat.check(nat.lib().bma_attn_plan(C.byref(a), C.byref(be), C.byref(tq), C.byref(tk)), "bma_attn_plan")
+    fn = nat.lib().bma_attn_bwd_plan if backward else nat.lib().bma_attn_plan
+    nat.check(fn(C.byref(a), C.byref(be), C.byref(tq), C.byref(tk)), "bma_attn_plan")
     return be.value, tq.value, tk.value
 
 
@@ -120,7 +121,7 @@ def attention_forward(Q, K, V, terms: _masks.MaskTerms, *, out_dtype=torch.float
         be, tq, tk = plan(Q, K, V, backend)
         dmask = _masks.to_device_mask(terms, N, L, dev)
         with _Span(_profile_sink, "mask_compile", dev):
-            lists, lt = compile_block_lists(dmask, B, Hq, N, L, tq, tk, dev, q_side=need_q_side)
+            lists, lt = compile_block_lists(dmask, B, Hq, N, L, tq, tk, dev, q_side=False)
         O = torch.empty((B, N, Hq, d), dtype=out_dtype, device=dev)
         lse = torch.empty((B, Hq, N), dtype=torch.float32, device=dev)
         a.o, a.lse = _tensor(O), lse.data_ptr()
@@ -135,8 +136,12 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
     lib = nat.lib()
     dev = Q.device
     B, N, Hq, d = Q.shape
+    L = K.shape[1]
     with torch.cuda.device(dev):
         a = _make_args(Q, K, V, backend)
+        be, tq, tk = plan(Q, K, V, backend, backward=True)
+        with _Span(_profile_sink, "mask_compile_bwd", dev):
+            lists, lt = compile_block_lists(ctx["dmask"], B, Hq, N, L, tq, tk, dev, q_side=True)
         if dO.stride(-1) != 1:
             dO = dO.contiguous()
         delta = torch.empty((B, Hq, N), dtype=torch.float32, device=dev)
@@ -145,7 +150,7 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
         a.dq, a.dk, a.dv = _tensor(dQ), _tensor(dK), _tensor(dV)
         st = _stream(dev)
         do_bf16 = None
-        if ctx["backend"] == nat.BMA_BACKEND_TCGEN05 and dO.dtype != torch.bfloat16:
+        if be == nat.BMA_BACKEND_TCGEN05 and dO.dtype != torch.bfloat16:
             do_bf16 = torch.empty((B, N, Hq, d), dtype=torch.bfloat16, device=dev)
         with _Span(_profile_sink, "bwd_preprocess", dev):
             nat.check(lib.bma_attn_bwd_preprocess(C.byref(a), do_bf16.data_ptr() if do_bf16 is not None else None, st),
@@ -155,7 +160,7 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
         ws_bytes = lib.bma_attn_bwd_workspace_bytes(C.byref(a))
         ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=dev)
         with _Span(_profile_sink, "bwd", dev):
-            nat.check(lib.bma_attn_bwd(C.byref(a), C.byref(ctx["dmask"].spec), C.byref(ctx["lists"]), ws.data_ptr(), ws_bytes, st),
+            nat.check(lib.bma_attn_bwd(C.byref(a), C.byref(ctx["dmask"].spec), C.byref(lists), ws.data_ptr(), ws_bytes, st),
                       "bma_attn_bwd")
     return dQ, dK, dV
 

@@ -128,6 +128,13 @@ int pick_backend(const bma_attn_args* a) {
   return BMA_BACKEND_SIMT;
 }
 
+int pick_backend_bwd(const bma_attn_args* a) {
+  if (a->backend == BMA_BACKEND_SIMT) return BMA_BACKEND_SIMT;
+  if (sm100_bwd_supported(*a)) return BMA_BACKEND_TCGEN05;
+  if (a->backend == BMA_BACKEND_TCGEN05) return -1;
+  return BMA_BACKEND_SIMT;
+}
+
 int sm_count() {
   int dev = 0, n = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
@@ -185,6 +192,18 @@ int bma_attn_plan(const bma_attn_args* args, int32_t* backend, int32_t* q_tile, 
   return BMA_OK;
 }
 
+int bma_attn_bwd_plan(const bma_attn_args* args, int32_t* backend, int32_t* q_tile, int32_t* kv_tile) {
+  int rc = validate_common(args);
+  if (rc != BMA_OK) return rc;
+  const int be = pick_backend_bwd(args);
+  BMA_REQUIRE(be > 0, BMA_ERR_UNSUPPORTED);
+  const int tile = be == BMA_BACKEND_TCGEN05 ? kSm100Tile : kSimtTile;
+  if (backend) *backend = be;
+  if (q_tile) *q_tile = tile;
+  if (kv_tile) *kv_tile = tile;
+  return BMA_OK;
+}
+
 int bma_attn_fwd(const bma_attn_args* args, const bma_mask_spec* spec, const bma_block_lists* lists,
                  bma_stream_t stream) {
   int rc = validate_common(args);
@@ -224,7 +243,7 @@ int bma_attn_bwd_preprocess(const bma_attn_args* args, void* d_o_bf16, bma_strea
 
 size_t bma_attn_bwd_workspace_bytes(const bma_attn_args* args) {
   if (validate_common(args) != BMA_OK) return 0;
-  return pick_backend(args) == BMA_BACKEND_TCGEN05 ? sm100_bwd_workspace_bytes(*args) : 0;
+  return pick_backend_bwd(args) == BMA_BACKEND_TCGEN05 ? sm100_bwd_workspace_bytes(*args) : 0;
 }
 
 int bma_attn_bwd(const bma_attn_args* args, const bma_mask_spec* spec, const bma_block_lists* lists, void* workspace,
@@ -241,7 +260,7 @@ int bma_attn_bwd(const bma_attn_args* args, const bma_mask_spec* spec, const bma
   BMA_REQUIRE(args->q.dtype == args->k.dtype && args->k.dtype == args->v.dtype, BMA_ERR_UNSUPPORTED);
   BMA_REQUIRE(args->dq.dtype == args->q.dtype && args->dk.dtype == args->q.dtype && args->dv.dtype == args->q.dtype,
               BMA_ERR_UNSUPPORTED);
-  const int be = pick_backend(args);
+  const int be = pick_backend_bwd(args);
   BMA_REQUIRE(be > 0, BMA_ERR_UNSUPPORTED);
   const int tile = be == BMA_BACKEND_TCGEN05 ? kSm100Tile : kSimtTile;
   if ((rc = validate_lists(args, lists, tile, true))) return rc;
