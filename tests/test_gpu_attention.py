@@ -2,8 +2,11 @@
 dense oracle, on the reference's test shapes, the benchmark configurations (reduced where the
 oracle would take minutes) and size-independent properties at full size.
 
-Tolerances (max-abs / mean-abs against the oracle): float32 I/O 1e-4 / 1e-5; bfloat16 I/O
-2e-2 / 2e-3 on O, dQ, dK and dV."""
+Tolerances against the oracle on O, dQ, dK and dV: float32 I/O max-abs 1e-4, mean-abs 1e-5;
+bfloat16 I/O max-abs 2e-2, mean-abs 2e-3.  The max-abs bound is applied as
+|got - ref| <= tol * max(1, |ref|): gradients of unscaled N(0,1) inputs reach magnitudes of 8
+and more, where one bfloat16 ulp (2^-4 at 8) already exceeds an absolute 2e-2, so above 1 the
+bound is relative (2 %, i.e. ten bfloat16 roundings)."""
 import math
 
 import numpy as np
@@ -39,7 +42,9 @@ def check(got, ref, dtype, what):
         r = ref[name]
         err = np.abs(g.float().numpy().astype(np.float64) - r)
         assert np.isfinite(g.float().numpy()).all(), f"{what}: {name} has non-finite values"
-        assert err.max() <= max_tol and err.mean() <= mean_tol, f"{what}: {name} max {err.max():.3e} mean {err.mean():.3e}"
+        scaled = err / np.maximum(1.0, np.abs(r))
+        assert scaled.max() <= max_tol and err.mean() <= mean_tol, \
+            f"{what}: {name} max {err.max():.3e} scaled max {scaled.max():.3e} mean {err.mean():.3e} (|ref| max {np.abs(r).max():.2f})"
 
 
 def oracle(Q, K, V, dO, **kw):
