@@ -38,6 +38,9 @@ WORKLOADS = {
     # BASELINE.json configs[1]: the dense-causal reference shape the metric is quoted on
     "c2": dict(B=8, L=4096, H=32, d=128, bs=128, mask="causal", dtype="bf16", qkv_scale="rsqrt_d",
                desc="causal bf16 B=8 L=4096 H=32 d=128 block_size=128"),
+    # a quarter of c2 (same per-(b,h) work): small enough for multi-pass ncu captures, inputs still exceed L2
+    "c2_small": dict(B=2, L=4096, H=32, d=128, bs=128, mask="causal", dtype="bf16", qkv_scale="rsqrt_d",
+                     desc="causal bf16 B=2 L=4096 H=32 d=128 block_size=128 (quarter of the dense-causal shape)"),
     # headline target shape of the north star (bf16 causal, L=8192, d=128)
     "t0": dict(B=4, L=8192, H=32, d=128, bs=128, mask="causal", dtype="bf16", qkv_scale="one",
                desc="causal bf16 B=4 L=8192 H=32 d=128 block_size=128"),
