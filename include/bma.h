@@ -152,6 +152,27 @@ int bma_mask_compile(const bma_mask_spec* spec, int32_t B, int32_t H,
                      const bma_block_lists* lists, void* workspace, size_t workspace_bytes,
                      bma_stream_t stream);
 
+/* bma_mask_compile without a caller-provided workspace and without any allocation.  This entry
+ * point has no counterpart in the reference.  It exists for callers that are not allowed to
+ * allocate device memory at call time -- for example a custom-call handler running inside a
+ * compiled program whose buffers were all planned ahead of time, or a serving loop that froze its
+ * memory pool at start-up -- where a cudaMalloc would stall the device or break that plan.  The
+ * scratch (block flags, segment summaries) is a fixed 4 MiB array inside the library image, held
+ * by every GPU that loads the library until the process exits; bma_mask_compile_static_limit()
+ * returns that size.  A mask whose bma_mask_compile_workspace_bytes() exceeds it is rejected with
+ * BMA_ERR_LIMIT (use bma_mask_compile with your own workspace).  Neither this call nor anything
+ * it runs calls cudaMalloc, cudaFree or an allocating library routine; inputs and outputs are
+ * still the caller's buffers.
+ *   - The first call on each device looks up the array's device address; make that first call
+ *     outside of any stream capture, with the device current.
+ *   - All calls on one device share the array: calls whose kernels may overlap on the GPU
+ *     (different streams, no ordering between them) race on it.  Calls ordered on one stream
+ *     are safe; nothing has to be cleared between them because every byte that is read was
+ *     written earlier in the same call. */
+size_t bma_mask_compile_static_limit(void);
+int bma_mask_compile_static(const bma_mask_spec* spec, int32_t B, int32_t H,
+                            const bma_block_lists* lists, bma_stream_t stream);
+
 /* Which backend and tile sizes bma_attn_fwd (bma_attn_plan) and bma_attn_bwd
  * (bma_attn_bwd_plan) will use for these arguments; the block lists passed to each must be
  * compiled at exactly those block sizes.  (The reference has one block_size for both passes,

@@ -72,6 +72,8 @@ SIGNATURES = {
     "bma_mask_compile_workspace_bytes": (C.c_size_t, [C.POINTER(MaskSpec), C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "bma_mask_compile": (C.c_int, [C.POINTER(MaskSpec), C.c_int32, C.c_int32, C.POINTER(BlockLists), C.c_void_p,
                                    C.c_size_t, C.c_void_p]),
+    "bma_mask_compile_static_limit": (C.c_size_t, []),
+    "bma_mask_compile_static": (C.c_int, [C.POINTER(MaskSpec), C.c_int32, C.c_int32, C.POINTER(BlockLists), C.c_void_p]),
     "bma_attn_plan": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "bma_attn_bwd_plan": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "bma_attn_fwd": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(MaskSpec), C.POINTER(BlockLists), C.c_void_p]),

@@ -15,6 +15,8 @@ size_t mask_compile_workspace_bytes(const bma_mask_spec& spec, int B, int H, int
 int mask_compile_validate(const bma_mask_spec& s, int B, int H, const bma_block_lists& l);
 int mask_compile_launch(const bma_mask_spec& spec, int B, int H, const bma_block_lists& l, void* workspace,
                         cudaStream_t st);
+size_t mask_compile_static_limit();
+int mask_compile_static(const bma_mask_spec& spec, int B, int H, const bma_block_lists& l, cudaStream_t st);
 
 namespace {
 thread_local char g_err_text[512] = "";
@@ -178,6 +180,14 @@ int bma_mask_compile(const bma_mask_spec* spec, int32_t B, int32_t H, const bma_
   const size_t need = mask_compile_workspace_bytes(*spec, B, H, lists->NQ, lists->NKV);
   BMA_REQUIRE(workspace != nullptr && workspace_bytes >= need, BMA_ERR_WORKSPACE);
   return mask_compile_launch(*spec, B, H, *lists, workspace, static_cast<cudaStream_t>(stream));
+}
+
+size_t bma_mask_compile_static_limit(void) { return mask_compile_static_limit(); }
+
+int bma_mask_compile_static(const bma_mask_spec* spec, int32_t B, int32_t H, const bma_block_lists* lists,
+                            bma_stream_t stream) {
+  BMA_REQUIRE(spec && lists, BMA_ERR_ARG);
+  return mask_compile_static(*spec, B, H, *lists, static_cast<cudaStream_t>(stream));
 }
 
 int bma_attn_plan(const bma_attn_args* args, int32_t* backend, int32_t* q_tile, int32_t* kv_tile) {

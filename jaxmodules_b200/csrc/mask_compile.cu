@@ -14,6 +14,7 @@
 // classified once and the rows are replicated on the way out, so the cost is writing the
 // int32 lists.
 #include <algorithm>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -331,6 +332,55 @@ int mask_compile_launch(const bma_mask_spec& spec, int B, int H, const bma_block
   }
   BMA_CUDA_TRY(cudaGetLastError());
   return BMA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Variant for callers that must not allocate: the scratch lives in the module image.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(4) << 20;  // 4 MiB per GPU that loads the library
+
+// Block flags and segment summaries of bma_mask_compile_static.  Every call on a device uses this
+// one array, so two calls whose kernels overlap on the GPU race on it.  Nothing in it has to start
+// at zero: the classify pass writes every flag and the summary pass every summary before they are
+// read, so no clearing is needed between calls.
+static __device__ __align__(256) uint8_t g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevicesStatic = 64;
+void* g_static_scratch_ptr[kMaxDevicesStatic] = {};
+std::mutex g_static_scratch_mutex;
+
+// Device address of g_static_scratch on the current device.  In host code the symbol name is only
+// a handle, not an address a kernel may dereference; the address comes from the runtime, once per
+// device, with that device current.
+int static_scratch_address(void** out) {
+  int dev = 0;
+  BMA_CUDA_TRY(cudaGetDevice(&dev));
+  BMA_REQUIRE(dev >= 0 && dev < kMaxDevicesStatic, BMA_ERR_LIMIT);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_ptr[dev]) {
+    void* ptr = nullptr;
+    BMA_CUDA_TRY(cudaGetSymbolAddress((void**)&ptr, g_static_scratch));
+    BMA_REQUIRE(ptr != nullptr, BMA_ERR_CUDA);
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return BMA_OK;
+}
+
+}  // namespace
+
+size_t mask_compile_static_limit() { return kStaticScratchBytes; }
+
+int mask_compile_static(const bma_mask_spec& spec, int B, int H, const bma_block_lists& l, cudaStream_t st) {
+  int rc = mask_compile_validate(spec, B, H, l);
+  if (rc != BMA_OK) return rc;
+  if (mask_compile_workspace_bytes(spec, B, H, l.NQ, l.NKV) > kStaticScratchBytes) return BMA_ERR_LIMIT;
+  void* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc != BMA_OK) return rc;
+  return mask_compile_launch(spec, B, H, l, scratch, st);
 }
 
 }  // namespace bma
