@@ -1,21 +1,24 @@
 // Flash-style forward for bf16, head dim 128, on the sm_100a tensor core (tcgen05) with TMEM
 // accumulators and TMA-staged operands.
 //
-// One CTA = one 128-query tile of one (batch, query head); two CTAs are resident per SM so that
-// one CTA's softmax overlaps the other's MMAs.  The CTA walks only the kv tiles named in the block
-// lists (full tiles first, then partial ones); the element predicate is evaluated only on partial
-// tiles.
+// One CTA per SM works on a PAIR of 128-query tiles (2p, 2p+1) of one (batch, query head) and
+// walks the union of the kv tiles their block lists name; each K / V tile is fetched once for both.
+// The two query tiles ping-pong on the tensor core: while one tile's softmax runs, the other
+// tile's MMAs execute.
 //
-//   warp 4 (one elected lane)  TMA loads of Q / K / V tiles (128-byte swizzle, K-major boxes of
-//                              [128 rows x 64 columns]) and tcgen05.mma issue:
-//                                S = Q K^T          (A, B from shared memory, 128x128x128)
-//                                O (+)= P V         (A = P from tensor memory, B = V MN-major)
-//   warps 0-3 (thread = row)   read S from TMEM, online softmax in FP32 (exp2 with the scale folded
-//                              in, running max with lazy rescale of O), write P as bf16 back into
-//                              the S columns, final O / l and log-sum-exp.
+//   warpgroup 0 / 1 (thread = query row of tile A / B): read S from TMEM, fp32 online softmax
+//       (exp2 with the scale folded in, running max with lazy rescale of O), write P as bf16 over
+//       the S columns, final O / l and the log-sum-exp.  The element predicate is evaluated only
+//       on partial tiles (a per-row bit mask); full tiles take a mask-free path.
+//   warp 8  (one lane): TMA loads, Q once, K and V through two-stage rings (128-byte swizzle,
+//       K-major boxes of [128 rows x 64 columns]).
+//   warp 9  (one lane): tcgen05.mma issue:  S_x = Q_x K^T  (A, B from shared memory),
+//       O_x (+)= P_x V  (A = P from tensor memory, B = V read MN-major).
 //
-// TMEM columns (256 per CTA): [0,128) S fp32, reused as P bf16 in [0,64); [128,256) O fp32.
-// Every mbarrier wait is bounded; on a timeout the CTA records an error code and unwinds.
+// TMEM (512 columns): S_A [0,128) (P_A bf16 in [0,64)), S_B [128,256), O_A [256,384), O_B [384,512).
+// MMAs issued by one thread execute in issue order, so P_x V (reads P_x) followed by the next
+// S_x (overwrites it) needs no extra barrier.  Every mbarrier wait is bounded; on a timeout the
+// thread records an error code and unwinds to the common exit where TMEM is released.
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -25,22 +28,30 @@ namespace {
 using namespace ptx;
 
 constexpr int BM = kSm100Tile, BN = kSm100Tile, HD = 128;
-constexpr int kSoftmaxThreads = 128;
-constexpr int kThreads = kSoftmaxThreads + 32;
-constexpr uint32_t kTmemCols = 256;
+constexpr int kThreads = 384;
+constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kHalfTile = BM * 64 * 2;     // one [128 x 64] bf16 box
 constexpr uint32_t kTileBytes = 2 * kHalfTile;  // a [128 x 128] operand tile
 constexpr float kRescaleThreshold = 8.0f;       // log2 units: rescale O only when the max grew by > 2^8
+constexpr int kMaxKvTiles = 4096;               // merged kv list kept in shared memory
 
-enum { BAR_Q = 0, BAR_K, BAR_V, BAR_S, BAR_P, BAR_O, NUM_BARS };
+enum {
+  BAR_Q = 0,
+  BAR_K_FULL0, BAR_K_FULL1, BAR_K_FREE0, BAR_K_FREE1,
+  BAR_V_FULL0, BAR_V_FULL1, BAR_V_FREE0, BAR_V_FREE1,
+  BAR_S0, BAR_S1, BAR_P0, BAR_P1, BAR_O0, BAR_O1,
+  NUM_BARS
+};
 
 struct __align__(1024) FwdSmem {
-  uint8_t q[kTileBytes];
-  uint8_t k[kTileBytes];
-  uint8_t v[kTileBytes];
+  uint8_t q[2][kTileBytes];
+  uint8_t k[2][kTileBytes];
+  uint8_t v[2][kTileBytes];
+  uint32_t merged[kMaxKvTiles];  // kv tile | class for tile A << 16 | class for tile B << 18  (1 partial, 2 full)
+  uint8_t cls[2][kMaxKvTiles];
   uint64_t bar[NUM_BARS];
   uint32_t tmem_base;
-  int abort;
+  int n_merged;
 };
 
 struct FwdParams {
@@ -51,6 +62,14 @@ struct FwdParams {
   int interval_mask;  // 1: the mask has only interval terms (no segment ids / bit table)
   int* status;
 };
+
+__device__ __forceinline__ void setmaxnreg_inc_216() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
+__device__ __forceinline__ void setmaxnreg_dec_72() { asm volatile("setmaxnreg.dec.sync.aligned.u32 72;"); }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 
 // Allowed key interval [jlo, jhi] (tile-local, inclusive) of query row q for interval-only masks.
 __device__ __forceinline__ void row_interval(const MaskView& m, int q, int k0, int& jlo, int& jhi) {
@@ -65,44 +84,61 @@ __device__ __forceinline__ void row_interval(const MaskView& m, int q, int k0, i
     lo = max(lo, wlo);
     hi = min(hi, whi - 1);
   }
-  // to tile-local key indices
   jlo = lo - m.k_offset - k0;
   jhi = min(hi - m.k_offset, m.k_valid - 1) - k0;
 }
 
-// Compiled for 256 threads x 2 CTAs per SM (128 registers); launched with kThreads.
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
            const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  FwdSmem& sm = *reinterpret_cast<FwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
 
   const bma_attn_args& a = p.a;
-  const int qi = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest causal tiles first
+  const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest causal tiles first
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (a.Hq / a.Hkv);
-  const int q0 = qi * BM;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wg = warp >> 2;
+  const int NQ = p.l.NQ, NKV = p.l.NKV;
 
-  // block lists of this q tile
+  if ((smem_u32(smem_raw) & 1023u) != 0u) {  // the swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) report_device_error(p.status, 101);
+    return;
+  }
+
+  // ---- merged kv list of the two query tiles ------------------------------------------------
   const int lb = p.l.B == 1 ? 0 : b, lh = p.l.H == 1 ? 0 : h;
-  const int64_t lrow = ((int64_t)lb * p.l.H + lh) * p.l.NQ + qi;
-  const int nfull = p.l.full_kv_num[lrow], npart = p.l.kv_num[lrow];
-  const int32_t* full_idx = p.l.full_kv_idx + lrow * p.l.NKV;
-  const int32_t* part_idx = p.l.kv_idx + lrow * p.l.NKV;
-  const int ntiles = nfull + npart;
-
+  for (int i = threadIdx.x; i < NKV; i += kThreads) { sm.cls[0][i] = 0; sm.cls[1][i] = 0; }
   if (threadIdx.x == 0) {
     mbar_init(&sm.bar[BAR_Q], 1);
-    mbar_init(&sm.bar[BAR_K], 1);
-    mbar_init(&sm.bar[BAR_V], 1);
-    mbar_init(&sm.bar[BAR_S], 1);
-    mbar_init(&sm.bar[BAR_P], kSoftmaxThreads);
-    mbar_init(&sm.bar[BAR_O], 1);
-    sm.abort = 0;
+    for (int i = BAR_K_FULL0; i < NUM_BARS; ++i) mbar_init(&sm.bar[i], (i == BAR_P0 || i == BAR_P1) ? 128 : 1);
     fence_barrier_init();
   }
-  if (warp == 4) {
+  __syncthreads();
+  for (int x = 0; x < 2; ++x) {
+    const int qi = pair * 2 + x;
+    if (qi >= NQ) break;
+    const int64_t lrow = ((int64_t)lb * p.l.H + lh) * NQ + qi;
+    const int nfull = p.l.full_kv_num[lrow], npart = p.l.kv_num[lrow];
+    const int32_t* full_idx = p.l.full_kv_idx + lrow * NKV;
+    const int32_t* part_idx = p.l.kv_idx + lrow * NKV;
+    for (int i = threadIdx.x; i < nfull; i += kThreads) sm.cls[x][full_idx[i]] = 2;
+    for (int i = threadIdx.x; i < npart; i += kThreads) sm.cls[x][part_idx[i]] = 1;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int count = 0;
+    for (int base = 0; base < NKV; base += 32) {
+      const int j = base + lane;
+      const uint32_t ca = j < NKV ? sm.cls[0][j] : 0, cb = j < NKV ? sm.cls[1][j] : 0;
+      const unsigned m = __ballot_sync(0xffffffffu, (ca | cb) != 0);
+      if (ca | cb) sm.merged[count + __popc(m & ((1u << lane) - 1))] = (uint32_t)j | (ca << 16) | (cb << 18);
+      count += __popc(m);
+    }
+    if (lane == 0) sm.n_merged = count;
+  }
+  if (warp == 8) {
     tmem_alloc(&sm.tmem_base, kTmemCols);
     tmem_relinquish();
   }
@@ -110,92 +146,139 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
-  const uint32_t tmem_s = tmem, tmem_p = tmem, tmem_o = tmem + 128;
+  const int T = sm.n_merged;
 
-  if (warp == 4) {
-    // ------------------------------------------------------------------ producer / MMA issuer
-    if (lane == 0 && ntiles > 0) {
+  if (wg == 2) {
+    setmaxnreg_dec_72();
+    if (warp == 8 && lane == 0 && T > 0) {
+      // ---------------------------------------------------------------- TMA producer
       prefetch_tensormap(&map_q);
       prefetch_tensormap(&map_k);
       prefetch_tensormap(&map_v);
-      constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
-      constexpr uint32_t idesc_o = make_idesc_bf16(BM, HD, 0, 1);
-      const uint32_t q_addr = smem_u32(sm.q), k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v);
-      bool ok = true;
-
       auto load_tile = [&](const CUtensorMap* m, uint8_t* dst, uint64_t* bar, int head, int row0) {
-        mbar_expect_tx(bar, kTileBytes);
         tma_load_4d(dst, m, bar, 0, head, row0, b);
         tma_load_4d(dst + kHalfTile, m, bar, 64, head, row0, b);
       };
-      auto tile_of = [&](int it) { return it < nfull ? full_idx[it] : part_idx[it - nfull]; };
-
-      load_tile(&map_q, sm.q, &sm.bar[BAR_Q], h, q0);
-      load_tile(&map_k, sm.k, &sm.bar[BAR_K], hk, tile_of(0) * BN);
-      load_tile(&map_v, sm.v, &sm.bar[BAR_V], hk, tile_of(0) * BN);
-      ok = mbar_wait(&sm.bar[BAR_Q], 0);
-
-      for (int it = 0; it < ntiles && ok; ++it) {
-        const uint32_t ph = it & 1;
-        // ---- S = Q K^T
-        ok = ok && mbar_wait(&sm.bar[BAR_K], ph);
+      mbar_expect_tx(&sm.bar[BAR_Q], 2 * kTileBytes);  // a tile past the end is zero-filled by TMA
+      load_tile(&map_q, sm.q[0], &sm.bar[BAR_Q], h, pair * 2 * BM);
+      load_tile(&map_q, sm.q[1], &sm.bar[BAR_Q], h, (pair * 2 + 1) * BM);
+      bool ok = true;
+      for (int n = 0; n < T && ok; ++n) {
+        const int st = n & 1;
+        const int row0 = (int)(sm.merged[n] & 0xffffu) * BN;
+        if (n >= 2) ok = mbar_wait(&sm.bar[BAR_K_FREE0 + st], ((n >> 1) - 1) & 1);
         if (!ok) break;
-        tc_fence_after();
+        mbar_expect_tx(&sm.bar[BAR_K_FULL0 + st], kTileBytes);
+        load_tile(&map_k, sm.k[st], &sm.bar[BAR_K_FULL0 + st], hk, row0);
+        if (n >= 2) ok = mbar_wait(&sm.bar[BAR_V_FREE0 + st], ((n >> 1) - 1) & 1);
+        if (!ok) break;
+        mbar_expect_tx(&sm.bar[BAR_V_FULL0 + st], kTileBytes);
+        load_tile(&map_v, sm.v[st], &sm.bar[BAR_V_FULL0 + st], hk, row0);
+      }
+      if (!ok) report_device_error(p.status, 110);
+    } else if (warp == 9 && lane == 0 && T > 0) {
+      // ---------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc_bf16(BM, HD, 0, 1);
+      const uint32_t q_addr[2] = {smem_u32(sm.q[0]), smem_u32(sm.q[1])};
+      const uint32_t k_addr[2] = {smem_u32(sm.k[0]), smem_u32(sm.k[1])};
+      const uint32_t v_addr[2] = {smem_u32(sm.v[0]), smem_u32(sm.v[1])};
+      int cnt[2] = {0, 0};  // tiles already multiplied into O_x (also the phase counter of BAR_P)
+      bool ok = mbar_wait(&sm.bar[BAR_Q], 0);
+
+      auto issue_s = [&](int x, int st) {
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t off = (ks >> 2) * kHalfTile + (ks & 3) * 32;  // 64-column box, then 32 B per k-step
-          mma_ss(tmem_s, make_smem_desc(q_addr + off, 16, 1024), make_smem_desc(k_addr + off, 16, 1024), idesc_s, ks > 0);
+          mma_ss(tmem + x * 128, make_smem_desc(q_addr[x] + off, 16, 1024), make_smem_desc(k_addr[st] + off, 16, 1024), idesc_s, ks > 0);
         }
-        mma_commit(&sm.bar[BAR_S]);
-        // K buffer is free once S is done: prefetch the next K tile
-        ok = mbar_wait(&sm.bar[BAR_S], ph);
-        if (!ok) break;
-        if (it + 1 < ntiles) load_tile(&map_k, sm.k, &sm.bar[BAR_K], hk, tile_of(it + 1) * BN);
-        // ---- O (+)= P V
-        ok = mbar_wait(&sm.bar[BAR_P], ph) && mbar_wait(&sm.bar[BAR_V], ph);
-        if (!ok) break;
+        mma_commit(&sm.bar[BAR_S0 + x]);
+      };
+      if (ok) ok = mbar_wait(&sm.bar[BAR_K_FULL0], 0);
+      if (ok) {
         tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks) {
-          // B = V[kv rows][d]: MN-major; 16 kv rows per k-step = 2048 B; the two 64-column boxes are kHalfTile apart
-          mma_ts(tmem_o, tmem_p + ks * 8, make_smem_desc(v_addr + ks * 2048, kHalfTile, 1024), idesc_o, (it > 0) || (ks > 0));
-        }
-        mma_commit(&sm.bar[BAR_O]);
-        ok = mbar_wait(&sm.bar[BAR_O], ph);
+        const uint32_t e = sm.merged[0];
+        if ((e >> 16) & 3u) issue_s(0, 0);
+        if ((e >> 18) & 3u) issue_s(1, 0);
+        mma_commit(&sm.bar[BAR_K_FREE0]);
+      }
+      for (int n = 0; n < T && ok; ++n) {
+        const int st = n & 1;
+        const uint32_t e = sm.merged[n];
+        const uint32_t e_next = (n + 1 < T) ? sm.merged[n + 1] : 0u;
+        ok = mbar_wait(&sm.bar[BAR_V_FULL0 + st], (n >> 1) & 1);
+        if (ok && n + 1 < T) ok = mbar_wait(&sm.bar[BAR_K_FULL0 + (st ^ 1)], ((n + 1) >> 1) & 1);
         if (!ok) break;
-        if (it + 1 < ntiles) load_tile(&map_v, sm.v, &sm.bar[BAR_V], hk, tile_of(it + 1) * BN);
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if ((e >> (16 + 2 * x)) & 3u) {
+            ok = mbar_wait(&sm.bar[BAR_P0 + x], cnt[x] & 1);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < BN / 16; ++ks) {
+              // B = V[kv rows][d] read MN-major: 16 kv rows per k-step = 2048 B; the two 64-column boxes are kHalfTile apart
+              mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, make_smem_desc(v_addr[st] + ks * 2048, kHalfTile, 1024),
+                     idesc_o, (cnt[x] > 0) || (ks > 0));
+            }
+            mma_commit(&sm.bar[BAR_O0 + x]);
+            ++cnt[x];
+          }
+          if ((e_next >> (16 + 2 * x)) & 3u) issue_s(x, st ^ 1);
+        }
+        if (!ok) break;
+        mma_commit(&sm.bar[BAR_V_FREE0 + st]);
+        if (n + 1 < T) mma_commit(&sm.bar[BAR_K_FREE0 + (st ^ 1)]);
       }
-      if (!ok) {
-        report_device_error(p.status, 100 + BAR_S);
-        atomicExch(&sm.abort, 1);
-      }
+      if (!ok) report_device_error(p.status, 120);
     }
   } else {
-    // ------------------------------------------------------------------ softmax warps
-    const int row = threadIdx.x;  // TMEM lane == query row of the tile
-    const int q = q0 + row;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    // ------------------------------------------------------------------ softmax warpgroups
+    setmaxnreg_inc_216();
+    const int x = wg;                         // which query tile of the pair
+    const int qi = pair * 2 + x;
+    const int row = threadIdx.x & 127;        // TMEM lane == query row of the tile
+    const int q = qi * BM + row;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem + x * 128 + lane_base, tmem_o = tmem + 256 + x * 128 + lane_base;
     const MaskView mv = make_mask_view(p.spec, b, h);
     float m_ref = -INFINITY;  // reference max (log2 domain) the exponentials are taken against
     float l = 0.f;
     bool ok = true;
+    int cnt = 0;
 
-    for (int it = 0; it < ntiles; ++it) {
-      const uint32_t ph = it & 1;
-      const bool partial = it >= nfull;
-      const int k0 = (partial ? part_idx[it - nfull] : full_idx[it]) * BN;
-      ok = mbar_wait(&sm.bar[BAR_S], ph);
+    for (int n = 0; n < T; ++n) {
+      const uint32_t e = sm.merged[n];
+      const uint32_t cls = (e >> (16 + 2 * x)) & 3u;
+      if (cls == 0) continue;
+      const int k0 = (int)(e & 0xffffu) * BN;
+      ok = mbar_wait(&sm.bar[BAR_S0 + x], cnt & 1);
       if (!ok) break;
       tc_fence_after();
-      // allowed-key bits of this row for the four 32-column chunks (all ones on full tiles)
-      uint32_t bits[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
-      if (partial) {
+      float s[BN];
+      {
+        uint32_t r0[32], r1[32], r2[32], r3[32];
+        tmem_ld32(tmem_s + 0, r0);
+        tmem_ld32(tmem_s + 32, r1);
+        tmem_ld32(tmem_s + 64, r2);
+        tmem_ld32(tmem_s + 96, r3);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          s[j] = __uint_as_float(r0[j]);
+          s[32 + j] = __uint_as_float(r1[j]);
+          s[64 + j] = __uint_as_float(r2[j]);
+          s[96 + j] = __uint_as_float(r3[j]);
+        }
+      }
+      if (cls == 1) {  // partial tile: masked scores become -inf (their exponential is exactly 0)
+        uint32_t bits[4];
         if (p.interval_mask) {
           int jlo, jhi;
           row_interval(mv, q, k0, jlo, jhi);
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            const int lo = max(jlo - c * 32, 0), hi = min(jhi - c * 32, 31);  // chunk-local inclusive range
+            const int lo = max(jlo - c * 32, 0), hi = min(jhi - c * 32, 31);
             bits[c] = (lo <= hi) ? ((0xffffffffu >> (31 - hi)) & (0xffffffffu << lo)) : 0u;
           }
         } else {
@@ -207,20 +290,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             bits[c] = w;
           }
         }
-      }
-      // pass 1: row maximum of the allowed scores
-      float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_s + lane_base + c * 32, r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float v = (bits[c] >> j) & 1u ? __uint_as_float(r[j]) : -INFINITY;
-          mx = fmaxf(mx, v);
-        }
+        for (int j = 0; j < BN; ++j) s[j] = (bits[j >> 5] >> (j & 31)) & 1u ? s[j] : -INFINITY;
       }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < BN; j += 8) {
+        mx0 = max3(mx0, s[j], s[j + 1]);
+        mx1 = max3(mx1, s[j + 2], s[j + 3]);
+        mx2 = max3(mx2, s[j + 4], s[j + 5]);
+        mx3 = max3(mx3, s[j + 6], s[j + 7]);
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_cand = fmaxf(m_ref, mx * p.scale_log2);
       // lazy rescale: keep the old reference unless the maximum grew by more than 2^threshold
       const bool grow = (m_cand - m_ref) > kRescaleThreshold;  // also true when m_ref == -inf and m_cand is finite
@@ -229,65 +310,65 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         alpha = ex2(m_ref - m_cand);  // 0 when m_ref == -inf
         m_ref = m_cand;
       }
-      if (it > 0 && __any_sync(0xffffffffu, grow)) {
+      if (cnt > 0 && __any_sync(0xffffffffu, grow)) {
+        // O_x must be quiescent: the previous P V of this tile has to be complete
+        ok = mbar_wait(&sm.bar[BAR_O0 + x], (cnt - 1) & 1);
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
-          tmem_ld32(tmem_o + lane_base + c * 32, r);
+          tmem_ld32(tmem_o + c * 32, r);
           tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
-          tmem_st32(tmem_o + lane_base + c * 32, r);
+          tmem_st32(tmem_o + c * 32, r);
         }
       }
-      // keep the compiler from carrying 128 per-element predicates from pass 1 into pass 2
-#pragma unroll
-      for (int c = 0; c < 4; ++c) asm volatile("" : "+r"(bits[c]));
-      // pass 2: exponentials, row sum, P as bf16 into the S columns already consumed
       const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float rs = 0.f;
+      float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_s + lane_base + c * 32, r);
-        tmem_wait_ld();
-        uint32_t pk[16];
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[32];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float e0 = ex2(fmaf(__uint_as_float(r[2 * j]), p.scale_log2, -m_sub));
-          float e1 = ex2(fmaf(__uint_as_float(r[2 * j + 1]), p.scale_log2, -m_sub));
-          e0 = (bits[c] >> (2 * j)) & 1u ? e0 : 0.f;
-          e1 = (bits[c] >> (2 * j + 1)) & 1u ? e1 : 0.f;
-          rs += e0 + e1;
+        for (int j = 0; j < 32; j += 2) {
+          const float e0 = ex2(fmaf(s[c * 64 + 2 * j], p.scale_log2, -m_sub));
+          const float e1 = ex2(fmaf(s[c * 64 + 2 * j + 1], p.scale_log2, -m_sub));
+          const float e2 = ex2(fmaf(s[c * 64 + 2 * j + 2], p.scale_log2, -m_sub));
+          const float e3 = ex2(fmaf(s[c * 64 + 2 * j + 3], p.scale_log2, -m_sub));
+          rs0 += e0; rs1 += e1; rs2 += e2; rs3 += e3;
           pk[j] = pack_bf16(e0, e1);
+          pk[j + 1] = pack_bf16(e2, e3);
         }
-        tmem_st16(tmem_p + lane_base + c * 16, pk);
+        tmem_st32(tmem_s + c * 32, pk);
       }
-      l = l * alpha + rs;
+      l = l * alpha + ((rs0 + rs1) + (rs2 + rs3));
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&sm.bar[BAR_P]);
+      mbar_arrive(&sm.bar[BAR_P0 + x]);
+      ++cnt;
     }
 
     // ---- epilogue: O / l and the log-sum-exp
-    if (ok && ntiles > 0) ok = mbar_wait(&sm.bar[BAR_O], (ntiles - 1) & 1);
+    if (ok && cnt > 0) ok = mbar_wait(&sm.bar[BAR_O0 + x], (cnt - 1) & 1);
     if (!ok) {
       report_device_error(p.status, 200 + warp);
-    } else {
+    } else if (qi < NQ) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const bool store = q < a.N;
+      const int qs = store ? q : 0;
       float* of = nullptr;
       __nv_bfloat16* ob = nullptr;
       if (a.o.dtype == BMA_DTYPE_F32)
-        of = static_cast<float*>(a.o.ptr) + (int64_t)b * a.o.stride_b + (int64_t)q * a.o.stride_l + (int64_t)h * a.o.stride_h;
+        of = static_cast<float*>(a.o.ptr) + (int64_t)b * a.o.stride_b + (int64_t)qs * a.o.stride_l + (int64_t)h * a.o.stride_h;
       else
-        ob = static_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)b * a.o.stride_b + (int64_t)q * a.o.stride_l + (int64_t)h * a.o.stride_h;
+        ob = static_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)b * a.o.stride_b + (int64_t)qs * a.o.stride_l + (int64_t)h * a.o.stride_h;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
-        if (ntiles > 0) {
-          tmem_ld32(tmem_o + lane_base + c * 32, r);
+        if (cnt > 0) {
+          tmem_ld32(tmem_o + c * 32, r);
           tmem_wait_ld();
         } else {
 #pragma unroll
@@ -322,7 +403,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   // ---- teardown: every thread arrives here (all waits above are bounded)
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, kTmemCols);
+  if (warp == 8) tmem_dealloc(tmem, kTmemCols);
 }
 
 }  // namespace
@@ -375,11 +456,13 @@ bool sm100_supported(const bma_attn_args& a) {
     else { (void)cudaGetLastError(); return false; }
   }
   if (cc_major != 10) return false;
-  return a.d == HD && tma_compatible(a.q) && tma_compatible(a.k) && tma_compatible(a.v);
+  return a.d == HD && tma_compatible(a.q) && tma_compatible(a.k) && tma_compatible(a.v) &&
+         ceil_div(a.L, BN) <= kMaxKvTiles;
 }
 
 int sm100_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, cudaStream_t st) {
   BMA_REQUIRE(lists.q_block == BM && lists.kv_block == BN, BMA_ERR_ARG);
+  BMA_REQUIRE(lists.NKV <= kMaxKvTiles, BMA_ERR_LIMIT);
   BMA_REQUIRE(a.o.dtype == BMA_DTYPE_F32 || a.o.dtype == BMA_DTYPE_BF16, BMA_ERR_UNSUPPORTED);
   BMA_REQUIRE((reinterpret_cast<uintptr_t>(a.o.ptr) & 15) == 0 && a.o.stride_b % 8 == 0 && a.o.stride_l % 8 == 0 &&
                   a.o.stride_h % 8 == 0,
@@ -395,9 +478,9 @@ int sm100_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   p.interval_mask = (spec.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP)) ? 0 : 1;
   p.status = device_status_ptr();
   BMA_REQUIRE(p.status != nullptr, BMA_ERR_CUDA);
-  const size_t smem = sizeof(FwdSmem) + 1024;
+  const size_t smem = sizeof(FwdSmem);
   BMA_CUDA_TRY(cudaFuncSetAttribute(fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid(ceil_div(a.N, BM), a.Hq, a.B);
+  dim3 grid(ceil_div(ceil_div(a.N, BM), 2), a.Hq, a.B);
   fwd_kernel<<<grid, kThreads, smem, st>>>(mq, mk, mv, p);
   count_launches(1);
   BMA_CUDA_TRY(cudaGetLastError());
