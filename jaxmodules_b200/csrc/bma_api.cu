@@ -50,7 +50,18 @@ int* device_status_ptr() {
 namespace {
 
 // ---- backward preprocess: delta = rowsum(dO * O), optional bf16 copy of dO ---------------
-template <typename TO, typename TDO>
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+  const float4 x = *reinterpret_cast<const float4*>(p);
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 x = *reinterpret_cast<const uint2*>(p);
+  v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
+  v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
+}
+
+// One warp per (b, q, h) row.  VEC: 4-element vector accesses (d % 4 == 0, 16-byte aligned rows).
+template <typename TO, typename TDO, bool VEC>
 __global__ void bwd_preprocess_kernel(bma_attn_args a, __nv_bfloat16* __restrict__ do_bf16) {
   const int lane = threadIdx.x & 31;
   const int64_t rows = (int64_t)a.B * a.N * a.Hq;
@@ -62,10 +73,27 @@ __global__ void bwd_preprocess_kernel(bma_attn_args a, __nv_bfloat16* __restrict
     const TO* o = static_cast<const TO*>(a.o.ptr) + (int64_t)b * a.o.stride_b + (int64_t)q * a.o.stride_l + (int64_t)h * a.o.stride_h;
     const TDO* g = static_cast<const TDO*>(a.d_o.ptr) + (int64_t)b * a.d_o.stride_b + (int64_t)q * a.d_o.stride_l + (int64_t)h * a.d_o.stride_h;
     float acc = 0.f;
-    for (int c = lane; c < a.d; c += 32) {
-      const float gv = to_float(g[c]);
-      acc = fmaf(gv, to_float(o[c]), acc);
-      if (do_bf16) do_bf16[r * a.d + c] = __float2bfloat16_rn(gv);
+    if (VEC) {
+      for (int c = lane * 4; c < a.d; c += 128) {
+        float gv[4], ov[4];
+        load4(g + c, gv);
+        load4(o + c, ov);
+        acc = fmaf(gv[0], ov[0], acc); acc = fmaf(gv[1], ov[1], acc);
+        acc = fmaf(gv[2], ov[2], acc); acc = fmaf(gv[3], ov[3], acc);
+        if (do_bf16) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(gv[0], gv[1]), hi = __floats2bfloat162_rn(gv[2], gv[3]);
+          uint2 w;
+          w.x = *reinterpret_cast<uint32_t*>(&lo);
+          w.y = *reinterpret_cast<uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(do_bf16 + r * a.d + c) = w;
+        }
+      }
+    } else {
+      for (int c = lane; c < a.d; c += 32) {
+        const float gv = to_float(g[c]);
+        acc = fmaf(gv, to_float(o[c]), acc);
+        if (do_bf16) do_bf16[r * a.d + c] = __float2bfloat16_rn(gv);
+      }
     }
     for (int off = 16; off; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
     if (lane == 0) a.delta[((int64_t)b * a.Hq + h) * a.N + q] = acc;
@@ -242,10 +270,20 @@ int bma_attn_bwd_preprocess(const bma_attn_args* args, void* d_o_bf16, bma_strea
   const int grid = (int)std::min<int64_t>((rows + 7) / 8, (int64_t)sm_count() * 16);
   __nv_bfloat16* out = static_cast<__nv_bfloat16*>(d_o_bf16);
   const bool of = args->o.dtype == BMA_DTYPE_F32, gf = args->d_o.dtype == BMA_DTYPE_F32;
-  if (of && gf) bwd_preprocess_kernel<float, float><<<grid, 256, 0, st>>>(*args, out);
-  else if (of) bwd_preprocess_kernel<float, __nv_bfloat16><<<grid, 256, 0, st>>>(*args, out);
-  else if (gf) bwd_preprocess_kernel<__nv_bfloat16, float><<<grid, 256, 0, st>>>(*args, out);
-  else bwd_preprocess_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>(*args, out);
+  auto vec_ok = [&](const bma_tensor& t) {
+    return (reinterpret_cast<uintptr_t>(t.ptr) & 15) == 0 && t.stride_b % 4 == 0 && t.stride_l % 4 == 0 && t.stride_h % 4 == 0;
+  };
+  const bool vec = args->d % 4 == 0 && vec_ok(args->o) && vec_ok(args->d_o) && (reinterpret_cast<uintptr_t>(out) & 7) == 0;
+#define BMA_PRE(TO, TDO)                                                                   \
+  do {                                                                                     \
+    if (vec) bwd_preprocess_kernel<TO, TDO, true><<<grid, 256, 0, st>>>(*args, out);       \
+    else bwd_preprocess_kernel<TO, TDO, false><<<grid, 256, 0, st>>>(*args, out);          \
+  } while (0)
+  if (of && gf) BMA_PRE(float, float);
+  else if (of) BMA_PRE(float, __nv_bfloat16);
+  else if (gf) BMA_PRE(__nv_bfloat16, float);
+  else BMA_PRE(__nv_bfloat16, __nv_bfloat16);
+#undef BMA_PRE
   count_launches(1);
   BMA_CUDA_TRY(cudaGetLastError());
   return BMA_OK;

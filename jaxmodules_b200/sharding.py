@@ -1,0 +1,155 @@
+"""Multi-GPU execution of the attention path: one process per GPU.
+
+Attention is independent per (batch, kv-head group) — the reference has no cross-(b, h) term
+(jaxmodules/attention.py:70-105 is batched over B and H only element-wise) — so the default
+partition deals contiguous ranges of the ``B * Hkv`` units to the ranks and needs no collective
+(``shard_units`` / ``sharded_attention``).
+
+For sequences too long for one device the sequence axis can be split instead
+(``ring_attention_forward``): every rank keeps its query chunk, the K/V chunks rotate around the
+ring with point-to-point sends (``torch.distributed`` over NCCL on GPUs) into local buffers, every
+step attends one chunk with global query/key offsets in the mask, and the partial results are
+merged with their log-sum-exps.  The reference itself is single-device; this mode has no
+counterpart there.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Callable, List, Optional, Tuple
+
+import torch
+
+from . import _native as nat
+from . import masks as _masks
+
+
+def shard_range(units: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous [lo, hi) of ``units`` items for ``rank``: sizes differ by at most one."""
+    if not (0 <= rank < world):
+        raise ValueError("rank outside the world")
+    base, extra = divmod(units, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def shard_units(B: int, Hkv: int, rank: int, world: int) -> List[Tuple[int, int, int]]:
+    """The (batch, kv_head_lo, kv_head_hi) slices that make up this rank's range of the
+    flattened ``B * Hkv`` units; a kv head's query-head group always stays together."""
+    lo, hi = shard_range(B * Hkv, rank, world)
+    out = []
+    u = lo
+    while u < hi:
+        b, h0 = divmod(u, Hkv)
+        h1 = min(Hkv, h0 + (hi - u))
+        out.append((b, h0, h1))
+        u += h1 - h0
+    return out
+
+
+def _offset_mask(mask_fn, b0: int, h0: int):
+    """The same mask seen from a shard whose batch / query-head indices start at (b0, h0)."""
+    if mask_fn is None:
+        return None
+    if isinstance(mask_fn, _masks.StructuredMask):
+        t = mask_fn.terms
+        if t.bitmap is not None:
+            raise NotImplementedError("table-backed masks cannot be re-indexed for a shard; use a callable")
+        if t.seg_q is None:
+            return mask_fn
+        terms = _masks.MaskTerms(causal=t.causal, band=t.band, seg_q=t.seg_q[b0:b0 + 1], seg_k=t.seg_k[b0:b0 + 1],
+                                 window=t.window, q_offset=t.q_offset, k_offset=t.k_offset)
+        return _masks.StructuredMask(terms, lambda b, h, q, k: mask_fn(b + b0, h + h0, q, k), mask_fn.__name__)
+    if _masks.argcount(mask_fn) == 3:
+        return lambda h, q, k: mask_fn(h + h0, q, k)
+    return lambda b, h, q, k: mask_fn(b + b0, h + h0, q, k)
+
+
+def sharded_attention(Q, K, V, *, rank: int, world: int, attend: Optional[Callable] = None, **kwargs):
+    """Runs this rank's share of ``masked_attention_via_map(Q, K, V, **kwargs)``.
+
+    Q, K, V are the full tensors (or views of them) visible to this process; the result is a
+    list of ``((b, hq_lo, hq_hi), O_slice)`` for the slices of ``shard_units``.  No communication
+    happens here; gather the slices only if one array is wanted.  ``attend`` replaces the CUDA
+    call (tests inject a CPU stand-in)."""
+    if attend is None:
+        from .attention import masked_attention_via_map as attend
+    B, N, Hq, d = Q.shape
+    Hkv = K.shape[2]
+    G = Hq // Hkv
+    out = []
+    mask_fn = kwargs.pop("mask_fn", None)
+    for b, h0, h1 in shard_units(B, Hkv, rank, world):
+        q = Q[b:b + 1, :, h0 * G:h1 * G]
+        k = K[b:b + 1, :, h0:h1]
+        v = V[b:b + 1, :, h0:h1]
+        o = attend(q, k, v, mask_fn=_offset_mask(mask_fn, b, h0 * G), **kwargs)
+        out.append(((b, h0 * G, h1 * G), o))
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# ring sequence partition (forward)
+# ---------------------------------------------------------------------------------------------
+
+def cuda_attend(Q, K, V, terms: _masks.MaskTerms):
+    """One partial attention on the CUDA kernels: (O float32, lse)."""
+    from .attention import attention_forward
+    O, lse, _ = attention_forward(Q, K, V, terms, out_dtype=torch.float32)
+    return O, lse
+
+
+def cuda_merge(O, lse, O2, lse2):
+    """In-place merge of (O2, lse2) into (O, lse) with ``bma_attn_merge``."""
+    from .attention import _tensor
+    a = nat.AttnArgs()
+    a.B, a.N, a.Hq, a.d = O.shape
+    a.L, a.Hkv = 1, a.Hq
+    a.o, a.d_o = _tensor(O), _tensor(O2)
+    a.lse, a.delta = lse.data_ptr(), lse2.data_ptr()
+    with torch.cuda.device(O.device):
+        nat.check(nat.lib().bma_attn_merge(C.byref(a), torch.cuda.current_stream(O.device).cuda_stream), "bma_attn_merge")
+    return O, lse
+
+
+def ring_schedule(rank: int, world: int) -> List[int]:
+    """Owner of the K/V chunk a rank holds at each ring step: its own first, then the chunks of
+    its predecessors as they arrive from rank-1."""
+    return [(rank - s) % world for s in range(world)]
+
+
+def ring_attention_forward(Q, K, V, *, rank: int, world: int, is_causal: bool = False,
+                           terms: Optional[_masks.MaskTerms] = None, group=None,
+                           attend: Callable = cuda_attend, merge: Callable = cuda_merge):
+    """Forward attention over a sequence split into ``world`` contiguous chunks.
+
+    Q ``[B, N/world, Hq, d]`` and K, V ``[B, L/world, Hkv, d]`` are this rank's chunks (equal
+    sizes on every rank).  Returns (O float32, lse) for the local queries.  Each step posts the
+    send of the chunk it holds to rank+1 and the receive of the next chunk from rank-1 before it
+    computes, so the transfer runs under the kernels; received data always lands in this
+    device's own memory before a kernel reads it."""
+    import torch.distributed as dist
+    terms = terms or _masks.MaskTerms(causal=is_causal)
+    n_local, l_local = Q.shape[1], K.shape[1]
+    k_cur, v_cur = K.contiguous(), V.contiguous()
+    O = lse = None
+    for s, owner in enumerate(ring_schedule(rank, world)):
+        reqs = []
+        if s + 1 < world:
+            k_nxt, v_nxt = torch.empty_like(k_cur), torch.empty_like(v_cur)
+            dst, src = (rank + 1) % world, (rank - 1) % world
+            ops = [dist.P2POp(dist.isend, k_cur, dst, group), dist.P2POp(dist.isend, v_cur, dst, group),
+                   dist.P2POp(dist.irecv, k_nxt, src, group), dist.P2POp(dist.irecv, v_nxt, src, group)]
+            reqs = dist.batch_isend_irecv(ops)
+        step_terms = _masks.MaskTerms(
+            causal=terms.causal, band=terms.band, seg_q=terms.seg_q, seg_k=terms.seg_k, window=terms.window,
+            bitmap=terms.bitmap, q_offset=terms.q_offset + rank * n_local, k_offset=terms.k_offset + owner * l_local)
+        O_s, lse_s = attend(Q, k_cur, v_cur, step_terms)
+        if O is None:
+            O, lse = O_s, lse_s
+        else:
+            O, lse = merge(O, lse, O_s, lse_s)
+        for r in reqs:
+            r.wait()
+        if s + 1 < world:
+            k_cur, v_cur = k_nxt, v_nxt
+    return O, lse

@@ -7,6 +7,7 @@ bfloat16 I/O max-abs 2e-2, mean-abs 2e-3.  The max-abs bound is applied as
 |got - ref| <= tol * max(1, |ref|): gradients of unscaled N(0,1) inputs reach magnitudes of 8
 and more, where one bfloat16 ulp (2^-4 at 8) already exceeds an absolute 2e-2, so above 1 the
 bound is relative (2 %, i.e. ten bfloat16 roundings)."""
+import ctypes as C
 import math
 
 import numpy as np
@@ -203,3 +204,38 @@ def test_full_size_properties_config2():
     lhs = V.grad.float().sum(dim=1)
     rhs = dO.to(torch.bfloat16).float().sum(dim=1) if False else dO.sum(dim=1)
     assert (lhs - rhs).abs().max() / rhs.abs().max() < 2e-2
+
+
+def test_virtual_ring_offsets_and_merge():
+    """The sequence-partition path on one GPU: every (query chunk, key chunk) pair is attended with
+    global offsets in the mask description and merged with bma_attn_merge, exactly what the ring
+    does step by step; the result must match the unsplit attention."""
+    from jaxmodules_b200 import sharding as S
+    B, L, H, d, world = 1, 1024, 2, 128, 4
+    Q, K, V = (gen((B, L, H, d), i, torch.bfloat16).cuda() for i in range(3))
+    n = L // world
+    for terms in (M.MaskTerms(causal=True), M.MaskTerms(band=(300, 40))):
+        full, full_lse = S.cuda_attend(Q, K, V, terms)
+        for r in range(world):
+            O = lse = None
+            for owner in S.ring_schedule(r, world):
+                t = M.MaskTerms(causal=terms.causal, band=terms.band, q_offset=r * n, k_offset=owner * n)
+                O_s, lse_s = S.cuda_attend(Q[:, r * n:(r + 1) * n], K[:, owner * n:(owner + 1) * n].contiguous(),
+                                           V[:, owner * n:(owner + 1) * n].contiguous(), t)
+                O, lse = (O_s, lse_s) if O is None else S.cuda_merge(O, lse, O_s, lse_s)
+            torch.cuda.synchronize()
+            assert (O - full[:, r * n:(r + 1) * n]).abs().max() < 2e-3
+            sl = full_lse[:, :, r * n:(r + 1) * n]
+            finite = torch.isfinite(sl)
+            assert torch.equal(torch.isfinite(lse), finite) and (lse[finite] - sl[finite]).abs().max() < 1e-4
+
+
+def test_tensor_core_backend_is_selected():
+    """bf16 with head dim 128 must run on the tcgen05 kernels (no silent fall-back to SIMT)."""
+    from jaxmodules_b200 import attention as A
+    Q = torch.zeros(1, 256, 2, 128, dtype=torch.bfloat16, device="cuda")
+    assert A.plan(Q, Q, Q)[0] == nat.BMA_BACKEND_TCGEN05 and A.plan(Q, Q, Q, backward=True)[0] == nat.BMA_BACKEND_TCGEN05
+    Qf = torch.zeros(1, 256, 2, 64, dtype=torch.float32, device="cuda")
+    assert A.plan(Qf, Qf, Qf)[0] == nat.BMA_BACKEND_SIMT
+    rc = C.c_int32()
+    assert nat.lib().bma_device_status(torch.cuda.current_stream().cuda_stream, C.byref(rc)) == nat.BMA_OK and rc.value == 0
