@@ -34,12 +34,18 @@ constexpr uint32_t kHalfTile = BM * 64 * 2;     // one [128 x 64] bf16 box
 constexpr uint32_t kTileBytes = 2 * kHalfTile;  // a [128 x 128] operand tile
 constexpr float kRescaleThreshold = 8.0f;       // log2 units: rescale O only when the max grew by > 2^8
 constexpr int kMaxKvTiles = 4096;               // merged kv list kept in shared memory
+#ifndef BMA_FWD_POLY
+#define BMA_FWD_POLY 0
+#endif
+#ifndef BMA_FWD_SPLIT
+#define BMA_FWD_SPLIT 1
+#endif
 
 enum {
   BAR_Q = 0,
   BAR_K_FULL0, BAR_K_FULL1, BAR_K_FREE0, BAR_K_FREE1,
   BAR_V_FULL0, BAR_V_FULL1, BAR_V_FREE0, BAR_V_FREE1,
-  BAR_S0, BAR_S1, BAR_P0, BAR_P1, BAR_O0, BAR_O1,
+  BAR_S0, BAR_S1, BAR_PH0, BAR_PH1, BAR_P0, BAR_P1, BAR_O0, BAR_O1,
   NUM_BARS
 };
 
@@ -65,6 +71,16 @@ struct FwdParams {
 
 __device__ __forceinline__ void setmaxnreg_inc_216() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
 __device__ __forceinline__ void setmaxnreg_dec_72() { asm volatile("setmaxnreg.dec.sync.aligned.u32 72;"); }
+// 2^x on the FMA pipe (Cody-Waite split + degree-3 polynomial, relative error 1e-4, well below
+// the bf16 rounding of P): a share of the exponentials is taken off the MUFU unit, which is the
+// narrowest pipe of the softmax.
+__device__ __forceinline__ float exp2_fma(float x) {
+  x = fmaxf(x, -126.0f);
+  const float xr = x + 12582912.0f;  // 1.5 * 2^23: round(x) lands in the low mantissa bits
+  const float f = x - (xr - 12582912.0f);  // in [-0.5, 0.5]
+  const float pf = fmaf(fmaf(fmaf(0.05500893f, f, 0.24221096f), f, 0.69328293f), f, 1.0f);
+  return __int_as_float(__float_as_int(pf) + (__float_as_int(xr) << 23));
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -112,7 +128,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   for (int i = threadIdx.x; i < NKV; i += kThreads) { sm.cls[0][i] = 0; sm.cls[1][i] = 0; }
   if (threadIdx.x == 0) {
     mbar_init(&sm.bar[BAR_Q], 1);
-    for (int i = BAR_K_FULL0; i < NUM_BARS; ++i) mbar_init(&sm.bar[i], (i == BAR_P0 || i == BAR_P1) ? 128 : 1);
+    for (int i = BAR_K_FULL0; i < NUM_BARS; ++i)
+      mbar_init(&sm.bar[i], (i == BAR_P0 || i == BAR_P1 || i == BAR_PH0 || i == BAR_PH1) ? 128 : 1);
     fence_barrier_init();
   }
   __syncthreads();
@@ -212,15 +229,21 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if ((e >> (16 + 2 * x)) & 3u) {
-            ok = mbar_wait(&sm.bar[BAR_P0 + x], cnt[x] & 1);
-            if (!ok) break;
-            tc_fence_after();
+            // P arrives in two halves (keys 0..63, then 64..127) so that the first k-steps run under
+            // the second half of the exponentials
 #pragma unroll
-            for (int ks = 0; ks < BN / 16; ++ks) {
-              // B = V[kv rows][d] read MN-major: 16 kv rows per k-step = 2048 B; the two 64-column boxes are kHalfTile apart
-              mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, make_smem_desc(v_addr[st] + ks * 2048, kHalfTile, 1024),
-                     idesc_o, (cnt[x] > 0) || (ks > 0));
+            for (int hf = 0; hf < 2; ++hf) {
+              ok = mbar_wait(&sm.bar[(hf == 0 ? BAR_PH0 : BAR_P0) + x], cnt[x] & 1);
+              if (!ok) break;
+              tc_fence_after();
+#pragma unroll
+              for (int ks = hf * 4; ks < hf * 4 + 4; ++ks) {
+                // B = V[kv rows][d] read MN-major: 16 kv rows per k-step = 2048 B; the two 64-column boxes are kHalfTile apart
+                mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, make_smem_desc(v_addr[st] + ks * 2048, kHalfTile, 1024),
+                       idesc_o, (cnt[x] > 0) || (ks > 0));
+              }
             }
+            if (!ok) break;
             mma_commit(&sm.bar[BAR_O0 + x]);
             ++cnt[x];
           }
@@ -335,17 +358,29 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           const float e0 = ex2(fmaf(s[c * 64 + 2 * j], p.scale_log2, -m_sub));
           const float e1 = ex2(fmaf(s[c * 64 + 2 * j + 1], p.scale_log2, -m_sub));
           const float e2 = ex2(fmaf(s[c * 64 + 2 * j + 2], p.scale_log2, -m_sub));
+#if BMA_FWD_POLY
+          const float e3 = exp2_fma(fmaf(s[c * 64 + 2 * j + 3], p.scale_log2, -m_sub));
+#else
           const float e3 = ex2(fmaf(s[c * 64 + 2 * j + 3], p.scale_log2, -m_sub));
+#endif
           rs0 += e0; rs1 += e1; rs2 += e2; rs3 += e3;
           pk[j] = pack_bf16(e0, e1);
           pk[j + 1] = pack_bf16(e2, e3);
         }
         tmem_st32(tmem_s + c * 32, pk);
+#if BMA_FWD_SPLIT
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&sm.bar[(c == 0 ? BAR_PH0 : BAR_P0) + x]);
+#endif
       }
-      l = l * alpha + ((rs0 + rs1) + (rs2 + rs3));
+#if !BMA_FWD_SPLIT
       tmem_wait_st();
       tc_fence_before();
+      mbar_arrive(&sm.bar[BAR_PH0 + x]);
       mbar_arrive(&sm.bar[BAR_P0 + x]);
+#endif
+      l = l * alpha + ((rs0 + rs1) + (rs2 + rs3));
       ++cnt;
     }
 
