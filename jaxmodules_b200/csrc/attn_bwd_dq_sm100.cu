@@ -1,0 +1,404 @@
+// Backward dQ for bf16, head dim 128, on the sm_100a tensor core (tcgen05 + TMEM + TMA).
+//
+// Query-major, the mirror image of the forward kernel: one CTA per SM works on a PAIR of 128-query
+// tiles (2p, 2p+1) of one (batch, query head) and walks the union of the kv tiles their block
+// lists name; the dQ accumulators stay in tensor memory for the whole walk, so nothing is
+// reduced through global memory and the summation order is fixed.  Per (query tile, kv tile):
+//     S  = Q K^T             A = Q  (K-major),  B = K (K-major)      -> TMEM SD_x [x*128, +128)
+//     dP = dO V^T            A = dO (K-major),  B = V (K-major)      -> the same columns, once S is in registers
+//     dQ += dS K             A = dS (bf16 in TMEM over dP),  B = K (MN-major) -> TMEM [256 + x*128, +128)
+// with P = exp2(S*scale*log2e - lse*log2e) and dS = P * (dP - delta) computed by the warpgroup of
+// the tile (thread = query row, so lse and delta are per-thread scalars).  The exponentials run
+// while dO V^T executes, and the two query tiles alternate on the tensor core.
+//
+//   warpgroup 0 / 1: element-wise math of tile A / B;  warp 8: TMA (Q, dO once; K two stages,
+//   V one stage);  warp 9: tcgen05.mma issue.
+// Every mbarrier wait is bounded; on a timeout the thread records an error code and unwinds.
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace bma {
+namespace {
+
+using namespace ptx;
+
+constexpr int BM = kSm100Tile, BN = kSm100Tile, HD = 128;
+constexpr int kThreads = 384;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kHalfTile = BM * 64 * 2;
+constexpr uint32_t kTileBytes = 2 * kHalfTile;
+constexpr int kMaxKvTiles = 1024;  // merged kv list (16-bit entries) kept in shared memory: L <= 131072
+
+enum {
+  BAR_Q = 0,
+  BAR_K_FULL0, BAR_K_FULL1, BAR_K_FREE0, BAR_K_FREE1, BAR_V_FULL, BAR_V_FREE,
+  BAR_S0, BAR_S1, BAR_LS0, BAR_LS1, BAR_DP0, BAR_DP1, BAR_DS0, BAR_DS1, BAR_DQ0, BAR_DQ1,
+  NUM_BARS
+};
+
+struct __align__(1024) DqSmem {
+  uint8_t q[2][kTileBytes];
+  uint8_t d_o[2][kTileBytes];
+  uint8_t k[2][kTileBytes];
+  uint8_t v[kTileBytes];
+  uint16_t merged[kMaxKvTiles];  // kv tile | class for tile A << 12 | class for tile B << 14  (1 partial, 2 full)
+  uint64_t bar[NUM_BARS];
+  uint32_t tmem_base;
+  int n_merged;
+};
+
+struct DqParams {
+  bma_attn_args a;
+  bma_mask_spec spec;
+  bma_block_lists l;
+  float scale_log2;
+  int interval_mask;
+  int* status;
+};
+
+__device__ __forceinline__ void setmaxnreg_inc_216() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
+__device__ __forceinline__ void setmaxnreg_dec_72() { asm volatile("setmaxnreg.dec.sync.aligned.u32 72;"); }
+
+// Allowed key interval [jlo, jhi] (tile-local, inclusive) of query row q for interval-only masks.
+__device__ __forceinline__ void row_interval(const MaskView& m, int q, int k0, int& jlo, int& jhi) {
+  if (q >= m.q_valid) { jlo = 1; jhi = 0; return; }
+  const int gq = q + m.q_offset;
+  int lo = 0, hi = INT32_MAX;
+  if (m.flags & BMA_MASK_CAUSAL) hi = min(hi, gq);
+  if (m.flags & BMA_MASK_BAND) { lo = max(lo, gq - m.band_left); hi = min(hi, gq + m.band_right); }
+  if (m.flags & BMA_MASK_BLOCK_WINDOW) {
+    int wlo, whi;
+    block_window_range(m, gq, wlo, whi);
+    lo = max(lo, wlo);
+    hi = min(hi, whi - 1);
+  }
+  jlo = lo - m.k_offset - k0;
+  jhi = min(hi - m.k_offset, m.k_valid - 1) - k0;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+              const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const DqParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  DqSmem& sm = *reinterpret_cast<DqSmem*>(smem_raw);
+
+  const bma_attn_args& a = p.a;
+  const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest causal tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (a.Hq / a.Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wg = warp >> 2;
+  const int NQ = p.l.NQ, NKV = p.l.NKV;
+
+  if ((smem_u32(smem_raw) & 1023u) != 0u) {
+    if (threadIdx.x == 0) report_device_error(p.status, 401);
+    return;
+  }
+
+  // ---- merged kv list of the two query tiles ------------------------------------------------
+  const int lb = p.l.B == 1 ? 0 : b, lh = p.l.H == 1 ? 0 : h;
+  uint8_t* cls0 = sm.v;                 // scratch: the V stage is not loaded before the list is built
+  uint8_t* cls1 = sm.v + kMaxKvTiles;
+  for (int i = threadIdx.x; i < NKV; i += kThreads) { cls0[i] = 0; cls1[i] = 0; }
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NUM_BARS; ++i) {
+      const bool wide = i == BAR_LS0 || i == BAR_LS1 || i == BAR_DS0 || i == BAR_DS1;
+      mbar_init(&sm.bar[i], wide ? 128 : 1);
+    }
+    fence_barrier_init();
+  }
+  __syncthreads();
+  for (int x = 0; x < 2; ++x) {
+    const int qi = pair * 2 + x;
+    if (qi >= NQ) break;
+    const int64_t lrow = ((int64_t)lb * p.l.H + lh) * NQ + qi;
+    const int nfull = p.l.full_kv_num[lrow], npart = p.l.kv_num[lrow];
+    const int32_t* full_idx = p.l.full_kv_idx + lrow * NKV;
+    const int32_t* part_idx = p.l.kv_idx + lrow * NKV;
+    uint8_t* cls = x ? cls1 : cls0;
+    for (int i = threadIdx.x; i < nfull; i += kThreads) cls[full_idx[i]] = 2;
+    for (int i = threadIdx.x; i < npart; i += kThreads) cls[part_idx[i]] = 1;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int count = 0;
+    for (int base = 0; base < NKV; base += 32) {
+      const int j = base + lane;
+      const uint32_t ca = j < NKV ? cls0[j] : 0, cb = j < NKV ? cls1[j] : 0;
+      const unsigned m = __ballot_sync(0xffffffffu, (ca | cb) != 0);
+      if (ca | cb) sm.merged[count + __popc(m & ((1u << lane) - 1))] = (uint16_t)((uint32_t)j | (ca << 12) | (cb << 14));
+      count += __popc(m);
+    }
+    if (lane == 0) sm.n_merged = count;
+  }
+  if (warp == 8) {
+    tmem_alloc(&sm.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const int T = sm.n_merged;
+
+  if (wg == 2) {
+    setmaxnreg_dec_72();
+    if (warp == 8 && lane == 0 && T > 0) {
+      // ---------------------------------------------------------------- TMA producer
+      prefetch_tensormap(&map_q);
+      prefetch_tensormap(&map_k);
+      prefetch_tensormap(&map_v);
+      prefetch_tensormap(&map_do);
+      auto load_tile = [&](const CUtensorMap* m, uint8_t* dst, uint64_t* bar, int head, int row0) {
+        tma_load_4d(dst, m, bar, 0, head, row0, b);
+        tma_load_4d(dst + kHalfTile, m, bar, 64, head, row0, b);
+      };
+      mbar_expect_tx(&sm.bar[BAR_Q], 4 * kTileBytes);  // rows past the end are zero-filled by TMA
+      load_tile(&map_q, sm.q[0], &sm.bar[BAR_Q], h, pair * 2 * BM);
+      load_tile(&map_q, sm.q[1], &sm.bar[BAR_Q], h, (pair * 2 + 1) * BM);
+      load_tile(&map_do, sm.d_o[0], &sm.bar[BAR_Q], h, pair * 2 * BM);
+      load_tile(&map_do, sm.d_o[1], &sm.bar[BAR_Q], h, (pair * 2 + 1) * BM);
+      bool ok = true;
+      for (int n = 0; n < T && ok; ++n) {
+        const int st = n & 1;
+        const int row0 = (int)(sm.merged[n] & 0x3ffu) * BN;
+        if (n >= 2) ok = mbar_wait(&sm.bar[BAR_K_FREE0 + st], ((n >> 1) - 1) & 1);
+        if (!ok) break;
+        mbar_expect_tx(&sm.bar[BAR_K_FULL0 + st], kTileBytes);
+        load_tile(&map_k, sm.k[st], &sm.bar[BAR_K_FULL0 + st], hk, row0);
+        if (n >= 1) ok = mbar_wait(&sm.bar[BAR_V_FREE], (n - 1) & 1);
+        if (!ok) break;
+        mbar_expect_tx(&sm.bar[BAR_V_FULL], kTileBytes);
+        load_tile(&map_v, sm.v, &sm.bar[BAR_V_FULL], hk, row0);
+      }
+      if (!ok) report_device_error(p.status, 410);
+    } else if (warp == 9 && lane == 0 && T > 0) {
+      // ---------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc_kk = make_idesc_bf16(BM, BN, 0, 0);
+      constexpr uint32_t idesc_kn = make_idesc_bf16(BM, HD, 0, 1);
+      const uint32_t q_addr[2] = {smem_u32(sm.q[0]), smem_u32(sm.q[1])};
+      const uint32_t do_addr[2] = {smem_u32(sm.d_o[0]), smem_u32(sm.d_o[1])};
+      const uint32_t k_addr[2] = {smem_u32(sm.k[0]), smem_u32(sm.k[1])};
+      const uint32_t v_addr = smem_u32(sm.v);
+      int cnt[2] = {0, 0};  // tiles of x already folded into dQ_x (phase counter of the per-tile barriers)
+      bool ok = mbar_wait(&sm.bar[BAR_Q], 0);
+
+      auto issue_s = [&](int x, int st) {  // S_x = Q_x K^T
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * kHalfTile + (ks & 3) * 32;
+          mma_ss(tmem + x * 128, make_smem_desc(q_addr[x] + off, 16, 1024), make_smem_desc(k_addr[st] + off, 16, 1024), idesc_kk, ks > 0);
+        }
+        mma_commit(&sm.bar[BAR_S0 + x]);
+      };
+      if (ok) ok = mbar_wait(&sm.bar[BAR_K_FULL0], 0);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t e = sm.merged[0];
+        if ((e >> 12) & 3u) issue_s(0, 0);
+        if ((e >> 14) & 3u) issue_s(1, 0);
+      }
+      for (int n = 0; n < T && ok; ++n) {
+        const int st = n & 1;
+        const uint32_t e = sm.merged[n];
+        const uint32_t e_next = (n + 1 < T) ? sm.merged[n + 1] : 0u;
+        ok = mbar_wait(&sm.bar[BAR_V_FULL], n & 1);
+        if (!ok) break;
+        // dP_x = dO_x V^T into the S columns, as soon as the warpgroup holds S in registers
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (!((e >> (12 + 2 * x)) & 3u)) continue;
+          ok = mbar_wait(&sm.bar[BAR_LS0 + x], cnt[x] & 1);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            const uint32_t off = (ks >> 2) * kHalfTile + (ks & 3) * 32;
+            mma_ss(tmem + x * 128, make_smem_desc(do_addr[x] + off, 16, 1024), make_smem_desc(v_addr + off, 16, 1024), idesc_kk, ks > 0);
+          }
+          mma_commit(&sm.bar[BAR_DP0 + x]);
+        }
+        if (!ok) break;
+        mma_commit(&sm.bar[BAR_V_FREE]);
+        if (n + 1 < T) {
+          ok = mbar_wait(&sm.bar[BAR_K_FULL0 + (st ^ 1)], ((n + 1) >> 1) & 1);
+          if (!ok) break;
+        }
+        // dQ_x += dS_x K, then the next S_x into the same columns (in-order execution keeps dS intact)
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if ((e >> (12 + 2 * x)) & 3u) {
+            ok = mbar_wait(&sm.bar[BAR_DS0 + x], cnt[x] & 1);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < BN / 16; ++ks)
+              mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, make_smem_desc(k_addr[st] + ks * 2048, kHalfTile, 1024),
+                     idesc_kn, (cnt[x] > 0) || (ks > 0));
+            mma_commit(&sm.bar[BAR_DQ0 + x]);
+            ++cnt[x];
+          }
+          if ((e_next >> (12 + 2 * x)) & 3u) { tc_fence_after(); issue_s(x, st ^ 1); }
+        }
+        if (!ok) break;
+        mma_commit(&sm.bar[BAR_K_FREE0 + st]);
+      }
+      if (!ok) report_device_error(p.status, 420);
+    }
+  } else {
+    // ------------------------------------------------------------------ element-wise warpgroups
+    setmaxnreg_inc_216();
+    const int x = wg;
+    const int qi = pair * 2 + x;
+    const int row = threadIdx.x & 127;  // TMEM lane == query row of the tile
+    const int q = qi * BM + row;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tmem_sd = tmem + x * 128 + lane_base, tmem_dq = tmem + 256 + x * 128 + lane_base;
+    const MaskView mv = make_mask_view(p.spec, b, h);
+    float lse2 = INFINITY, delta = 0.f;  // +inf: rows outside the tensor or without any key get P = 0
+    if (qi < NQ && q < a.N) {
+      const int64_t off = ((int64_t)b * a.Hq + h) * a.N + q;
+      const float lv = a.lse[off];
+      lse2 = (lv == -INFINITY) ? INFINITY : lv * kLog2e;
+      delta = a.delta[off];
+    }
+    bool ok = true;
+    int cnt = 0;
+
+    for (int n = 0; n < T; ++n) {
+      const uint32_t e = sm.merged[n];
+      const uint32_t cls = (e >> (12 + 2 * x)) & 3u;
+      if (cls == 0) continue;
+      const int k0 = (int)(e & 0x3ffu) * BN;
+      ok = mbar_wait(&sm.bar[BAR_S0 + x], cnt & 1);
+      if (!ok) break;
+      tc_fence_after();
+      float pr[BN];
+      {
+        uint32_t r0[32], r1[32], r2[32], r3[32];
+        tmem_ld32(tmem_sd + 0, r0);
+        tmem_ld32(tmem_sd + 32, r1);
+        tmem_ld32(tmem_sd + 64, r2);
+        tmem_ld32(tmem_sd + 96, r3);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&sm.bar[BAR_LS0 + x]);  // dO V^T may overwrite the columns now
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          pr[j] = ex2(fmaf(__uint_as_float(r0[j]), p.scale_log2, -lse2));
+          pr[32 + j] = ex2(fmaf(__uint_as_float(r1[j]), p.scale_log2, -lse2));
+          pr[64 + j] = ex2(fmaf(__uint_as_float(r2[j]), p.scale_log2, -lse2));
+          pr[96 + j] = ex2(fmaf(__uint_as_float(r3[j]), p.scale_log2, -lse2));
+        }
+      }
+      if (cls == 1) {
+        uint32_t bits[4];
+        if (p.interval_mask) {
+          int jlo, jhi;
+          row_interval(mv, q, k0, jlo, jhi);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int lo = max(jlo - c * 32, 0), hi = min(jhi - c * 32, 31);
+            bits[c] = (lo <= hi) ? ((0xffffffffu >> (31 - hi)) & (0xffffffffu << lo)) : 0u;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) w |= (mask_allowed(mv, q, k0 + c * 32 + j) ? 1u : 0u) << j;
+            bits[c] = w;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < BN; ++j) pr[j] = (bits[j >> 5] >> (j & 31)) & 1u ? pr[j] : 0.f;
+      }
+      // dS = P * (dP - delta), bf16, back into the first 64 columns
+      ok = mbar_wait(&sm.bar[BAR_DP0 + x], cnt & 1);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_sd + c * 32, r);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float d0 = pr[c * 32 + 2 * j] * (__uint_as_float(r[2 * j]) - delta);
+          const float d1 = pr[c * 32 + 2 * j + 1] * (__uint_as_float(r[2 * j + 1]) - delta);
+          pk[j] = pack_bf16(d0, d1);
+        }
+        tmem_st16(tmem_sd + c * 16, pk);  // columns [16c, 16c+16) lie inside chunks already read
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&sm.bar[BAR_DS0 + x]);
+      ++cnt;
+    }
+
+    // ---- epilogue: dQ * scale
+    if (ok && cnt > 0) ok = mbar_wait(&sm.bar[BAR_DQ0 + x], (cnt - 1) & 1);
+    if (!ok) {
+      report_device_error(p.status, 430 + warp);
+    } else if (qi < NQ) {
+      tc_fence_after();
+      const bool store = q < a.N;
+      const int qs = store ? q : 0;
+      __nv_bfloat16* dq = static_cast<__nv_bfloat16*>(a.dq.ptr) + (int64_t)b * a.dq.stride_b + (int64_t)qs * a.dq.stride_l + (int64_t)h * a.dq.stride_h;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        if (cnt > 0) {
+          tmem_ld32(tmem_dq + c * 32, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (store) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 v4;
+            v4.x = pack_bf16(__uint_as_float(r[j]) * a.scale, __uint_as_float(r[j + 1]) * a.scale);
+            v4.y = pack_bf16(__uint_as_float(r[j + 2]) * a.scale, __uint_as_float(r[j + 3]) * a.scale);
+            v4.z = pack_bf16(__uint_as_float(r[j + 4]) * a.scale, __uint_as_float(r[j + 5]) * a.scale);
+            v4.w = pack_bf16(__uint_as_float(r[j + 6]) * a.scale, __uint_as_float(r[j + 7]) * a.scale);
+            *reinterpret_cast<uint4*>(dq + c * 32 + j) = v4;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace
+
+int sm100_bwd_dq(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, cudaStream_t st) {
+  BMA_REQUIRE(lists.NKV <= kMaxKvTiles, BMA_ERR_LIMIT);
+  CUtensorMap mq, mk, mv, mdo;
+  int rc;
+  if ((rc = make_tile_map_bf16(&mq, a.q.ptr, a.B, a.N, a.Hq, a.d, a.q.stride_b, a.q.stride_l, a.q.stride_h, BM))) return rc;
+  if ((rc = make_tile_map_bf16(&mk, a.k.ptr, a.B, a.L, a.Hkv, a.d, a.k.stride_b, a.k.stride_l, a.k.stride_h, BN))) return rc;
+  if ((rc = make_tile_map_bf16(&mv, a.v.ptr, a.B, a.L, a.Hkv, a.d, a.v.stride_b, a.v.stride_l, a.v.stride_h, BN))) return rc;
+  if ((rc = make_tile_map_bf16(&mdo, a.d_o.ptr, a.B, a.N, a.Hq, a.d, a.d_o.stride_b, a.d_o.stride_l, a.d_o.stride_h, BM))) return rc;
+  DqParams p;
+  p.a = a; p.spec = spec; p.l = lists;
+  p.scale_log2 = a.scale * kLog2e;
+  p.interval_mask = (spec.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP)) ? 0 : 1;
+  p.status = device_status_ptr();
+  BMA_REQUIRE(p.status != nullptr, BMA_ERR_CUDA);
+  const size_t smem = sizeof(DqSmem);
+  BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(ceil_div(ceil_div(a.N, BM), 2), a.Hq, a.B);
+  bwd_dq_kernel<<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, p);
+  count_launches(1);
+  BMA_CUDA_TRY(cudaGetLastError());
+  return BMA_OK;
+}
+
+}  // namespace bma
