@@ -317,6 +317,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             col_interval(mv, k, q0, jlo, jhi);
             const int lo = max(jlo - cg * 32, 0), hi = min(jhi - cg * 32, 31);
             bits[c] = (lo <= hi) ? ((0xffffffffu >> (31 - hi)) & (0xffffffffu << lo)) : 0u;
+            if (bits[c] && (mv.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP))) bits[c] &= table_bits_col32(mv, k, q0 + cg * 32);
           } else {
             uint32_t w = 0;
 #pragma unroll
@@ -488,7 +489,7 @@ int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   BMA_REQUIRE(a.d_o.dtype == BMA_DTYPE_BF16, BMA_ERR_UNSUPPORTED);  // bma_attn_bwd_preprocess provides the bf16 copy
   BMA_REQUIRE(aligned16(a.d_o) && aligned16(a.dq) && aligned16(a.dk) && aligned16(a.dv), BMA_ERR_UNSUPPORTED);
   // the per-row form of the block window needs the window to be constant over a 128-query tile
-  int interval = (spec.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP)) ? 0 : 1;
+  int interval = 1;
   if ((spec.flags & BMA_MASK_BLOCK_WINDOW) && !(spec.win_block % BT == 0 && spec.q_offset % BT == 0)) interval = 0;
 
   CUtensorMap mq, mk, mv, mdo;

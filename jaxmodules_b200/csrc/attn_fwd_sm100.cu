@@ -296,7 +296,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       }
       if (cls == 1) {  // partial tile: masked scores become -inf (their exponential is exactly 0)
         uint32_t bits[4];
-        if (p.interval_mask) {
+        {
           int jlo, jhi;
           row_interval(mv, q, k0, jlo, jhi);
 #pragma unroll
@@ -304,13 +304,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             const int lo = max(jlo - c * 32, 0), hi = min(jhi - c * 32, 31);
             bits[c] = (lo <= hi) ? ((0xffffffffu >> (31 - hi)) & (0xffffffffu << lo)) : 0u;
           }
-        } else {
+          if (mv.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP)) {  // segment ids / bit table: 32 keys per word
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t w = 0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) w |= (mask_allowed(mv, q, k0 + c * 32 + j) ? 1u : 0u) << j;
-            bits[c] = w;
+            for (int c = 0; c < 4; ++c)
+              if (bits[c]) bits[c] &= table_bits_row32(mv, q, k0 + c * 32);
           }
         }
 #pragma unroll

@@ -97,6 +97,64 @@ __device__ __forceinline__ bool mask_allowed(const MaskView& m, int q, int k) {
   return ok;
 }
 
+// Bit j of the result: ids[j] == ref for j in [0, n) (n <= 32), 0 for j >= n.  `ids` is a run of
+// segment ids in global memory; the common aligned full run is read with four-wide loads.
+__device__ __forceinline__ uint32_t seg_equal_bits32(const int32_t* ids, int n, int ref) {
+  uint32_t w = 0;
+  if (n >= 32 && (reinterpret_cast<uintptr_t>(ids) & 15) == 0) {
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+      const int4 v = __ldg(reinterpret_cast<const int4*>(ids) + j4);
+      w |= (uint32_t)(v.x == ref) << (j4 * 4);
+      w |= (uint32_t)(v.y == ref) << (j4 * 4 + 1);
+      w |= (uint32_t)(v.z == ref) << (j4 * 4 + 2);
+      w |= (uint32_t)(v.w == ref) << (j4 * 4 + 3);
+    }
+  } else {
+    for (int j = 0; j < 32; ++j)
+      if (j < n && __ldg(ids + j) == ref) w |= 1u << j;
+  }
+  return w;
+}
+
+// Bits of the segment and bit-table terms of query row q (local) for the 32 keys starting at local
+// key k_start: bit j set = key k_start + j passes both terms.  The interval terms (valid box,
+// causal, band, block window) are NOT included; callers AND this with their interval bits.
+__device__ __forceinline__ uint32_t table_bits_row32(const MaskView& m, int q, int k_start) {
+  uint32_t w = 0xffffffffu;
+  if (q >= m.q_valid) return 0u;
+  const int gq = q + m.q_offset, gk = k_start + m.k_offset;
+  const int n = min(32, m.k_valid - k_start);
+  if (n <= 0) return 0u;
+  if (m.flags & BMA_MASK_SEGMENT) w &= seg_equal_bits32(m.seg_k_row + gk, n, __ldg(m.seg_q_row + gq));
+  if (m.flags & BMA_MASK_BITMAP) {
+    const uint32_t* rowp = m.bitmap_bh + (int64_t)gq * m.bitmap_words;
+    const int word = gk >> 5, sh = gk & 31;
+    uint32_t v = __ldg(rowp + word) >> sh;
+    if (sh && word + 1 < m.bitmap_words) v |= __ldg(rowp + word + 1) << (32 - sh);
+    w &= v;
+  }
+  return w;
+}
+
+// The same for key row k (local) and the 32 queries starting at local query q_start (bit j =
+// query q_start + j).  The bit table is stored by query row, so that term is gathered bit by bit.
+__device__ __forceinline__ uint32_t table_bits_col32(const MaskView& m, int k, int q_start) {
+  uint32_t w = 0xffffffffu;
+  if (k >= m.k_valid) return 0u;
+  const int gk = k + m.k_offset, gq = q_start + m.q_offset;
+  const int n = min(32, m.q_valid - q_start);
+  if (n <= 0) return 0u;
+  if (m.flags & BMA_MASK_SEGMENT) w &= seg_equal_bits32(m.seg_q_row + gq, n, __ldg(m.seg_k_row + gk));
+  if (m.flags & BMA_MASK_BITMAP) {
+    uint32_t v = 0;
+    for (int j = 0; j < n; ++j)
+      v |= ((__ldg(m.bitmap_bh + (int64_t)(gq + j) * m.bitmap_words + (gk >> 5)) >> (gk & 31)) & 1u) << j;
+    w &= v;
+  }
+  return w;
+}
+
 // ---- numeric helpers -------------------------------------------------------------------
 __device__ __forceinline__ float to_float(float x) { return x; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
