@@ -192,8 +192,8 @@ int bma_attn_fwd(const bma_attn_args* args, const bma_mask_spec* spec,
  * jax.vjp derives at jaxmodules/attention.py:320-321. */
 int bma_attn_bwd_preprocess(const bma_attn_args* args, void* d_o_bf16, bma_stream_t stream);
 
-/* Scratch bytes bma_attn_bwd needs (float32 dQ accumulator when the tensor-core backend
- * accumulates dQ with atomics; 0 for the SIMT backend). */
+/* Scratch bytes bma_attn_bwd needs.  Currently 0 for every backend (all gradients are
+ * accumulated on chip); the query stays so that a backend with scratch can be added. */
 size_t bma_attn_bwd_workspace_bytes(const bma_attn_args* args);
 
 /* Backward: dQ, dK, dV from (Q, K, V, O, dO, lse, delta).  Replaces
