@@ -54,11 +54,11 @@ def _tensor(t: Optional[torch.Tensor]) -> nat.Tensor:
     return out
 
 
-def _make_args(Q, K, V, backend=nat.BMA_BACKEND_AUTO) -> nat.AttnArgs:
+def _make_args(Q, K, V, backend=nat.BMA_BACKEND_AUTO, scale=None) -> nat.AttnArgs:
     a = nat.AttnArgs()
     a.B, a.N, a.Hq, a.d = Q.shape
     a.L, a.Hkv = K.shape[1], K.shape[2]
-    a.scale = 1.0 / math.sqrt(K.shape[-1])
+    a.scale = 1.0 / math.sqrt(K.shape[-1]) if scale is None else float(scale)
     a.backend = backend
     a.q, a.k, a.v = _tensor(Q), _tensor(K), _tensor(V)
     return a
@@ -109,25 +109,30 @@ def set_profile_sink(sink):
 
 
 def attention_forward(Q, K, V, terms: _masks.MaskTerms, *, out_dtype=torch.float32, backend=nat.BMA_BACKEND_AUTO,
-                      need_q_side: bool = False):
+                      need_q_side: bool = False, scale=None, lists_fn=None):
     """One forward launch sequence: mask compile at the kernel's tile size, then attention.
-    Returns (O, lse, ctx) where ctx carries what the backward needs."""
+    Returns (O, lse, ctx) where ctx carries what the backward needs.
+
+    ``scale`` replaces 1/sqrt(d).  ``lists_fn(q_tile, kv_tile, q_side)`` supplies ready-made
+    block lists (struct, tensors) instead of compiling them from the mask terms; it returns
+    None when it has none for that tile size."""
     lib = nat.lib()
     dev = Q.device
     B, N, Hq, d = Q.shape
     L = K.shape[1]
     with torch.cuda.device(dev):
-        a = _make_args(Q, K, V, backend)
+        a = _make_args(Q, K, V, backend, scale)
         be, tq, tk = plan(Q, K, V, backend)
         dmask = _masks.to_device_mask(terms, N, L, dev)
         with _Span(_profile_sink, "mask_compile", dev):
-            lists, lt = compile_block_lists(dmask, B, Hq, N, L, tq, tk, dev, q_side=False)
+            ready = lists_fn(tq, tk, False) if lists_fn is not None else None
+            lists, lt = ready if ready is not None else compile_block_lists(dmask, B, Hq, N, L, tq, tk, dev, q_side=False)
         O = torch.empty((B, N, Hq, d), dtype=out_dtype, device=dev)
         lse = torch.empty((B, Hq, N), dtype=torch.float32, device=dev)
         a.o, a.lse = _tensor(O), lse.data_ptr()
         with _Span(_profile_sink, "fwd", dev):
             nat.check(lib.bma_attn_fwd(C.byref(a), C.byref(dmask.spec), C.byref(lists), _stream(dev)), "bma_attn_fwd")
-    ctx = dict(dmask=dmask, lists=lists, list_tensors=lt, backend=be)
+    ctx = dict(dmask=dmask, lists=lists, list_tensors=lt, backend=be, scale=scale, lists_fn=lists_fn)
     return O, lse, ctx
 
 
@@ -138,10 +143,12 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
     B, N, Hq, d = Q.shape
     L = K.shape[1]
     with torch.cuda.device(dev):
-        a = _make_args(Q, K, V, backend)
+        a = _make_args(Q, K, V, backend, ctx.get("scale"))
         be, tq, tk = plan(Q, K, V, backend, backward=True)
         with _Span(_profile_sink, "mask_compile_bwd", dev):
-            lists, lt = compile_block_lists(ctx["dmask"], B, Hq, N, L, tq, tk, dev, q_side=True)
+            lists_fn = ctx.get("lists_fn")
+            ready = lists_fn(tq, tk, True) if lists_fn is not None else None
+            lists, lt = ready if ready is not None else compile_block_lists(ctx["dmask"], B, Hq, N, L, tq, tk, dev, q_side=True)
         if dO.stride(-1) != 1:
             dO = dO.contiguous()
         delta = torch.empty((B, Hq, N), dtype=torch.float32, device=dev)
@@ -167,9 +174,10 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
 
 class _MaskedAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, Q, K, V, terms, out_dtype, backend):
+    def forward(ctx, Q, K, V, terms, out_dtype, backend, scale=None, lists_fn=None):
         need_grad = any(ctx.needs_input_grad[:3])
-        O, lse, fctx = attention_forward(Q, K, V, terms, out_dtype=out_dtype, backend=backend, need_q_side=need_grad)
+        O, lse, fctx = attention_forward(Q, K, V, terms, out_dtype=out_dtype, backend=backend, need_q_side=need_grad,
+                                         scale=scale, lists_fn=lists_fn)
         ctx.save_for_backward(Q, K, V, O, lse)
         ctx.fctx, ctx.backend = fctx, backend
         ctx.mark_non_differentiable(lse)
@@ -179,7 +187,7 @@ class _MaskedAttention(torch.autograd.Function):
     def backward(ctx, dO, _dlse):
         Q, K, V, O, lse = ctx.saved_tensors
         dQ, dK, dV = attention_backward(Q, K, V, O, lse, dO, ctx.fctx, ctx.backend)
-        return dQ, dK, dV, None, None, None
+        return dQ, dK, dV, None, None, None, None, None
 
 
 def masked_attention_via_map(
