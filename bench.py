@@ -228,6 +228,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--api", default="via_map", choices=["via_map", "flex"],
+                    help="public entry point under test: masked_attention_via_map on [B,L,H,d] (default) or "
+                         "flex_attention on [B,H,L,d] with a BlockMask built once outside the timed region")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -257,14 +260,22 @@ def main():
     dt = torch_dtype(w["dtype"])
     scale = 1 / math.sqrt(d) if w["qkv_scale"] == "rsqrt_d" else 1.0
     # every rank owns its own batch (seeds offset by rank): batch x head shards, no collective
-    hQ, hK, hV = (synth((B, L, H, d), 10 * rank + s, dt, scale, pin=True) for s in (0, 1, 2))
-    hdO = synth((B, L, H, d), 10 * rank + 3, torch.float32, pin=True)
+    flex = args.api == "flex"
+    shape = (B, H, L, d) if flex else (B, L, H, d)
+    hQ, hK, hV = (synth(shape, 10 * rank + s, dt, scale, pin=True) for s in (0, 1, 2))
+    hdO = synth(shape, 10 * rank + 3, torch.float32, pin=True)
     Q, K, V = (x.to(dev).requires_grad_(True) for x in (hQ, hK, hV))
     dO = hdO.to(dev)
     kw = mask_kwargs(w, M)
+    if flex:
+        mask_mod = M.causal_mask() if kw.get("is_causal") else kw["mask_fn"]
+        block_mask = jm.create_block_mask(mask_mod, B if w["mask"] == "documents" else 1, 1, L, L, 128, device=dev)
+        attend = lambda q, k, v: jm.flex_attention(q, k, v, block_mask=block_mask)
+    else:
+        attend = lambda q, k, v: jm.masked_attention_via_map(q, k, v, **kw)
 
     def step():
-        O = jm.masked_attention_via_map(Q, K, V, **kw)
+        O = attend(Q, K, V)
         Q.grad = K.grad = V.grad = None
         O.backward(dO)
         return O
@@ -275,7 +286,7 @@ def main():
         torch.cuda.synchronize(dev)
 
     # FLOP count from the block lists the kernels actually walk
-    be, tq, tk = A.plan(Q, K, V)
+    be, tq, tk = A.plan(*((x.transpose(1, 2) for x in (Q, K, V)) if flex else (Q, K, V)))
     terms = M.MaskTerms(causal=True) if kw.get("is_causal") else M.terms_from_mask_fn(kw["mask_fn"], B, H, L, L)
     if kw.get("window_size") is not None:
         bs = w["bs"]
@@ -312,13 +323,13 @@ def main():
     # end to end through the public API with host buffers (H2D of inputs, D2H of results inside the timed region)
     e2e = None
     if not args.no_e2e:
-        outs = [torch.empty((B, L, H, d), dtype=torch.float32).pin_memory()] + \
-               [torch.empty((B, L, H, d), dtype=dt).pin_memory() for _ in range(3)]
+        outs = [torch.empty(shape, dtype=torch.float32).pin_memory()] + \
+               [torch.empty(shape, dtype=dt).pin_memory() for _ in range(3)]
 
         def e2e_step():
             q, k, v = (x.to(dev, non_blocking=True).requires_grad_(True) for x in (hQ, hK, hV))
             g = hdO.to(dev, non_blocking=True)
-            o = jm.masked_attention_via_map(q, k, v, **kw)
+            o = attend(q, k, v)
             o.backward(g)
             for dst, src in zip(outs, (o.detach(), q.grad, k.grad, v.grad)):
                 dst.copy_(src, non_blocking=True)
@@ -357,7 +368,8 @@ def main():
             "metric": METRIC, "value": total_flops / (ms_step * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-            "config": {"workload": w["desc"], "per_gpu_batch": B, "global_batch": B * world,
+            "config": {"workload": w["desc"], "api": "flex_attention [B,H,L,d] + BlockMask(128)" if flex else "masked_attention_via_map [B,L,H,d]",
+                       "per_gpu_batch": B, "global_batch": B * world,
                        "parallelism": f"batch x head shards, {world} GPU(s), no collective",
                        "backend": {1: "simt", 2: "tcgen05"}.get(be, str(be)), "tile": tq, "nonempty_blocks_per_gpu": blocks,
                        "l2": "inputs (Q,K,V,dO > 1 GB) exceed the 126 MB L2; no flush needed",
