@@ -56,8 +56,8 @@ struct DqParams {
   int* status;
 };
 
-__device__ __forceinline__ void setmaxnreg_inc_216() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
-__device__ __forceinline__ void setmaxnreg_dec_72() { asm volatile("setmaxnreg.dec.sync.aligned.u32 72;"); }
+__device__ __forceinline__ void setmaxnreg_inc_200() { asm volatile("setmaxnreg.inc.sync.aligned.u32 200;"); }
+__device__ __forceinline__ void setmaxnreg_dec_96() { asm volatile("setmaxnreg.dec.sync.aligned.u32 96;"); }
 
 // Allowed key interval [jlo, jhi] (tile-local, inclusive) of query row q for interval-only masks.
 __device__ __forceinline__ void row_interval(const MaskView& m, int q, int k0, int& jlo, int& jhi) {
@@ -142,7 +142,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   const int T = sm.n_merged;
 
   if (wg == 2) {
-    setmaxnreg_dec_72();
+    setmaxnreg_dec_96();
     if (warp == 8 && lane == 0 && T > 0) {
       // ---------------------------------------------------------------- TMA producer
       prefetch_tensormap(&map_q);
@@ -247,7 +247,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     }
   } else {
     // ------------------------------------------------------------------ element-wise warpgroups
-    setmaxnreg_inc_216();
+    setmaxnreg_inc_200();
     const int x = wg;
     const int qi = pair * 2 + x;
     const int row = threadIdx.x & 127;  // TMEM lane == query row of the tile

@@ -37,9 +37,6 @@ constexpr int kMaxKvTiles = 4096;               // merged kv list kept in shared
 #ifndef BMA_FWD_POLY
 #define BMA_FWD_POLY 0
 #endif
-#ifndef BMA_FWD_SPLIT
-#define BMA_FWD_SPLIT 1
-#endif
 
 enum {
   BAR_Q = 0,
@@ -69,8 +66,8 @@ struct FwdParams {
   int* status;
 };
 
-__device__ __forceinline__ void setmaxnreg_inc_216() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
-__device__ __forceinline__ void setmaxnreg_dec_72() { asm volatile("setmaxnreg.dec.sync.aligned.u32 72;"); }
+__device__ __forceinline__ void setmaxnreg_inc_208() { asm volatile("setmaxnreg.inc.sync.aligned.u32 208;"); }
+__device__ __forceinline__ void setmaxnreg_dec_80() { asm volatile("setmaxnreg.dec.sync.aligned.u32 80;"); }
 // 2^x on the FMA pipe (Cody-Waite split + degree-3 polynomial, relative error 1e-4, well below
 // the bf16 rounding of P): a share of the exponentials is taken off the MUFU unit, which is the
 // narrowest pipe of the softmax.
@@ -166,7 +163,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const int T = sm.n_merged;
 
   if (wg == 2) {
-    setmaxnreg_dec_72();
+    setmaxnreg_dec_80();
     if (warp == 8 && lane == 0 && T > 0) {
       // ---------------------------------------------------------------- TMA producer
       prefetch_tensormap(&map_q);
@@ -197,17 +194,22 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
       constexpr uint32_t idesc_o = make_idesc_bf16(BM, HD, 0, 1);
-      const uint32_t q_addr[2] = {smem_u32(sm.q[0]), smem_u32(sm.q[1])};
-      const uint32_t k_addr[2] = {smem_u32(sm.k[0]), smem_u32(sm.k[1])};
-      const uint32_t v_addr[2] = {smem_u32(sm.v[0]), smem_u32(sm.v[1])};
-      int cnt[2] = {0, 0};  // tiles already multiplied into O_x (also the phase counter of BAR_P)
+      // Descriptors are built once; per MMA only the 16-byte-unit start address in the low bits moves
+      // (tiles are 1024-byte aligned and below 256 KB, so the sum never leaves the address field).
+      // Everything is kept in scalars: an array indexed by the stage would live in local memory and
+      // every MMA would wait on a load — the issuing thread must stay ahead of the tensor core.
+      const uint64_t dq0 = make_smem_desc(smem_u32(sm.q[0]), 16, 1024), dq1 = make_smem_desc(smem_u32(sm.q[1]), 16, 1024);
+      const uint64_t dk0 = make_smem_desc(smem_u32(sm.k[0]), 16, 1024);
+      const uint64_t dv0 = make_smem_desc(smem_u32(sm.v[0]), kHalfTile, 1024);
+      constexpr uint32_t kStageUnits = kTileBytes >> 4;
+      int cnt0 = 0, cnt1 = 0;  // tiles already multiplied into O_x (also the phase counter of BAR_PH / BAR_P)
       bool ok = mbar_wait(&sm.bar[BAR_Q], 0);
 
       auto issue_s = [&](int x, int st) {
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * kHalfTile + (ks & 3) * 32;  // 64-column box, then 32 B per k-step
-          mma_ss(tmem + x * 128, make_smem_desc(q_addr[x] + off, 16, 1024), make_smem_desc(k_addr[st] + off, 16, 1024), idesc_s, ks > 0);
+          const uint32_t off = ((ks >> 2) * kHalfTile + (ks & 3) * 32) >> 4;  // 64-column box, then 32 B per k-step
+          mma_ss(tmem + x * 128, (x == 0 ? dq0 : dq1) + off, dk0 + (uint32_t)(st * kStageUnits + off), idesc_s, ks > 0);
         }
         mma_commit(&sm.bar[BAR_S0 + x]);
       };
@@ -229,23 +231,24 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if ((e >> (16 + 2 * x)) & 3u) {
+            int& cnt = x == 0 ? cnt0 : cnt1;
             // P arrives in two halves (keys 0..63, then 64..127) so that the first k-steps run under
             // the second half of the exponentials
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
-              ok = mbar_wait(&sm.bar[(hf == 0 ? BAR_PH0 : BAR_P0) + x], cnt[x] & 1);
+              ok = mbar_wait(&sm.bar[(hf == 0 ? BAR_PH0 : BAR_P0) + x], cnt & 1);
               if (!ok) break;
               tc_fence_after();
 #pragma unroll
               for (int ks = hf * 4; ks < hf * 4 + 4; ++ks) {
                 // B = V[kv rows][d] read MN-major: 16 kv rows per k-step = 2048 B; the two 64-column boxes are kHalfTile apart
-                mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, make_smem_desc(v_addr[st] + ks * 2048, kHalfTile, 1024),
-                       idesc_o, (cnt[x] > 0) || (ks > 0));
+                mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, dv0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)),
+                       idesc_o, (cnt > 0) || (ks > 0));
               }
             }
             if (!ok) break;
             mma_commit(&sm.bar[BAR_O0 + x]);
-            ++cnt[x];
+            ++cnt;
           }
           if ((e_next >> (16 + 2 * x)) & 3u) issue_s(x, st ^ 1);
         }
@@ -257,7 +260,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     }
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
-    setmaxnreg_inc_216();
+    setmaxnreg_inc_208();
     const int x = wg;                         // which query tile of the pair
     const int qi = pair * 2 + x;
     const int row = threadIdx.x & 127;        // TMEM lane == query row of the tile
@@ -365,18 +368,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           pk[j + 1] = pack_bf16(e2, e3);
         }
         tmem_st32(tmem_s + c * 32, pk);
-#if BMA_FWD_SPLIT
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&sm.bar[(c == 0 ? BAR_PH0 : BAR_P0) + x]);
-#endif
       }
-#if !BMA_FWD_SPLIT
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(&sm.bar[BAR_PH0 + x]);
-      mbar_arrive(&sm.bar[BAR_P0 + x]);
-#endif
       l = l * alpha + ((rs0 + rs1) + (rs2 + rs3));
       ++cnt;
     }
