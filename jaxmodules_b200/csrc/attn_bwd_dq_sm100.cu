@@ -17,6 +17,10 @@
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
+#ifndef BMA_DQ_POLY
+#define BMA_DQ_POLY 0  // measured: 3.84 ms against 3.78 ms for the whole backward on the config-2 shape, so off
+#endif
+
 namespace bma {
 namespace {
 
@@ -288,7 +292,11 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           pr[j] = ex2(fmaf(__uint_as_float(r0[j]), p.scale_log2, -lse2));
           pr[32 + j] = ex2(fmaf(__uint_as_float(r1[j]), p.scale_log2, -lse2));
           pr[64 + j] = ex2(fmaf(__uint_as_float(r2[j]), p.scale_log2, -lse2));
+#if BMA_DQ_POLY
+          pr[96 + j] = exp2_fma(fmaf(__uint_as_float(r3[j]), p.scale_log2, -lse2));  // a quarter of the exponentials on the FMA pipe
+#else
           pr[96 + j] = ex2(fmaf(__uint_as_float(r3[j]), p.scale_log2, -lse2));
+#endif
         }
       }
       if (cls == 1) {

@@ -23,6 +23,10 @@
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
+#ifndef BMA_DKDV_POLY
+#define BMA_DKDV_POLY 0  // measured: 3.87 ms against 3.78 ms for the whole backward on the config-2 shape, so off
+#endif
+
 namespace bma {
 
 int sm100_bwd_dq(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, cudaStream_t st);
@@ -344,7 +348,13 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int e = 0; e < 4; ++e) {
           const int j = j4 * 4 + e;
           pr[j] = ex2(fmaf(__uint_as_float(s0[j]), p.scale_log2, -lav[e]));
+#if BMA_DKDV_POLY
+          // a quarter of the exponentials on the FMA pipe (e is a compile-time index after unrolling)
+          pr[32 + j] = (e & 1) ? exp2_fma(fmaf(__uint_as_float(s1[j]), p.scale_log2, -lbv[e]))
+                               : ex2(fmaf(__uint_as_float(s1[j]), p.scale_log2, -lbv[e]));
+#else
           pr[32 + j] = ex2(fmaf(__uint_as_float(s1[j]), p.scale_log2, -lbv[e]));
+#endif
         }
       }
       if (partial_) {

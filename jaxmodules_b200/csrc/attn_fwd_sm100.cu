@@ -35,7 +35,7 @@ constexpr uint32_t kTileBytes = 2 * kHalfTile;  // a [128 x 128] operand tile
 constexpr float kRescaleThreshold = 8.0f;       // log2 units: rescale O only when the max grew by > 2^8
 constexpr int kMaxKvTiles = 4096;               // merged kv list kept in shared memory
 #ifndef BMA_FWD_POLY
-#define BMA_FWD_POLY 0
+#define BMA_FWD_POLY 1
 #endif
 
 enum {
@@ -68,16 +68,6 @@ struct FwdParams {
 
 __device__ __forceinline__ void setmaxnreg_inc_208() { asm volatile("setmaxnreg.inc.sync.aligned.u32 208;"); }
 __device__ __forceinline__ void setmaxnreg_dec_80() { asm volatile("setmaxnreg.dec.sync.aligned.u32 80;"); }
-// 2^x on the FMA pipe (Cody-Waite split + degree-3 polynomial, relative error 1e-4, well below
-// the bf16 rounding of P): a share of the exponentials is taken off the MUFU unit, which is the
-// narrowest pipe of the softmax.
-__device__ __forceinline__ float exp2_fma(float x) {
-  x = fmaxf(x, -126.0f);
-  const float xr = x + 12582912.0f;  // 1.5 * 2^23: round(x) lands in the low mantissa bits
-  const float f = x - (xr - 12582912.0f);  // in [-0.5, 0.5]
-  const float pf = fmaf(fmaf(fmaf(0.05500893f, f, 0.24221096f), f, 0.69328293f), f, 1.0f);
-  return __int_as_float(__float_as_int(pf) + (__float_as_int(xr) << 23));
-}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -111,7 +101,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest causal tiles first
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (a.Hq / a.Hkv);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;  // provably warp-uniform
   const int wg = warp >> 2;
   const int NQ = p.l.NQ, NKV = p.l.NKV;
 
@@ -190,8 +180,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         load_tile(&map_v, sm.v[st], &sm.bar[BAR_V_FULL0 + st], hk, row0);
       }
       if (!ok) report_device_error(p.status, 110);
-    } else if (warp == 9 && lane == 0 && T > 0) {
-      // ---------------------------------------------------------------- MMA issuer
+    } else if (warp == 9 && T > 0) {
+      // ---------------------------------------------------------------- MMA issuer (whole warp, one elected lane issues)
+      const bool leader = elect_one();
       constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
       constexpr uint32_t idesc_o = make_idesc_bf16(BM, HD, 0, 1);
       // Descriptors are built once; per MMA only the 16-byte-unit start address in the low bits moves
@@ -209,9 +200,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * kHalfTile + (ks & 3) * 32) >> 4;  // 64-column box, then 32 B per k-step
-          mma_ss(tmem + x * 128, (x == 0 ? dq0 : dq1) + off, dk0 + (uint32_t)(st * kStageUnits + off), idesc_s, ks > 0);
+          if (leader) mma_ss(tmem + x * 128, (x == 0 ? dq0 : dq1) + off, dk0 + (uint32_t)(st * kStageUnits + off), idesc_s, ks > 0);
         }
-        mma_commit(&sm.bar[BAR_S0 + x]);
+        if (leader) mma_commit(&sm.bar[BAR_S0 + x]);
       };
       if (ok) ok = mbar_wait(&sm.bar[BAR_K_FULL0], 0);
       if (ok) {
@@ -219,7 +210,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         const uint32_t e = sm.merged[0];
         if ((e >> 16) & 3u) issue_s(0, 0);
         if ((e >> 18) & 3u) issue_s(1, 0);
-        mma_commit(&sm.bar[BAR_K_FREE0]);
+        if (leader) mma_commit(&sm.bar[BAR_K_FREE0]);
       }
       for (int n = 0; n < T && ok; ++n) {
         const int st = n & 1;
@@ -242,21 +233,24 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 #pragma unroll
               for (int ks = hf * 4; ks < hf * 4 + 4; ++ks) {
                 // B = V[kv rows][d] read MN-major: 16 kv rows per k-step = 2048 B; the two 64-column boxes are kHalfTile apart
-                mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, dv0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)),
-                       idesc_o, (cnt > 0) || (ks > 0));
+                if (leader)
+                  mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, dv0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)),
+                         idesc_o, (cnt > 0) || (ks > 0));
               }
             }
             if (!ok) break;
-            mma_commit(&sm.bar[BAR_O0 + x]);
+            if (leader) mma_commit(&sm.bar[BAR_O0 + x]);
             ++cnt;
           }
           if ((e_next >> (16 + 2 * x)) & 3u) issue_s(x, st ^ 1);
         }
         if (!ok) break;
-        mma_commit(&sm.bar[BAR_V_FREE0 + st]);
-        if (n + 1 < T) mma_commit(&sm.bar[BAR_K_FREE0 + (st ^ 1)]);
+        if (leader) {
+          mma_commit(&sm.bar[BAR_V_FREE0 + st]);
+          if (n + 1 < T) mma_commit(&sm.bar[BAR_K_FREE0 + (st ^ 1)]);
+        }
       }
-      if (!ok) report_device_error(p.status, 120);
+      if (!ok && leader) report_device_error(p.status, 120);
     }
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
@@ -357,8 +351,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         for (int j = 0; j < 32; j += 2) {
           const float e0 = ex2(fmaf(s[c * 64 + 2 * j], p.scale_log2, -m_sub));
           const float e1 = ex2(fmaf(s[c * 64 + 2 * j + 1], p.scale_log2, -m_sub));
+#if BMA_FWD_POLY >= 2
+          const float e2 = exp2_fma(fmaf(s[c * 64 + 2 * j + 2], p.scale_log2, -m_sub));
+#else
           const float e2 = ex2(fmaf(s[c * 64 + 2 * j + 2], p.scale_log2, -m_sub));
-#if BMA_FWD_POLY
+#endif
+#if BMA_FWD_POLY >= 1
           const float e3 = exp2_fma(fmaf(s[c * 64 + 2 * j + 3], p.scale_log2, -m_sub));
 #else
           const float e3 = ex2(fmaf(s[c * 64 + 2 * j + 3], p.scale_log2, -m_sub));

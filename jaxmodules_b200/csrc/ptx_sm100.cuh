@@ -145,6 +145,15 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// One lane of a converged warp.  The MMA-issuing warp runs its loop with all 32 lanes (warp-uniform
+// control flow and addresses, which the compiler keeps on the uniform datapath) and predicates only
+// the tcgen05 instructions on the elected lane: measured 64 cycles per 128x128x16 MMA under full
+// load from the other warps, against 70 for a loop run by lane 0 alone inside a divergent branch.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 // D[tmem] (+)= A[tmem] * B[smem]; issued by ONE thread.
 __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -162,6 +171,16 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// 2^x on the FMA pipe (Cody-Waite split + degree-3 polynomial, relative error 1e-4, well below
+// the bf16 rounding of P): a share of the exponentials is taken off the MUFU unit, which is the
+// narrowest pipe of the softmax.
+__device__ __forceinline__ float exp2_fma(float x) {
+  x = fmaxf(x, -126.0f);
+  const float xr = x + 12582912.0f;  // 1.5 * 2^23: round(x) lands in the low mantissa bits
+  const float f = x - (xr - 12582912.0f);  // in [-0.5, 0.5]
+  const float pf = fmaf(fmaf(fmaf(0.05500893f, f, 0.24221096f), f, 0.69328293f), f, 1.0f);
+  return __int_as_float(__float_as_int(pf) + (__float_as_int(xr) << 23));
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
