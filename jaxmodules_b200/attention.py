@@ -28,15 +28,57 @@ def default_kernel(q, k):
 
 
 def threshold_kernel(threshold: Optional[float] = None):
-    """jaxmodules/attention.py:18-36.  Not available on the CUDA path yet; passing the result
-    as ``kernel_fn`` raises NotImplementedError."""
+    """jaxmodules/attention.py:18-36: ``exp(q.k - threshold / sqrt(d))`` — note that the dot
+    product is NOT divided by sqrt(d).  The constant factor cancels in the normalised output,
+    so on the CUDA path this is the softmax with scale 1 (the log-sum-exp is shifted by
+    ``-threshold / sqrt(d)``)."""
     def kernel_fn(q, k):
         q, k = torch.as_tensor(q), torch.as_tensor(k)
         dotp = torch.dot(q, k)
         if threshold is not None:
             dotp = dotp - threshold / math.sqrt(q.shape[0])
         return torch.exp(dotp)
+    kernel_fn.log_affine = lambda d: (1.0, 0.0 if threshold is None else -float(threshold) / math.sqrt(d))
     return kernel_fn
+
+
+def kernel_log_affine(kernel_fn: Callable, d: int) -> Tuple[float, float]:
+    """(a, b) with ``kernel_fn(q, k) == exp(a * q.k + b)`` for vectors of length ``d``.
+
+    The CUDA kernels implement exactly this family (``a`` is their logit scale, ``b`` only
+    shifts the log-sum-exp).  ``default_kernel`` and ``threshold_kernel`` carry the pair; any
+    other callable is probed on random vectors (NumPy float64, then torch) and accepted when
+    ``log kernel_fn`` is an affine function of the dot product to 1e-6, e.g. the custom kernel
+    of the reference's tests/test_mapped_attention.py:1122-1142.  Everything else — kernels
+    that are not exponentials of the dot product — raises NotImplementedError."""
+    if kernel_fn is default_kernel:
+        return 1.0 / math.sqrt(d), 0.0
+    if hasattr(kernel_fn, "log_affine"):
+        a, b = kernel_fn.log_affine(d)
+        return float(a), float(b)
+    import numpy as np
+    rng = np.random.default_rng(0)
+    xs, ys = [], []
+    for i in range(12):
+        # different norms and angles, dot products spread over roughly [-4, 4]
+        q = rng.standard_normal(d) * (0.25 + 0.25 * (i % 4)) / math.sqrt(math.sqrt(d))
+        k = rng.standard_normal(d) * (1.5 - 0.25 * (i % 5)) / math.sqrt(math.sqrt(d))
+        if i % 3 == 0:
+            k = k + q * (1.0 + i / 6.0)
+        try:
+            w = kernel_fn(q, k)
+        except Exception:
+            w = kernel_fn(torch.from_numpy(q), torch.from_numpy(k))
+        w = float(w)
+        if not (w > 0.0 and math.isfinite(w)):
+            raise NotImplementedError("kernel_fn must be positive and finite; only exp(a*q.k + b) kernels run on the CUDA path")
+        xs.append(float(q @ k))
+        ys.append(math.log(w))
+    A = np.stack([np.asarray(xs), np.ones(len(xs))], axis=1)
+    (a, b), *_ = np.linalg.lstsq(A, np.asarray(ys), rcond=None)
+    if np.abs(A @ np.array([a, b]) - np.asarray(ys)).max() > 1e-6 * (1.0 + np.abs(ys).max()):
+        raise NotImplementedError("kernel_fn is not of the form exp(a*q.k + b); only such kernels run on the CUDA path")
+    return float(a), float(b)
 
 
 _DTYPES = {torch.float32: nat.BMA_DTYPE_F32, torch.bfloat16: nat.BMA_DTYPE_BF16}
@@ -207,6 +249,8 @@ def masked_attention_via_map(
     """Drop-in for jaxmodules/attention.py:347-455.
 
     K, V: ``[B, L, Hkv, d]`` or ``[L, Hkv, d]``; Q: ``[B, N, Hq, d]`` or ``[N, Hq, d]``.
+    ``kernel_fn``: ``default_kernel``, ``threshold_kernel(t)`` or any callable equal to
+    ``exp(a * q.k + b)`` (see ``kernel_log_affine``); other kernels raise NotImplementedError.
     ``mask_fn(b, h, q, k)`` or ``mask_fn(h, q, k)``; ``is_causal`` excludes ``mask_fn``.
     ``block_size`` / ``window_size`` keep the reference's meaning: the key window is a whole
     number of ``block_size`` blocks, clamped at the sequence ends, applied on top of the mask
@@ -231,8 +275,7 @@ def masked_attention_via_map(
 
     if is_causal and mask_fn is not None:
         raise ValueError("cannot specify both 'is_causal' and 'mask_fn'!")
-    if kernel_fn is not default_kernel:
-        raise NotImplementedError("only default_kernel (exp(q.k/sqrt(d))) is implemented on the CUDA path")
+    scale, shift = kernel_log_affine(kernel_fn, K.shape[-1])
 
     assert K.shape[0] == Q.shape[0] == V.shape[0], "Q, K, and V must have the same batch dimension"
     B, N, Hq, dq = Q.shape
@@ -273,7 +316,10 @@ def masked_attention_via_map(
         terms = terms.merged(_masks.MaskTerms(window=(bs, lb, rb, nkb)))
 
     fix = lambda t: t if t.stride(-1) == 1 else t.contiguous()
-    O, lse = _MaskedAttention.apply(fix(Q), fix(K), fix(V), terms, out_dtype or torch.float32, backend)
+    O, lse = _MaskedAttention.apply(fix(Q), fix(K), fix(V), terms, out_dtype or torch.float32, backend,
+                                    None if kernel_fn is default_kernel else scale)
+    if shift != 0.0 and return_lse:
+        lse = lse + shift
     if added_batch_dim:
         O, lse = O[0], lse[0]
     return (O, lse) if return_lse else O

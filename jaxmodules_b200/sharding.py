@@ -153,3 +153,74 @@ def ring_attention_forward(Q, K, V, *, rank: int, world: int, is_causal: bool = 
         if s + 1 < world:
             k_cur, v_cur = k_nxt, v_nxt
     return O, lse
+
+
+# ---------------------------------------------------------------------------------------------
+# ring sequence partition (backward)
+# ---------------------------------------------------------------------------------------------
+
+def cuda_backward(Q, K, V, O, lse, dO, terms: _masks.MaskTerms):
+    """Gradients of one (query chunk, key chunk) pair on the CUDA kernels.  ``O`` and ``lse`` are
+    the FINAL output and log-sum-exp of the local queries over the whole sequence, so that
+    ``P = exp(s - lse)`` and ``delta = rowsum(dO * O)`` are the global quantities and the three
+    partial gradients simply add up over the key chunks."""
+    from .attention import attention_backward
+    dmask = _masks.to_device_mask(terms, Q.shape[1], K.shape[1], Q.device)
+    return attention_backward(Q, K, V, O, lse, dO, dict(dmask=dmask))
+
+
+def _step_terms(terms: _masks.MaskTerms, q_offset: int, k_offset: int) -> _masks.MaskTerms:
+    return _masks.MaskTerms(causal=terms.causal, band=terms.band, seg_q=terms.seg_q, seg_k=terms.seg_k,
+                            window=terms.window, bitmap=terms.bitmap, q_offset=terms.q_offset + q_offset,
+                            k_offset=terms.k_offset + k_offset)
+
+
+def ring_attention_backward(Q, K, V, O, lse, dO, *, rank: int, world: int, is_causal: bool = False,
+                            terms: Optional[_masks.MaskTerms] = None, group=None,
+                            backward: Callable = cuda_backward, exchange: Optional[Callable] = None):
+    """dQ, dK, dV for a sequence split into ``world`` contiguous chunks (the counterpart of
+    ``ring_attention_forward``; ``O`` / ``lse`` are its results for the local queries).
+
+    K and V travel round the ring as in the forward pass, and the float32 accumulators of dK and
+    dV travel with them: at step s this rank adds the contribution of its queries to the chunk it
+    holds and hands chunk and accumulators to rank+1.  The K/V transfer of the next step is posted
+    before the kernels of this step and runs under them; the accumulators follow once the step's
+    kernels are queued.  After the last step one more hop brings every accumulator back to the
+    rank that owns the chunk.  dQ stays local (float32 accumulation over the steps).
+
+    ``exchange(tensors, dst, src)`` replaces the point-to-point transfer (it returns the received
+    tensors); the default uses ``torch.distributed.batch_isend_irecv`` on ``group``."""
+    import torch.distributed as dist
+    terms = terms or _masks.MaskTerms(causal=is_causal)
+    n_local, l_local = Q.shape[1], K.shape[1]
+    dst, src = (rank + 1) % world, (rank - 1) % world
+
+    def default_exchange(tensors, dst_, src_):
+        recv = [torch.empty_like(t) for t in tensors]
+        ops = [dist.P2POp(dist.isend, t, dst_, group) for t in tensors] + [dist.P2POp(dist.irecv, t, src_, group) for t in recv]
+        return recv, dist.batch_isend_irecv(ops)
+
+    def start(tensors):
+        if exchange is not None:
+            return exchange(tensors, dst, src), []
+        return default_exchange(tensors, dst, src)
+
+    k_cur, v_cur = K.contiguous(), V.contiguous()
+    dk_acc = torch.zeros(K.shape, dtype=torch.float32, device=K.device)
+    dv_acc = torch.zeros(V.shape, dtype=torch.float32, device=V.device)
+    dq_acc = torch.zeros(Q.shape, dtype=torch.float32, device=Q.device)
+    for s, owner in enumerate(ring_schedule(rank, world)):
+        kv_next, kv_reqs = (None, [])
+        if s + 1 < world:
+            kv_next, kv_reqs = start([k_cur, v_cur])
+        dq_s, dk_s, dv_s = backward(Q, k_cur, v_cur, O, lse, dO, _step_terms(terms, rank * n_local, owner * l_local))
+        dq_acc += dq_s
+        dk_acc += dk_s
+        dv_acc += dv_s
+        # the accumulators move on after every step, the last hop returns them to the chunk's owner
+        (dk_acc, dv_acc), acc_reqs = start([dk_acc, dv_acc])
+        for r in kv_reqs + acc_reqs:
+            r.wait()
+        if kv_next is not None:
+            k_cur, v_cur = kv_next
+    return dq_acc.to(Q.dtype), dk_acc.to(K.dtype), dv_acc.to(V.dtype)

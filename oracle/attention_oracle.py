@@ -138,13 +138,16 @@ def padded_lengths(N, L, block_size):
 # float64 ground truth
 # --------------------------------------------------------------------------------------
 
-def dense_attention(Q, K, V, mask, dO=None):
+def dense_attention(Q, K, V, mask, dO=None, kernel=None):
     """Dense masked softmax attention in float64 (NumPy) with analytic gradients.
 
     Q [B,N,Hq,d], K,V [B,L,Hkv,d], mask [B,Hq,N,L] bool.  Scores are exp(q.k/sqrt(d))
     (default_kernel, jaxmodules/attention.py:39-50); masked scores are multiplied by zero
     (line 81); rows without any allowed key return 0 (lines 99-100) and get zero gradient.
     Query head hq reads kv head hq // (Hq/Hkv) (rearrange at lines 68, 80).
+
+    ``kernel=(a, b)`` replaces the score by exp(a*q.k + b) — threshold_kernel (lines 18-36) is
+    (1, -threshold/sqrt(d)); b only shifts the log-sum-exp.
 
     Returns dict(O [B,N,Hq,d], lse [B,Hq,N]) and, when dO is given, dQ, dK, dV.
     """
@@ -154,7 +157,7 @@ def dense_attention(Q, K, V, mask, dO=None):
     B, N, Hq, d = Q.shape
     _, L, Hkv, _ = K.shape
     G = Hq // Hkv
-    scale = 1.0 / math.sqrt(d)
+    scale, shift = (1.0 / math.sqrt(d), 0.0) if kernel is None else kernel
     O = np.zeros((B, N, Hq, d))
     lse = np.full((B, Hq, N), -np.inf)
     out = {}
@@ -178,7 +181,7 @@ def dense_attention(Q, K, V, mask, dO=None):
             P = p / safe
             O[b, :, h, :] = P @ V[b, :, hk, :]
             with np.errstate(divide="ignore"):
-                lse[b, h] = np.where(valid[:, 0], np.log(safe[:, 0]) + row_max[:, 0], -np.inf)
+                lse[b, h] = np.where(valid[:, 0], np.log(safe[:, 0]) + row_max[:, 0] + shift, -np.inf)
             if dO is not None:
                 g = dO[b, :, h, :]
                 dV[b, :, hk, :] += P.T @ g
@@ -194,7 +197,8 @@ def dense_attention(Q, K, V, mask, dO=None):
     return out
 
 
-def masked_attention_dense(Q, K, V, *, is_causal=False, mask_fn=None, block_size=None, window_size=None, dO=None):
+def masked_attention_dense(Q, K, V, *, is_causal=False, mask_fn=None, block_size=None, window_size=None, dO=None,
+                           kernel=None):
     """Ground truth for the whole public call (jaxmodules/attention.py:347-455) in float64,
     including 3-D inputs, mask canonicalisation, padding and the block window."""
     Q, K, V = (np.asarray(x) for x in (Q, K, V))
@@ -207,7 +211,7 @@ def masked_attention_dense(Q, K, V, *, is_causal=False, mask_fn=None, block_size
     B, N, Hq, d = Q.shape
     L = K.shape[1]
     mask = effective_dense_mask(mask_fn, B, Hq, N, L, block_size, window_size)
-    out = dense_attention(Q, K, V, mask, dO)
+    out = dense_attention(Q, K, V, mask, dO, kernel)
     if added:
         out = {k: v[0] for k, v in out.items()}
     return out

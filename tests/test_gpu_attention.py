@@ -230,6 +230,35 @@ def test_virtual_ring_offsets_and_merge():
             assert torch.equal(torch.isfinite(lse), finite) and (lse[finite] - sl[finite]).abs().max() < 1e-4
 
 
+def test_virtual_ring_backward():
+    """Backward of the sequence partition on one GPU: each (query chunk, key chunk) pair is
+    differentiated with the queries' FINAL output and log-sum-exp and global offsets in the mask;
+    summed over the pairs the gradients must equal those of the unsplit attention."""
+    from jaxmodules_b200 import sharding as S
+    B, L, H, d, world = 1, 1024, 2, 128, 4
+    Q, K, V = (gen((B, L, H, d), i, torch.bfloat16).cuda() for i in range(3))
+    dO = gen((B, L, H, d), 3, torch.float32).cuda()
+    n = L // world
+    for terms in (M.MaskTerms(causal=True), M.MaskTerms(band=(300, 40))):
+        O, lse = S.cuda_attend(Q, K, V, terms)
+        ref = S.cuda_backward(Q, K, V, O, lse, dO, terms)
+        acc = [torch.zeros(B, L, H, d, device="cuda") for _ in range(3)]
+        for r in range(world):
+            qs = slice(r * n, (r + 1) * n)
+            for owner in S.ring_schedule(r, world):
+                ks = slice(owner * n, (owner + 1) * n)
+                t = M.MaskTerms(causal=terms.causal, band=terms.band, q_offset=r * n, k_offset=owner * n)
+                dq, dk, dv = S.cuda_backward(Q[:, qs].contiguous(), K[:, ks].contiguous(), V[:, ks].contiguous(),
+                                             O[:, qs].contiguous(), lse[:, :, qs].contiguous(), dO[:, qs].contiguous(), t)
+                acc[0][:, qs] += dq
+                acc[1][:, ks] += dk
+                acc[2][:, ks] += dv
+        torch.cuda.synchronize()
+        for got, want, name in zip(acc, ref, ("dQ", "dK", "dV")):
+            err = (got - want.float()).abs() / want.float().abs().clamp(min=1.0)
+            assert err.max() < 3e-2 and err.mean() < 2e-3, (name, float(err.max()), float(err.mean()))
+
+
 def test_tensor_core_backend_is_selected():
     """bf16 with head dim 128 must run on the tcgen05 kernels (no silent fall-back to SIMT)."""
     from jaxmodules_b200 import attention as A
@@ -239,3 +268,24 @@ def test_tensor_core_backend_is_selected():
     assert A.plan(Qf, Qf, Qf)[0] == nat.BMA_BACKEND_SIMT
     rc = C.c_int32()
     assert nat.lib().bma_device_status(torch.cuda.current_stream().cuda_stream, C.byref(rc)) == nat.BMA_OK and rc.value == 0
+
+
+@pytest.mark.parametrize("dtype,d", [(torch.float32, 16), (torch.bfloat16, 128)], ids=["f32_simt", "bf16_tcgen05"])
+def test_kernel_fn_family(dtype, d):
+    """kernel_fn = exp(a*q.k + b): threshold_kernel (jaxmodules/attention.py:18-36) and the custom
+    kernel of the reference's tests/test_mapped_attention.py:1122-1142; forward, lse and gradients."""
+    B, N, H = 1, 256, 2
+    scale = 1.0 if dtype == torch.float32 else 0.3     # keeps exp(q.k) representable without the 1/sqrt(d)
+    Q, K, V = (gen((B, N, H, d), i, dtype, scale) for i in range(3))
+    dO = gen((B, N, H, d), 3, torch.float32)
+    custom = lambda q, k: np.exp(np.dot(q, k) / (2 * np.sqrt(k.shape[-1])))
+    for kernel_fn, kernel in ((jm.threshold_kernel(3.0), (1.0, -3.0 / math.sqrt(d))), (jm.threshold_kernel(), (1.0, 0.0)),
+                              (custom, (0.5 / math.sqrt(d), 0.0))):
+        got = run(Q, K, V, dO, is_causal=True, kernel_fn=kernel_fn)
+        ref = ao.masked_attention_dense(Q.float().numpy(), K.float().numpy(), V.float().numpy(), dO=dO.numpy(),
+                                        is_causal=True, kernel=kernel)
+        check(got, ref, dtype, f"kernel {kernel}")
+        _, lse = jm.masked_attention_via_map(Q.cuda(), K.cuda(), V.cuda(), is_causal=True, kernel_fn=kernel_fn, return_lse=True)
+        assert np.abs(lse.cpu().numpy() - ref["lse"]).max() <= (1e-4 if dtype == torch.float32 else 2e-2)
+    default = run(Q, K, V, dO, is_causal=True)
+    assert not torch.allclose(got[0], default[0], rtol=1e-2)      # the reference's own assertion (:1141-1142)

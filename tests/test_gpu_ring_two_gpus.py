@@ -28,12 +28,19 @@ def _worker(rank, world, port, results):
         O, lse = S.ring_attention_forward(Q[:, sl].contiguous(), K[:, sl].contiguous(), V[:, sl].contiguous(),
                                           rank=rank, world=world, terms=terms)
         torch.cuda.synchronize()
-        results[rank] = (float((O - full[:, sl]).abs().max()), float((lse - full_lse[:, :, sl]).abs().max()))
+        dO = torch.randn(B, L, H, d, generator=g).cuda()
+        want = S.cuda_backward(Q, K, V, full, full_lse, dO, terms)
+        got = S.ring_attention_backward(Q[:, sl].contiguous(), K[:, sl].contiguous(), V[:, sl].contiguous(), O, lse,
+                                        dO[:, sl].contiguous(), rank=rank, world=world, terms=terms)
+        torch.cuda.synchronize()
+        grad_err = max(float(((a.float() - b[:, sl].float()).abs() / b[:, sl].float().abs().clamp(min=1.0)).max())
+                       for a, b in zip(got, want))
+        results[rank] = (float((O - full[:, sl]).abs().max()), float((lse - full_lse[:, :, sl]).abs().max()), grad_err)
     finally:
         dist.destroy_process_group()
 
 
-def test_ring_forward_two_gpus():
+def test_ring_forward_and_backward_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -44,4 +51,4 @@ def test_ring_forward_two_gpus():
     results = mgr.dict()
     mp.spawn(_worker, args=(2, port, results), nprocs=2, join=True)
     for r in range(2):
-        assert results[r][0] < 2e-3 and results[r][1] < 1e-4, dict(results)
+        assert results[r][0] < 2e-3 and results[r][1] < 1e-4 and results[r][2] < 3e-2, dict(results)

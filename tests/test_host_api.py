@@ -2,6 +2,8 @@
 reference's known answers, mask factories, bit-table packing, and the argument checks of
 masked_attention_via_map that fire before any CUDA work."""
 import numpy as np
+import math
+
 import pytest
 import torch
 
@@ -104,8 +106,10 @@ def test_argument_errors_precede_cuda():
         jm.masked_attention_via_map(Q[None], K, V)
     with pytest.raises(AssertionError):
         jm.masked_attention_via_map(torch.randn(8, 3, 16), K, V)   # Hq % Hkv != 0
-    with pytest.raises(NotImplementedError):
-        jm.masked_attention_via_map(Q, K, V, kernel_fn=jm.threshold_kernel(1.0))
+    with pytest.raises(NotImplementedError):    # not an exponential of the dot product
+        jm.masked_attention_via_map(Q, K, V, kernel_fn=lambda q, k: 1.0 + (q @ k) ** 2)
+    with pytest.raises(NotImplementedError):    # depends on more than the dot product
+        jm.masked_attention_via_map(Q, K, V, kernel_fn=lambda q, k: math.exp(float(q @ k) - float(q @ q)))
     with pytest.raises(RuntimeError):   # CPU tensors: there is no CPU path
         jm.masked_attention_via_map(Q, K, V)
 
@@ -115,3 +119,22 @@ def test_no_cpu_path_for_create_block_mask():
         pytest.skip("CUDA present")
     with pytest.raises(RuntimeError):
         jm.create_block_mask(lambda b, h, q, k: q >= k, 1, 1, 8, 8, 4)
+
+
+def test_kernel_log_affine():
+    """kernel_fn family of the CUDA path: exp(a*q.k + b), found from the marker functions or by probing."""
+    from jaxmodules_b200.attention import kernel_log_affine
+    d = 16
+    assert kernel_log_affine(jm.default_kernel, d) == (0.25, 0.0)
+    a, b = kernel_log_affine(jm.threshold_kernel(2.0), d)
+    assert a == 1.0 and b == pytest.approx(-0.5)
+    assert kernel_log_affine(jm.threshold_kernel(None), d) == (1.0, 0.0)
+    # the custom kernel of the reference's tests/test_mapped_attention.py:1135-1136, in NumPy and in torch
+    a, b = kernel_log_affine(lambda q, k: np.exp(np.dot(q, k) / (2 * np.sqrt(k.shape[-1]))), d)
+    assert a == pytest.approx(0.125, abs=1e-9) and b == pytest.approx(0.0, abs=1e-9)
+    a, b = kernel_log_affine(lambda q, k: torch.exp(torch.dot(q, k) * 0.3 - 1.5), d)
+    assert a == pytest.approx(0.3, abs=1e-9) and b == pytest.approx(-1.5, abs=1e-9)
+    # the marker functions evaluate like the reference's kernels
+    q, k = torch.arange(4.0) / 4, torch.ones(4)
+    assert float(jm.default_kernel(q, k)) == pytest.approx(math.exp(1.5 / 2))
+    assert float(jm.threshold_kernel(1.0)(q, k)) == pytest.approx(math.exp(1.5 - 0.5))

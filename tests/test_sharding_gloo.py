@@ -2,6 +2,7 @@
 and the ring sequence partition (K/V rotation, global offsets, log-sum-exp merge).  The CUDA
 kernels are replaced by the float64 oracle as the per-shard stand-in; what is under test is the
 partitioning, offset and merge logic of jaxmodules_b200/sharding.py."""
+import math
 import os
 import socket
 
@@ -61,6 +62,25 @@ def _oracle_merge(O, lse, O2, lse2):
     return w(wa) * O + w(wb) * O2, torch.from_numpy(l)
 
 
+def _oracle_backward(Q, K, V, O, lse, dO, terms):
+    """Gradients of one (query chunk, key chunk) pair from the GLOBAL lse and output of the queries."""
+    B, nq, Hq, d = Q.shape
+    nk, Hkv = K.shape[1], K.shape[2]
+    G = Hq // Hkv
+    m = torch.from_numpy(np.ascontiguousarray(_terms_mask(terms, B, Hq, nq, nk)))
+    Kr, Vr = K.repeat_interleave(G, dim=2), V.repeat_interleave(G, dim=2)
+    s = torch.einsum("bqhd,bkhd->bhqk", Q, Kr) / math.sqrt(d)
+    safe_lse = torch.where(torch.isfinite(lse), lse, torch.zeros_like(lse))
+    P = torch.where(m & torch.isfinite(lse)[..., None], torch.exp(s - safe_lse[..., None]), torch.zeros_like(s))
+    dP = torch.einsum("bqhd,bkhd->bhqk", dO, Vr)
+    delta = (dO * O).sum(-1).permute(0, 2, 1)
+    dS = P * (dP - delta[..., None])
+    dQ = torch.einsum("bhqk,bkhd->bqhd", dS, Kr) / math.sqrt(d)
+    dK = (torch.einsum("bhqk,bqhd->bkhd", dS, Q) / math.sqrt(d)).reshape(B, nk, Hkv, G, d).sum(3)
+    dV = torch.einsum("bhqk,bqhd->bkhd", P, dO).reshape(B, nk, Hkv, G, d).sum(3)
+    return dQ, dK, dV
+
+
 def _worker(rank, world, port, results):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -87,7 +107,7 @@ def _worker(rank, world, port, results):
 
         # --- ring sequence partition, causal and banded
         n = L // world
-        ok_ring = True
+        ok_ring = ok_bwd = True
         for terms in (M.MaskTerms(causal=True), M.MaskTerms(band=(20, 5)), M.MaskTerms(causal=True, band=(17, 1 << 20))):
             O, lse = S.ring_attention_forward(Q[:, rank * n:(rank + 1) * n], K[:, rank * n:(rank + 1) * n],
                                               V[:, rank * n:(rank + 1) * n], rank=rank, world=world, terms=terms,
@@ -95,7 +115,15 @@ def _worker(rank, world, port, results):
             ref = ao.dense_attention(Q.numpy(), K.numpy(), V.numpy(), _terms_mask(terms, B, Hq, L, L))
             ok_ring &= np.abs(O.numpy() - ref["O"][:, rank * n:(rank + 1) * n]).max() < 1e-10
             ok_ring &= np.abs(lse.numpy() - ref["lse"][:, :, rank * n:(rank + 1) * n]).max() < 1e-10
-        results[rank] = (bool(ok_shard), bool(ok_ring))
+            # backward round the same ring: dK / dV accumulators travel with their chunk and come home
+            dO = torch.from_numpy(np.random.default_rng(1).standard_normal((B, L, Hq, d)))
+            sl = slice(rank * n, (rank + 1) * n)
+            grads = S.ring_attention_backward(Q[:, sl], K[:, sl], V[:, sl], O, lse, dO[:, sl], rank=rank, world=world,
+                                              terms=terms, backward=_oracle_backward)
+            full = ao.dense_attention(Q.numpy(), K.numpy(), V.numpy(), _terms_mask(terms, B, Hq, L, L), dO.numpy())
+            for got, name in zip(grads, ("dQ", "dK", "dV")):
+                ok_bwd &= np.abs(got.numpy() - full[name][:, sl]).max() < 1e-5     # float32 accumulators
+        results[rank] = (bool(ok_shard), bool(ok_ring), bool(ok_bwd))
     finally:
         dist.destroy_process_group()
 
@@ -108,4 +136,4 @@ def test_two_ranks_gloo():
     mgr = mp.Manager()
     results = mgr.dict()
     mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
-    assert dict(results) == {0: (True, True), 1: (True, True)}
+    assert dict(results) == {0: (True, True, True), 1: (True, True, True)}
