@@ -173,6 +173,47 @@ size_t bma_mask_compile_static_limit(void);
 int bma_mask_compile_static(const bma_mask_spec* spec, int32_t B, int32_t H,
                             const bma_block_lists* lists, bma_stream_t stream);
 
+/* ---- mask programs: an arbitrary integer predicate of (b, h, q, k) evaluated on the device --------
+ * Replaces the fancy_vmap evaluation of a Python mask_fn over index grids
+ * (jaxmodules/attention.py:70-73, jaxmodules/vectorize.py:407-527) for predicates outside the
+ * bma_mask_spec family.  A program is straight-line three-address code over 32-bit integers:
+ * values 0..3 are b, h, q, k (global indices, offsets already added), instruction i defines value
+ * 4+i, the last value is the predicate (non-zero = attend).  code[4*i..4*i+3] = {op, x, y, z}:
+ *   CONST        value = x (immediate)
+ *   unary        NEG ABS NOT(value == 0) INV(bitwise ~)                          operand value x
+ *   binary       ADD SUB MUL FLOORDIV MOD (Python floor semantics; divisor 0 gives 0) MIN MAX
+ *                LT LE GT GE EQ NE (0 / 1) AND OR XOR SHL SHR                    operand values x, y
+ *   SELECT       value = x ? y : z
+ *   LOAD1        value = tables[x][clamp(value y)]                               (z unused)
+ *   LOAD2        value = tables[x][clamp(value y) * table_stride[x] + clamp(value z)]
+ * Table reads clamp their indices into range, so no program can read outside its tables.
+ * bma_mask_table_build evaluates the program for every (b, h, q, k) of the box and packs the
+ * result along k into the bit table a bma_mask_spec takes (BMA_MASK_BITMAP: bit k%32 of word
+ * k/32, [B, H, N, ceil(L/32)] int32, padding bits zero); B or H may be 1 when the program does
+ * not read that index. */
+enum {
+  BMA_OP_CONST = 0, BMA_OP_NEG, BMA_OP_ABS, BMA_OP_NOT, BMA_OP_INV,
+  BMA_OP_ADD, BMA_OP_SUB, BMA_OP_MUL, BMA_OP_FLOORDIV, BMA_OP_MOD, BMA_OP_MIN, BMA_OP_MAX,
+  BMA_OP_LT, BMA_OP_LE, BMA_OP_GT, BMA_OP_GE, BMA_OP_EQ, BMA_OP_NE,
+  BMA_OP_AND, BMA_OP_OR, BMA_OP_XOR, BMA_OP_SHL, BMA_OP_SHR,
+  BMA_OP_SELECT, BMA_OP_LOAD1, BMA_OP_LOAD2, BMA_OP_COUNT
+};
+#define BMA_PROGRAM_MAX_INSTR 60
+#define BMA_PROGRAM_MAX_TABLES 4
+
+typedef struct bma_mask_program {
+  int32_t n_instr;                                  /* 1 .. BMA_PROGRAM_MAX_INSTR */
+  int32_t n_tables;                                 /* 0 .. BMA_PROGRAM_MAX_TABLES */
+  int32_t code[4 * BMA_PROGRAM_MAX_INSTR];
+  const int32_t* tables[BMA_PROGRAM_MAX_TABLES];    /* device pointers */
+  int64_t table_rows[BMA_PROGRAM_MAX_TABLES];       /* LOAD2: rows; LOAD1: 1 */
+  int64_t table_cols[BMA_PROGRAM_MAX_TABLES];       /* elements per row */
+  int64_t table_stride[BMA_PROGRAM_MAX_TABLES];     /* elements between rows */
+} bma_mask_program;
+
+int bma_mask_table_build(const bma_mask_program* program, int32_t B, int32_t H, int32_t N, int32_t L,
+                         int32_t q_offset, int32_t k_offset, int32_t* bits, bma_stream_t stream);
+
 /* Which backend and tile sizes bma_attn_fwd (bma_attn_plan) and bma_attn_bwd
  * (bma_attn_bwd_plan) will use for these arguments; the block lists passed to each must be
  * compiled at exactly those block sizes.  (The reference has one block_size for both passes,

@@ -45,6 +45,24 @@ class BlockLists(C.Structure):
     ]
 
 
+PROGRAM_MAX_INSTR, PROGRAM_MAX_TABLES = 60, 4
+OPS = ["CONST", "NEG", "ABS", "NOT", "INV", "ADD", "SUB", "MUL", "FLOORDIV", "MOD", "MIN", "MAX",
+       "LT", "LE", "GT", "GE", "EQ", "NE", "AND", "OR", "XOR", "SHL", "SHR", "SELECT", "LOAD1", "LOAD2"]
+OP = {name: i for i, name in enumerate(OPS)}
+
+
+class MaskProgram(C.Structure):
+    """bma_mask_program of include/bma.h."""
+    _fields_ = [
+        ("n_instr", C.c_int32), ("n_tables", C.c_int32),
+        ("code", C.c_int32 * (4 * PROGRAM_MAX_INSTR)),
+        ("tables", C.c_void_p * PROGRAM_MAX_TABLES),
+        ("table_rows", C.c_int64 * PROGRAM_MAX_TABLES),
+        ("table_cols", C.c_int64 * PROGRAM_MAX_TABLES),
+        ("table_stride", C.c_int64 * PROGRAM_MAX_TABLES),
+    ]
+
+
 class Tensor(C.Structure):
     _fields_ = [
         ("ptr", C.c_void_p),
@@ -74,6 +92,8 @@ SIGNATURES = {
                                    C.c_size_t, C.c_void_p]),
     "bma_mask_compile_static_limit": (C.c_size_t, []),
     "bma_mask_compile_static": (C.c_int, [C.POINTER(MaskSpec), C.c_int32, C.c_int32, C.POINTER(BlockLists), C.c_void_p]),
+    "bma_mask_table_build": (C.c_int, [C.POINTER(MaskProgram), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                       C.c_void_p, C.c_void_p]),
     "bma_attn_plan": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "bma_attn_bwd_plan": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "bma_attn_fwd": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(MaskSpec), C.POINTER(BlockLists), C.c_void_p]),

@@ -292,7 +292,7 @@ def masked_attention_via_map(
     if is_causal:
         terms = _masks.MaskTerms(causal=True)
     else:
-        terms = _masks.terms_from_mask_fn(mask_fn, B, Hq, N, L)
+        terms = _masks.terms_from_mask_fn(mask_fn, B, Hq, N, L, device=Q.device)
 
     # Block geometry exactly as the reference derives it: padding only when N is not a
     # multiple of block_size (jaxmodules/attention.py:426-434), kv blocks sized like q blocks

@@ -289,7 +289,7 @@ def create_block_mask(mask_mod, B: int, H: int, Q_LEN: int, KV_LEN: int, BLOCK_S
     device = torch.device(device if device is not None else "cuda")
     QB, KVB = extract_block_size(BLOCK_SIZE)
     with torch.cuda.device(device):
-        terms = _masks.terms_from_mask_fn(mask_mod, B, H, Q_LEN, KV_LEN)
+        terms = _masks.terms_from_mask_fn(mask_mod, B, H, Q_LEN, KV_LEN, device=device)
         dmask = _masks.to_device_mask(terms, Q_LEN, KV_LEN, device)
         _, t = compile_block_lists(dmask, B, H, Q_LEN, KV_LEN, QB, KVB, device, out_B=B, out_H=H, q_side=True,
                                    floor_blocks=True)

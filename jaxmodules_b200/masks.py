@@ -215,8 +215,27 @@ def to_device_mask(terms: MaskTerms, N: int, L: int, device) -> DeviceMask:
     return DeviceMask(spec=s, keep=tuple(keep), depends_b=depends_b, depends_h=depends_h)
 
 
-def terms_from_mask_fn(mask_fn, B: int, Hq: int, N: int, L: int) -> MaskTerms:
-    """Structured masks pass through; any other callable becomes a bit table."""
+def _table_from_program(mask_fn, nargs: int, B: int, Hq: int, N: int, L: int, device) -> Optional[torch.Tensor]:
+    """The bit table of ``mask_fn`` built on the GPU from its traced program, or None when the
+    function cannot be traced (it is then evaluated on the host)."""
+    from . import mask_program as mp
+    try:
+        prog = mp.trace(mask_fn, nargs)
+    except mp.TraceError:
+        return None
+    Bm, Hm = (B if prog.uses_b else 1), (Hq if prog.uses_h else 1)
+    if Bm * Hm * N * L > MAX_BITMAP_BITS:
+        raise NotImplementedError(
+            "the bit table of this mask_fn would exceed 2 GiB; build the mask with "
+            "jaxmodules_b200.masks (causal_mask, sliding_window_mask, document_mask, and_masks)")
+    return mp.build_table(prog, B, Hq, N, L, device)
+
+
+def terms_from_mask_fn(mask_fn, B: int, Hq: int, N: int, L: int, device=None) -> MaskTerms:
+    """Structured masks pass through; any other callable becomes a bit table — built on the GPU
+    from the traced mask program when ``device`` is a CUDA device and the function can be traced
+    (arithmetic, comparisons, ``& | ~``, ``mask_program.where`` / ``Table``), evaluated on the host
+    over index grids otherwise."""
     if mask_fn is None:
         return MaskTerms()
     if isinstance(mask_fn, StructuredMask):
@@ -225,6 +244,10 @@ def terms_from_mask_fn(mask_fn, B: int, Hq: int, N: int, L: int) -> MaskTerms:
             raise ValueError("document_mask batch size differs from the batch size of Q")
         return t
     n = argcount(mask_fn)
+    if n in (3, 4) and device is not None and torch.device(device).type == "cuda":
+        bits = _table_from_program(mask_fn, n, B, Hq, N, L, device)
+        if bits is not None:
+            return MaskTerms(bitmap=bits)
     if n == 3:
         fn = lambda b, h, q, k: mask_fn(h, q, k)
         return MaskTerms(bitmap=bitmap_from_callable(fn, B, Hq, N, L, batch_dependent=False))
