@@ -48,6 +48,9 @@ WORKLOADS = {
                desc="sliding window |q-k|<=256 bf16 B=4 L=8192 H=16 d=128 window_size=(256,256) block_size=128"),
     "c4": dict(B=4, L=16384, H=16, d=128, bs=128, mask="documents", dtype="bf16", qkv_scale="one",
                desc="packed documents (segments 256..4096) & causal, bf16 B=4 L=16384 H=16 d=128"),
+    # head dimension 64 on the tensor-core path (same model width as c2: 64 heads of 64)
+    "d64": dict(B=8, L=4096, H=64, d=64, bs=128, mask="causal", dtype="bf16", qkv_scale="rsqrt_d",
+                desc="causal bf16 B=8 L=4096 H=64 d=64 block_size=128"),
     "c1": dict(B=2, L=128, H=8, d=64, bs=32, mask="causal", dtype="f32", qkv_scale="one",
                desc="causal fp32 B=2 L=128 H=8 d=64 block_size=32"),
 }

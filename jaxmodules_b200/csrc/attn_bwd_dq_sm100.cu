@@ -26,11 +26,11 @@ namespace {
 
 using namespace ptx;
 
-constexpr int BM = kSm100Tile, BN = kSm100Tile, HD = 128;
+constexpr int BM = kSm100Tile, BN = kSm100Tile;  // the head dimension HD (64 or 128) is a template parameter
 constexpr int kThreads = 384;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kHalfTile = BM * 64 * 2;
-constexpr uint32_t kTileBytes = 2 * kHalfTile;
+template <int HD> constexpr uint32_t kTileBytesOf = (HD / 64) * kHalfTile;  // a [128 x HD] operand tile
 constexpr int kMaxKvTiles = 1024;  // merged kv list (16-bit entries) kept in shared memory: L <= 131072
 
 enum {
@@ -40,11 +40,12 @@ enum {
   NUM_BARS
 };
 
+template <int HD>
 struct __align__(1024) DqSmem {
-  uint8_t q[2][kTileBytes];
-  uint8_t d_o[2][kTileBytes];
-  uint8_t k[2][kTileBytes];
-  uint8_t v[kTileBytes];
+  uint8_t q[2][kTileBytesOf<HD>];
+  uint8_t d_o[2][kTileBytesOf<HD>];
+  uint8_t k[2][kTileBytesOf<HD>];
+  uint8_t v[kTileBytesOf<HD>];
   uint16_t merged[kMaxKvTiles];  // kv tile | class for tile A << 12 | class for tile B << 14  (1 partial, 2 full)
   uint64_t bar[NUM_BARS];
   uint32_t tmem_base;
@@ -80,11 +81,13 @@ __device__ __forceinline__ void row_interval(const MaskView& m, int q, int k0, i
   jhi = min(hi - m.k_offset, m.k_valid - 1) - k0;
 }
 
+template <int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const DqParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  DqSmem& sm = *reinterpret_cast<DqSmem*>(smem_raw);
+  constexpr uint32_t kTileBytes = kTileBytesOf<HD>;
+  DqSmem<HD>& sm = *reinterpret_cast<DqSmem<HD>*>(smem_raw);
 
   const bma_attn_args& a = p.a;
   const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest causal tiles first
@@ -154,8 +157,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       prefetch_tensormap(&map_v);
       prefetch_tensormap(&map_do);
       auto load_tile = [&](const CUtensorMap* m, uint8_t* dst, uint64_t* bar, int head, int row0) {
-        tma_load_4d(dst, m, bar, 0, head, row0, b);
-        tma_load_4d(dst + kHalfTile, m, bar, 64, head, row0, b);
+#pragma unroll
+        for (int box = 0; box < HD / 64; ++box) tma_load_4d(dst + box * kHalfTile, m, bar, box * 64, head, row0, b);
       };
       mbar_expect_tx(&sm.bar[BAR_Q], 4 * kTileBytes);  // rows past the end are zero-filled by TMA
       load_tile(&map_q, sm.q[0], &sm.bar[BAR_Q], h, pair * 2 * BM);
@@ -352,7 +355,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       const int qs = store ? q : 0;
       __nv_bfloat16* dq = static_cast<__nv_bfloat16*>(a.dq.ptr) + (int64_t)b * a.dq.stride_b + (int64_t)qs * a.dq.stride_l + (int64_t)h * a.dq.stride_h;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < HD / 32; ++c) {
         uint32_t r[32];
         if (cnt > 0) {
           tmem_ld32(tmem_dq + c * 32, r);
@@ -397,10 +400,17 @@ int sm100_bwd_dq(const bma_attn_args& a, const bma_mask_spec& spec, const bma_bl
   p.interval_mask = (spec.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP)) ? 0 : 1;
   p.status = device_status_ptr();
   BMA_REQUIRE(p.status != nullptr, BMA_ERR_CUDA);
-  const size_t smem = sizeof(DqSmem);
-  BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+
   dim3 grid(ceil_div(ceil_div(a.N, BM), 2), a.Hq, a.B);
-  bwd_dq_kernel<<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, p);
+  if (a.d == 128) {
+    const size_t smem = sizeof(DqSmem<128>);
+    BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    bwd_dq_kernel<128><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, p);
+  } else {
+    const size_t smem = sizeof(DqSmem<64>);
+    BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    bwd_dq_kernel<64><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, p);
+  }
   count_launches(1);
   BMA_CUDA_TRY(cudaGetLastError());
   return BMA_OK;

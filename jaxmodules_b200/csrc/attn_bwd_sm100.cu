@@ -35,12 +35,13 @@ namespace {
 
 using namespace ptx;
 
-constexpr int BT = kSm100Tile, HD = 128;
+constexpr int BT = kSm100Tile;  // the head dimension HD (64 or 128) is a template parameter
 constexpr int kConsumers = 256;
 constexpr int kThreads = kConsumers + 128;  // + one warpgroup: warp 8 TMA, warp 9 MMA issue, warp 10 row statistics
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kHalfTile = BT * 64 * 2;
-constexpr uint32_t kTileBytes = 2 * kHalfTile;
+template <int HD> constexpr uint32_t kTileBytesOf = (HD / 64) * kHalfTile;  // a [128 x HD] operand tile
+constexpr uint32_t kDsBytes = 2 * kHalfTile;  // dSt: [128 keys x 128 queries]
 constexpr uint32_t COL_DV = 0, COL_DK = 128, COL_ST = 256, COL_DPT = 384, COL_PT = 384;
 
 enum {
@@ -49,12 +50,13 @@ enum {
   NUM_BARS
 };
 
+template <int HD>
 struct __align__(1024) BwdSmem {
-  uint8_t k[kTileBytes];
-  uint8_t v[kTileBytes];
-  uint8_t ds[kTileBytes];
-  uint8_t q[2][kTileBytes];
-  uint8_t d_o[2][kTileBytes];
+  uint8_t k[kTileBytesOf<HD>];
+  uint8_t v[kTileBytesOf<HD>];
+  uint8_t ds[kDsBytes];
+  uint8_t q[2][kTileBytesOf<HD>];
+  uint8_t d_o[2][kTileBytesOf<HD>];
   float lse2[2][BT];
   float delta[2][BT];
   uint64_t bar[NUM_BARS];
@@ -132,11 +134,13 @@ struct QTileIter {  // flattened walk over (group head, listed q tile)
   }
 };
 
+template <int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
+  constexpr uint32_t kTileBytes = kTileBytesOf<HD>;
+  BwdSmem<HD>& sm = *reinterpret_cast<BwdSmem<HD>*>(smem_raw);
 
   const bma_attn_args& a = p.a;
   const int kj = blockIdx.x;  // causal: kv tile 0 sees the most q tiles, so launch order is already heavy-first
@@ -185,8 +189,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       prefetch_tensormap(&map_v);
       prefetch_tensormap(&map_do);
       auto load_tile = [&](const CUtensorMap* m, uint8_t* dst, uint64_t* bar, int head, int row0) {
-        tma_load_4d(dst, m, bar, 0, head, row0, b);
-        tma_load_4d(dst + kHalfTile, m, bar, 64, head, row0, b);
+#pragma unroll
+        for (int box = 0; box < HD / 64; ++box) tma_load_4d(dst + box * kHalfTile, m, bar, box * 64, head, row0, b);
       };
       mbar_expect_tx(&sm.bar[BAR_KV], 2 * kTileBytes);
       load_tile(&map_k, sm.k, &sm.bar[BAR_KV], hk, k0);
@@ -444,14 +448,14 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // every lane takes part in the collective TMEM loads; only rows inside the tensor store
       const bool store = k < a.L;
       const int ks = store ? k : 0;
-      __nv_bfloat16* dk = static_cast<__nv_bfloat16*>(a.dk.ptr) + (int64_t)b * a.dk.stride_b + (int64_t)ks * a.dk.stride_l + (int64_t)hk * a.dk.stride_h + half * 64;
-      __nv_bfloat16* dv = static_cast<__nv_bfloat16*>(a.dv.ptr) + (int64_t)b * a.dv.stride_b + (int64_t)ks * a.dv.stride_l + (int64_t)hk * a.dv.stride_h + half * 64;
+      __nv_bfloat16* dk = static_cast<__nv_bfloat16*>(a.dk.ptr) + (int64_t)b * a.dk.stride_b + (int64_t)ks * a.dk.stride_l + (int64_t)hk * a.dk.stride_h + half * (HD / 2);
+      __nv_bfloat16* dv = static_cast<__nv_bfloat16*>(a.dv.ptr) + (int64_t)b * a.dv.stride_b + (int64_t)ks * a.dv.stride_l + (int64_t)hk * a.dv.stride_h + half * (HD / 2);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < HD / 64; ++c) {
         uint32_t rk[32], rv[32];
         if (total > 0) {
-          tmem_ld32(tmem + COL_DK + lane_base + half * 64 + c * 32, rk);
-          tmem_ld32(tmem + COL_DV + lane_base + half * 64 + c * 32, rv);
+          tmem_ld32(tmem + COL_DK + lane_base + half * (HD / 2) + c * 32, rk);
+          tmem_ld32(tmem + COL_DV + lane_base + half * (HD / 2) + c * 32, rv);
           tmem_wait_ld();
         } else {
 #pragma unroll
@@ -515,10 +519,16 @@ int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   p.interval_mask = interval;
   p.status = device_status_ptr();
   BMA_REQUIRE(p.status != nullptr, BMA_ERR_CUDA);
-  const size_t smem = sizeof(BwdSmem);
-  BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(ceil_div(a.L, BT), a.Hkv, a.B);
-  bwd_dkdv_kernel<<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, p);
+  if (a.d == 128) {
+    const size_t smem = sizeof(BwdSmem<128>);
+    BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dkdv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    bwd_dkdv_kernel<128><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, p);
+  } else {
+    const size_t smem = sizeof(BwdSmem<64>);
+    BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dkdv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    bwd_dkdv_kernel<64><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, p);
+  }
   count_launches(1);
   BMA_CUDA_TRY(cudaGetLastError());
   return sm100_bwd_dq(a, spec, lists, st);

@@ -27,11 +27,11 @@ namespace {
 
 using namespace ptx;
 
-constexpr int BM = kSm100Tile, BN = kSm100Tile, HD = 128;
+constexpr int BM = kSm100Tile, BN = kSm100Tile;  // the head dimension HD (64 or 128) is a template parameter
 constexpr int kThreads = 384;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kHalfTile = BM * 64 * 2;     // one [128 x 64] bf16 box
-constexpr uint32_t kTileBytes = 2 * kHalfTile;  // a [128 x 128] operand tile
+template <int HD> constexpr uint32_t kTileBytesOf = (HD / 64) * kHalfTile;  // a [128 x HD] operand tile: HD/64 boxes
 constexpr float kRescaleThreshold = 8.0f;       // log2 units: rescale O only when the max grew by > 2^8
 constexpr int kMaxKvTiles = 4096;               // merged kv list kept in shared memory
 #ifndef BMA_FWD_POLY
@@ -46,10 +46,11 @@ enum {
   NUM_BARS
 };
 
+template <int HD>
 struct __align__(1024) FwdSmem {
-  uint8_t q[2][kTileBytes];
-  uint8_t k[2][kTileBytes];
-  uint8_t v[2][kTileBytes];
+  uint8_t q[2][kTileBytesOf<HD>];
+  uint8_t k[2][kTileBytesOf<HD>];
+  uint8_t v[2][kTileBytesOf<HD>];
   uint32_t merged[kMaxKvTiles];  // kv tile | class for tile A << 16 | class for tile B << 18  (1 partial, 2 full)
   uint8_t cls[2][kMaxKvTiles];
   uint64_t bar[NUM_BARS];
@@ -91,11 +92,13 @@ __device__ __forceinline__ void row_interval(const MaskView& m, int q, int k0, i
   jhi = min(hi - m.k_offset, m.k_valid - 1) - k0;
 }
 
+template <int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
            const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
+  constexpr uint32_t kTileBytes = kTileBytesOf<HD>;
+  FwdSmem<HD>& sm = *reinterpret_cast<FwdSmem<HD>*>(smem_raw);
 
   const bma_attn_args& a = p.a;
   const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest causal tiles first
@@ -160,8 +163,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       prefetch_tensormap(&map_k);
       prefetch_tensormap(&map_v);
       auto load_tile = [&](const CUtensorMap* m, uint8_t* dst, uint64_t* bar, int head, int row0) {
-        tma_load_4d(dst, m, bar, 0, head, row0, b);
-        tma_load_4d(dst + kHalfTile, m, bar, 64, head, row0, b);
+#pragma unroll
+        for (int box = 0; box < HD / 64; ++box) tma_load_4d(dst + box * kHalfTile, m, bar, box * 64, head, row0, b);
       };
       mbar_expect_tx(&sm.bar[BAR_Q], 2 * kTileBytes);  // a tile past the end is zero-filled by TMA
       load_tile(&map_q, sm.q[0], &sm.bar[BAR_Q], h, pair * 2 * BM);
@@ -333,7 +336,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < HD / 32; ++c) {
           uint32_t r[32];
           tmem_ld32(tmem_o + c * 32, r);
           tmem_wait_ld();
@@ -390,7 +393,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       else
         ob = static_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)b * a.o.stride_b + (int64_t)qs * a.o.stride_l + (int64_t)h * a.o.stride_h;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < HD / 32; ++c) {
         uint32_t r[32];
         if (cnt > 0) {
           tmem_ld32(tmem_o + c * 32, r);
@@ -481,7 +484,7 @@ bool sm100_supported(const bma_attn_args& a) {
     else { (void)cudaGetLastError(); return false; }
   }
   if (cc_major != 10) return false;
-  return a.d == HD && tma_compatible(a.q) && tma_compatible(a.k) && tma_compatible(a.v) &&
+  return (a.d == 128 || a.d == 64) && tma_compatible(a.q) && tma_compatible(a.k) && tma_compatible(a.v) &&
          ceil_div(a.L, BN) <= kMaxKvTiles;
 }
 
@@ -503,10 +506,16 @@ int sm100_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   p.interval_mask = (spec.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP)) ? 0 : 1;
   p.status = device_status_ptr();
   BMA_REQUIRE(p.status != nullptr, BMA_ERR_CUDA);
-  const size_t smem = sizeof(FwdSmem);
-  BMA_CUDA_TRY(cudaFuncSetAttribute(fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(ceil_div(ceil_div(a.N, BM), 2), a.Hq, a.B);
-  fwd_kernel<<<grid, kThreads, smem, st>>>(mq, mk, mv, p);
+  if (a.d == 128) {
+    const size_t smem = sizeof(FwdSmem<128>);
+    BMA_CUDA_TRY(cudaFuncSetAttribute(fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    fwd_kernel<128><<<grid, kThreads, smem, st>>>(mq, mk, mv, p);
+  } else {
+    const size_t smem = sizeof(FwdSmem<64>);
+    BMA_CUDA_TRY(cudaFuncSetAttribute(fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    fwd_kernel<64><<<grid, kThreads, smem, st>>>(mq, mk, mv, p);
+  }
   count_launches(1);
   BMA_CUDA_TRY(cudaGetLastError());
   return BMA_OK;

@@ -153,6 +153,10 @@ BF16_CASES = {
                               kw=lambda L: dict(mask_fn=M.document_mask(document_segments(2, L, 64, 700, 4), causal=True), block_size=128)),
     "ragged_gqa": dict(B=1, L=300, H=4, d=128, scale=1.0, kw=lambda L: dict(is_causal=True, block_size=64), Hkv=2, N=200),
     "d64": dict(B=1, L=512, H=2, d=64, scale=1.0, kw=lambda L: dict(is_causal=True, block_size=128)),
+    "d64_gqa_sliding_ragged": dict(B=2, L=700, H=4, d=64, scale=1.0, Hkv=2, N=333,
+                                   kw=lambda L: dict(mask_fn=M.sliding_window_mask(150, 20), block_size=64)),
+    "d64_documents": dict(B=2, L=1024, H=2, d=64, scale=1.0,
+                          kw=lambda L: dict(mask_fn=M.document_mask(document_segments(2, L, 64, 400, 5), causal=True), block_size=128)),
 }
 
 
@@ -264,6 +268,10 @@ def test_tensor_core_backend_is_selected():
     from jaxmodules_b200 import attention as A
     Q = torch.zeros(1, 256, 2, 128, dtype=torch.bfloat16, device="cuda")
     assert A.plan(Q, Q, Q)[0] == nat.BMA_BACKEND_TCGEN05 and A.plan(Q, Q, Q, backward=True)[0] == nat.BMA_BACKEND_TCGEN05
+    Q64 = torch.zeros(1, 256, 2, 64, dtype=torch.bfloat16, device="cuda")
+    assert A.plan(Q64, Q64, Q64)[0] == nat.BMA_BACKEND_TCGEN05 and A.plan(Q64, Q64, Q64, backward=True)[0] == nat.BMA_BACKEND_TCGEN05
+    Q32 = torch.zeros(1, 256, 2, 32, dtype=torch.bfloat16, device="cuda")
+    assert A.plan(Q32, Q32, Q32)[0] == nat.BMA_BACKEND_SIMT
     Qf = torch.zeros(1, 256, 2, 64, dtype=torch.float32, device="cuda")
     assert A.plan(Qf, Qf, Qf)[0] == nat.BMA_BACKEND_SIMT
     rc = C.c_int32()
