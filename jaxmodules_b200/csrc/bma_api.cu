@@ -60,6 +60,66 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
   v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
 }
 
+// Streaming form for d <= 128 with vector accesses: one warp takes FOUR consecutive queries of one
+// (batch, head), issues all eight 16-byte loads per lane before it uses any of them, and writes the four
+// delta values as one 16-byte line, so that the [B, Hq, N] delta array is written in whole sectors
+// (one warp per row wrote 4 bytes per 32-byte sector).  Bound by HBM: reads |O| + |dO|, writes the bf16
+// copy of dO and delta.
+template <typename TO, typename TDO>
+__global__ void __launch_bounds__(256) bwd_preprocess_rows4_kernel(bma_attn_args a, __nv_bfloat16* __restrict__ do_bf16) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (blockDim.x >> 5);
+  const int64_t nq4 = (a.N + 3) / 4;
+  const int64_t units = (int64_t)a.B * a.Hq * nq4;
+  const int c = lane * 4;
+  const bool act = c < a.d;
+  for (int64_t u = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5); u < units; u += (int64_t)gridDim.x * warps) {
+    const int q0 = (int)(u % nq4) * 4;
+    const int h = (int)((u / nq4) % a.Hq);
+    const int b = (int)(u / (nq4 * a.Hq));
+    float gv[4][4], ov[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int q = q0 + i;
+      if (act && q < a.N) {
+        load4(static_cast<const TDO*>(a.d_o.ptr) + (int64_t)b * a.d_o.stride_b + (int64_t)q * a.d_o.stride_l + (int64_t)h * a.d_o.stride_h + c, gv[i]);
+        load4(static_cast<const TO*>(a.o.ptr) + (int64_t)b * a.o.stride_b + (int64_t)q * a.o.stride_l + (int64_t)h * a.o.stride_h + c, ov[i]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { gv[i][e] = 0.f; ov[i][e] = 0.f; }
+      }
+    }
+    float acc[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[i] = fmaf(gv[i][0], ov[i][0], fmaf(gv[i][1], ov[i][1], fmaf(gv[i][2], ov[i][2], gv[i][3] * ov[i][3])));
+      const int q = q0 + i;
+      if (do_bf16 && act && q < a.N) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(gv[i][0], gv[i][1]), hi = __floats2bfloat162_rn(gv[i][2], gv[i][3]);
+        uint2 w;
+        w.x = *reinterpret_cast<uint32_t*>(&lo);
+        w.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(do_bf16 + (((int64_t)b * a.N + q) * a.Hq + h) * a.d + c) = w;
+      }
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
+    }
+    float* dst = a.delta + ((int64_t)b * a.Hq + h) * a.N + q0;
+    if (lane == 0) {
+      if (q0 + 3 < a.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (q0 + i < a.N) dst[i] = acc[i];
+      }
+    }
+  }
+}
+
 // One warp per (b, q, h) row.  VEC: 4-element vector accesses (d % 4 == 0, 16-byte aligned rows).
 template <typename TO, typename TDO, bool VEC>
 __global__ void bwd_preprocess_kernel(bma_attn_args a, __nv_bfloat16* __restrict__ do_bf16) {
@@ -274,9 +334,12 @@ int bma_attn_bwd_preprocess(const bma_attn_args* args, void* d_o_bf16, bma_strea
     return (reinterpret_cast<uintptr_t>(t.ptr) & 15) == 0 && t.stride_b % 4 == 0 && t.stride_l % 4 == 0 && t.stride_h % 4 == 0;
   };
   const bool vec = args->d % 4 == 0 && vec_ok(args->o) && vec_ok(args->d_o) && (reinterpret_cast<uintptr_t>(out) & 7) == 0;
+  const int64_t units4 = (int64_t)args->B * args->Hq * ((args->N + 3) / 4);
+  const int grid4 = (int)std::min<int64_t>((units4 + 7) / 8, (int64_t)sm_count() * 32);
 #define BMA_PRE(TO, TDO)                                                                   \
   do {                                                                                     \
-    if (vec) bwd_preprocess_kernel<TO, TDO, true><<<grid, 256, 0, st>>>(*args, out);       \
+    if (vec && args->d <= 128) bwd_preprocess_rows4_kernel<TO, TDO><<<grid4, 256, 0, st>>>(*args, out); \
+    else if (vec) bwd_preprocess_kernel<TO, TDO, true><<<grid, 256, 0, st>>>(*args, out);  \
     else bwd_preprocess_kernel<TO, TDO, false><<<grid, 256, 0, st>>>(*args, out);          \
   } while (0)
   if (of && gf) BMA_PRE(float, float);
