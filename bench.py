@@ -48,6 +48,9 @@ WORKLOADS = {
                desc="sliding window |q-k|<=256 bf16 B=4 L=8192 H=16 d=128 window_size=(256,256) block_size=128"),
     "c4": dict(B=4, L=16384, H=16, d=128, bs=128, mask="documents", dtype="bf16", qkv_scale="one",
                desc="packed documents (segments 256..4096) & causal, bf16 B=4 L=16384 H=16 d=128"),
+    # BASELINE.json configs[4]: one long sequence (on one GPU here; the ring partition splits it over ranks)
+    "c5": dict(B=1, L=131072, H=32, d=128, bs=128, mask="causal", dtype="bf16", qkv_scale="one",
+               desc="causal bf16 B=1 L=131072 H=32 d=128 block_size=128"),
     # head dimension 64 on the tensor-core path (same model width as c2: 64 heads of 64)
     "d64": dict(B=8, L=4096, H=64, d=64, bs=128, mask="causal", dtype="bf16", qkv_scale="rsqrt_d",
                 desc="causal bf16 B=8 L=4096 H=64 d=64 block_size=128"),
@@ -224,6 +227,71 @@ def run_reference(args, w, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_ring(args, w, rank, world, local_rank, dev, dist, warmup):
+    """Sequence-partition mode: forward and backward of one causal sequence set split over the ranks."""
+    from jaxmodules_b200 import _native as nat, masks as M, sharding as S
+    B, L, H, d = w["B"], w["L"], w["H"], w["d"]
+    assert w["mask"] == "causal" and L % (2 * world * 128) == 0
+    dt = torch_dtype(w["dtype"])
+    n = L // world
+    scale = 1 / math.sqrt(d) if w["qkv_scale"] == "rsqrt_d" else 1.0
+    Q, K, V = (synth((B, n, H, d), 10 * rank + s, dt, scale).to(dev) for s in (0, 1, 2))
+    dO = synth((B, n, H, d), 10 * rank + 3, torch.float32).to(dev)
+    layout = (S.zigzag_layout if args.ring == "zigzag" else S.contiguous_layout)(n)
+    terms = M.MaskTerms(causal=True)
+
+    def step():
+        O, lse = S.ring_attention_forward(Q, K, V, rank=rank, world=world, terms=terms, layout=layout)
+        return S.ring_attention_backward(Q, K, V, O, lse, dO, rank=rank, world=world, terms=terms, layout=layout)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    nblk = L // 128
+    blocks = B * H * nblk * (nblk + 1) // 2                      # non-empty 128x128 blocks of the whole causal sequence
+    step_flops = 3.5 * 4.0 * 128 * 128 * d * blocks
+    for _ in range(warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = nat.lib().bma_launch_count()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for _ in range(args.steps):
+        step()
+    t1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    launches = nat.lib().bma_launch_count() - launches0
+    ms_step = t0.elapsed_time(t1) / args.steps
+    if dist is not None:
+        t = torch.tensor([ms_step], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step = float(t[0])
+    if rank == 0:
+        sustained, burst, hbm, peak_kind = peaks()
+        tf = step_flops / (ms_step * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": w["dtype"],
+            "data": "synthetic",
+            "config": {"workload": w["desc"], "api": "sharding.ring_attention_forward + ring_attention_backward",
+                       "parallelism": f"sequence split over {world} GPU(s), {args.ring} token layout, K/V and dK/dV ring over NCCL P2P",
+                       "tokens_per_gpu": n, "nonempty_blocks_total": blocks, "flop_model": "fwd 4*bq*bk*d per non-empty block, bwd 2.5x fwd",
+                       "l2": "inputs exceed the 126 MB L2; no flush needed"},
+            "roofline": {"bound": "tensor", "kernel": "forward + backward kernels of all ring steps", "achieved": tf / world,
+                         "peak": sustained, "unit": "TFLOP/s per GPU", "frac": tf / world / sustained, "traffic": None,
+                         "peak_kind": f"{peak_kind} sustained dense bf16"},
+            "clocks": clocks, "gpu_launches": int(launches)}), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -234,6 +302,9 @@ def main():
     ap.add_argument("--api", default="via_map", choices=["via_map", "flex"],
                     help="public entry point under test: masked_attention_via_map on [B,L,H,d] (default) or "
                          "flex_attention on [B,H,L,d] with a BlockMask built once outside the timed region")
+    ap.add_argument("--ring", default=None, choices=["contiguous", "zigzag"],
+                    help="sequence partition instead of batch x head shards: every rank holds L/N tokens of ONE sequence "
+                         "set (strong scaling); K/V and the dK/dV accumulators travel round the ring")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -258,6 +329,9 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     warmup = max(args.warmup, 3)
+    if args.ring:
+        run_ring(args, w, rank, world, local_rank, dev, dist, warmup)
+        return
 
     B, L, H, d = w["B"], w["L"], w["H"], w["d"]
     dt = torch_dtype(w["dtype"])

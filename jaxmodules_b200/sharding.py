@@ -117,21 +117,67 @@ def ring_schedule(rank: int, world: int) -> List[int]:
     return [(rank - s) % world for s in range(world)]
 
 
+def _step_terms(terms: _masks.MaskTerms, q_offset: int, k_offset: int) -> _masks.MaskTerms:
+    return _masks.MaskTerms(causal=terms.causal, band=terms.band, seg_q=terms.seg_q, seg_k=terms.seg_k,
+                            window=terms.window, bitmap=terms.bitmap, q_offset=terms.q_offset + q_offset,
+                            k_offset=terms.k_offset + k_offset)
+
+
+def contiguous_layout(n_local: int) -> Callable[[int, int], List[Tuple[int, int]]]:
+    """Rank r holds tokens [r*n, (r+1)*n)."""
+    return lambda rank, world: [(rank * n_local, n_local)]
+
+
+def zigzag_layout(n_local: int) -> Callable[[int, int], List[Tuple[int, int]]]:
+    """The sequence is cut into 2*world chunks and rank r holds chunks r and 2*world-1-r (its local
+    tensors are the two chunks back to back).  Under a causal mask every rank then has the same
+    number of allowed (query, key) pairs at every ring step, where the contiguous layout leaves
+    rank 0 idle for world-1 steps."""
+    if n_local % 2:
+        raise ValueError("zig-zag layout needs an even local length")
+    c = n_local // 2
+    return lambda rank, world: [(rank * c, c), ((2 * world - 1 - rank) * c, c)]
+
+
+def _segments(layout, rank: int, world: int):
+    """[(local start, global start, length)] of a rank's local sequence."""
+    out, pos = [], 0
+    for g0, n in layout(rank, world):
+        out.append((pos, g0, n))
+        pos += n
+    return out
+
+
+def _pair_is_empty(terms: _masks.MaskTerms, q0: int, qn: int, k0: int, kn: int) -> bool:
+    """True when the interval terms alone rule out every (q, k) of the pair (no launch needed)."""
+    q_lo, q_hi = terms.q_offset + q0, terms.q_offset + q0 + qn - 1
+    k_lo, k_hi = terms.k_offset + k0, terms.k_offset + k0 + kn - 1
+    if terms.causal and k_lo > q_hi:
+        return True
+    if terms.band is not None and (k_hi < q_lo - terms.band[0] or k_lo > q_hi + terms.band[1]):
+        return True
+    return False
+
+
 def ring_attention_forward(Q, K, V, *, rank: int, world: int, is_causal: bool = False,
                            terms: Optional[_masks.MaskTerms] = None, group=None,
-                           attend: Callable = cuda_attend, merge: Callable = cuda_merge):
-    """Forward attention over a sequence split into ``world`` contiguous chunks.
+                           attend: Callable = cuda_attend, merge: Callable = cuda_merge, layout=None):
+    """Forward attention over a sequence split across ``world`` ranks.
 
-    Q ``[B, N/world, Hq, d]`` and K, V ``[B, L/world, Hkv, d]`` are this rank's chunks (equal
-    sizes on every rank).  Returns (O float32, lse) for the local queries.  Each step posts the
-    send of the chunk it holds to rank+1 and the receive of the next chunk from rank-1 before it
-    computes, so the transfer runs under the kernels; received data always lands in this
-    device's own memory before a kernel reads it."""
+    Q ``[B, n, Hq, d]`` and K, V ``[B, n, Hkv, d]`` are this rank's tokens (equal sizes on every
+    rank); ``layout(rank, world)`` says which global token ranges they are — ``contiguous_layout``
+    (default) or ``zigzag_layout``.  Returns (O float32, lse) for the local queries.  Each step
+    posts the send of the K/V it holds to rank+1 and the receive of the next from rank-1 before it
+    computes, so the transfer runs under the kernels; received data always lands in this device's
+    own memory before a kernel reads it.  Within a step every (local query range, visiting key
+    range) pair is one attention call with the global offsets in the mask description; pairs the
+    interval terms rule out entirely are skipped."""
     import torch.distributed as dist
     terms = terms or _masks.MaskTerms(causal=is_causal)
-    n_local, l_local = Q.shape[1], K.shape[1]
+    layout = layout or contiguous_layout(Q.shape[1])
+    q_segs = _segments(layout, rank, world)
     k_cur, v_cur = K.contiguous(), V.contiguous()
-    O = lse = None
+    parts = [None] * len(q_segs)          # (O, lse) per local query range
     for s, owner in enumerate(ring_schedule(rank, world)):
         reqs = []
         if s + 1 < world:
@@ -140,19 +186,23 @@ def ring_attention_forward(Q, K, V, *, rank: int, world: int, is_causal: bool = 
             ops = [dist.P2POp(dist.isend, k_cur, dst, group), dist.P2POp(dist.isend, v_cur, dst, group),
                    dist.P2POp(dist.irecv, k_nxt, src, group), dist.P2POp(dist.irecv, v_nxt, src, group)]
             reqs = dist.batch_isend_irecv(ops)
-        step_terms = _masks.MaskTerms(
-            causal=terms.causal, band=terms.band, seg_q=terms.seg_q, seg_k=terms.seg_k, window=terms.window,
-            bitmap=terms.bitmap, q_offset=terms.q_offset + rank * n_local, k_offset=terms.k_offset + owner * l_local)
-        O_s, lse_s = attend(Q, k_cur, v_cur, step_terms)
-        if O is None:
-            O, lse = O_s, lse_s
-        else:
-            O, lse = merge(O, lse, O_s, lse_s)
+        for i, (ql, qg, qn) in enumerate(q_segs):
+            for kl, kg, kn in _segments(layout, owner, world):
+                if _pair_is_empty(terms, qg, qn, kg, kn):
+                    continue
+                O_s, lse_s = attend(Q[:, ql:ql + qn], k_cur[:, kl:kl + kn], v_cur[:, kl:kl + kn], _step_terms(terms, qg, kg))
+                parts[i] = (O_s, lse_s) if parts[i] is None else merge(parts[i][0], parts[i][1], O_s, lse_s)
         for r in reqs:
             r.wait()
         if s + 1 < world:
             k_cur, v_cur = k_nxt, v_nxt
-    return O, lse
+    for i, (ql, qg, qn) in enumerate(q_segs):
+        if parts[i] is None:   # a query range without any allowed key anywhere
+            parts[i] = (torch.zeros((Q.shape[0], qn, Q.shape[2], Q.shape[3]), dtype=torch.float32, device=Q.device),
+                        torch.full((Q.shape[0], Q.shape[2], qn), float("-inf"), dtype=torch.float32, device=Q.device))
+    if len(parts) == 1:
+        return parts[0]
+    return torch.cat([p[0] for p in parts], dim=1), torch.cat([p[1] for p in parts], dim=2)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -169,30 +219,26 @@ def cuda_backward(Q, K, V, O, lse, dO, terms: _masks.MaskTerms):
     return attention_backward(Q, K, V, O, lse, dO, dict(dmask=dmask))
 
 
-def _step_terms(terms: _masks.MaskTerms, q_offset: int, k_offset: int) -> _masks.MaskTerms:
-    return _masks.MaskTerms(causal=terms.causal, band=terms.band, seg_q=terms.seg_q, seg_k=terms.seg_k,
-                            window=terms.window, bitmap=terms.bitmap, q_offset=terms.q_offset + q_offset,
-                            k_offset=terms.k_offset + k_offset)
-
-
 def ring_attention_backward(Q, K, V, O, lse, dO, *, rank: int, world: int, is_causal: bool = False,
                             terms: Optional[_masks.MaskTerms] = None, group=None,
-                            backward: Callable = cuda_backward, exchange: Optional[Callable] = None):
-    """dQ, dK, dV for a sequence split into ``world`` contiguous chunks (the counterpart of
-    ``ring_attention_forward``; ``O`` / ``lse`` are its results for the local queries).
+                            backward: Callable = cuda_backward, exchange: Optional[Callable] = None, layout=None):
+    """dQ, dK, dV for a sequence split across ``world`` ranks (the counterpart of
+    ``ring_attention_forward`` with the same ``layout``; ``O`` / ``lse`` are its results for the
+    local queries).
 
     K and V travel round the ring as in the forward pass, and the float32 accumulators of dK and
-    dV travel with them: at step s this rank adds the contribution of its queries to the chunk it
-    holds and hands chunk and accumulators to rank+1.  The K/V transfer of the next step is posted
+    dV travel with them: at step s this rank adds the contribution of its queries to the tokens it
+    holds and hands tokens and accumulators to rank+1.  The K/V transfer of the next step is posted
     before the kernels of this step and runs under them; the accumulators follow once the step's
     kernels are queued.  After the last step one more hop brings every accumulator back to the
-    rank that owns the chunk.  dQ stays local (float32 accumulation over the steps).
+    rank that owns the tokens.  dQ stays local (float32 accumulation over the steps).
 
     ``exchange(tensors, dst, src)`` replaces the point-to-point transfer (it returns the received
     tensors); the default uses ``torch.distributed.batch_isend_irecv`` on ``group``."""
     import torch.distributed as dist
     terms = terms or _masks.MaskTerms(causal=is_causal)
-    n_local, l_local = Q.shape[1], K.shape[1]
+    layout = layout or contiguous_layout(Q.shape[1])
+    q_segs = _segments(layout, rank, world)
     dst, src = (rank + 1) % world, (rank - 1) % world
 
     def default_exchange(tensors, dst_, src_):
@@ -209,15 +255,22 @@ def ring_attention_backward(Q, K, V, O, lse, dO, *, rank: int, world: int, is_ca
     dk_acc = torch.zeros(K.shape, dtype=torch.float32, device=K.device)
     dv_acc = torch.zeros(V.shape, dtype=torch.float32, device=V.device)
     dq_acc = torch.zeros(Q.shape, dtype=torch.float32, device=Q.device)
+    O, dO = O.contiguous(), dO.contiguous()
     for s, owner in enumerate(ring_schedule(rank, world)):
         kv_next, kv_reqs = (None, [])
         if s + 1 < world:
             kv_next, kv_reqs = start([k_cur, v_cur])
-        dq_s, dk_s, dv_s = backward(Q, k_cur, v_cur, O, lse, dO, _step_terms(terms, rank * n_local, owner * l_local))
-        dq_acc += dq_s
-        dk_acc += dk_s
-        dv_acc += dv_s
-        # the accumulators move on after every step, the last hop returns them to the chunk's owner
+        for ql, qg, qn in q_segs:
+            for kl, kg, kn in _segments(layout, owner, world):
+                if _pair_is_empty(terms, qg, qn, kg, kn):
+                    continue
+                qs, ks = slice(ql, ql + qn), slice(kl, kl + kn)
+                dq_s, dk_s, dv_s = backward(Q[:, qs], k_cur[:, ks], v_cur[:, ks], O[:, qs], lse[:, :, qs].contiguous(),
+                                            dO[:, qs], _step_terms(terms, qg, kg))
+                dq_acc[:, qs] += dq_s
+                dk_acc[:, ks] += dk_s
+                dv_acc[:, ks] += dv_s
+        # the accumulators move on after every step, the last hop returns them to the tokens' owner
         (dk_acc, dv_acc), acc_reqs = start([dk_acc, dv_acc])
         for r in kv_reqs + acc_reqs:
             r.wait()

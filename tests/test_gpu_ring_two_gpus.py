@@ -24,18 +24,22 @@ def _worker(rank, world, port, results):
         n = L // world
         terms = M.MaskTerms(causal=True)
         full, full_lse = S.cuda_attend(Q, K, V, terms)
-        sl = slice(rank * n, (rank + 1) * n)
-        O, lse = S.ring_attention_forward(Q[:, sl].contiguous(), K[:, sl].contiguous(), V[:, sl].contiguous(),
-                                          rank=rank, world=world, terms=terms)
-        torch.cuda.synchronize()
         dO = torch.randn(B, L, H, d, generator=g).cuda()
         want = S.cuda_backward(Q, K, V, full, full_lse, dO, terms)
-        got = S.ring_attention_backward(Q[:, sl].contiguous(), K[:, sl].contiguous(), V[:, sl].contiguous(), O, lse,
-                                        dO[:, sl].contiguous(), rank=rank, world=world, terms=terms)
-        torch.cuda.synchronize()
-        grad_err = max(float(((a.float() - b[:, sl].float()).abs() / b[:, sl].float().abs().clamp(min=1.0)).max())
-                       for a, b in zip(got, want))
-        results[rank] = (float((O - full[:, sl]).abs().max()), float((lse - full_lse[:, :, sl]).abs().max()), grad_err)
+        worst = [0.0, 0.0, 0.0]
+        for make_layout in (S.contiguous_layout, S.zigzag_layout):
+            layout = make_layout(n)
+            idx = torch.cat([torch.arange(g0, g0 + m) for g0, m in layout(rank, world)]).cuda()   # global ids of the local tokens
+            loc = lambda t: t[:, idx].contiguous()
+            O, lse = S.ring_attention_forward(loc(Q), loc(K), loc(V), rank=rank, world=world, terms=terms, layout=layout)
+            got = S.ring_attention_backward(loc(Q), loc(K), loc(V), O, lse, loc(dO), rank=rank, world=world, terms=terms,
+                                            layout=layout)
+            torch.cuda.synchronize()
+            worst[0] = max(worst[0], float((O - full[:, idx]).abs().max()))
+            worst[1] = max(worst[1], float((lse - full_lse[:, :, idx]).abs().max()))
+            worst[2] = max(worst[2], max(float(((a.float() - b[:, idx].float()).abs() / b[:, idx].float().abs().clamp(min=1.0)).max())
+                                         for a, b in zip(got, want)))
+        results[rank] = tuple(worst)
     finally:
         dist.destroy_process_group()
 

@@ -105,24 +105,24 @@ def _worker(rank, world, port, results):
         want = ao.masked_attention_dense(Q.numpy(), K.numpy(), V.numpy(), mask_fn=head_mask)["O"]
         ok_shard = np.abs(full - want).max() < 1e-10
 
-        # --- ring sequence partition, causal and banded
+        # --- ring sequence partition, causal and banded, contiguous and zig-zag token layouts
         n = L // world
         ok_ring = ok_bwd = True
-        for terms in (M.MaskTerms(causal=True), M.MaskTerms(band=(20, 5)), M.MaskTerms(causal=True, band=(17, 1 << 20))):
-            O, lse = S.ring_attention_forward(Q[:, rank * n:(rank + 1) * n], K[:, rank * n:(rank + 1) * n],
-                                              V[:, rank * n:(rank + 1) * n], rank=rank, world=world, terms=terms,
-                                              attend=_oracle_attend, merge=_oracle_merge)
-            ref = ao.dense_attention(Q.numpy(), K.numpy(), V.numpy(), _terms_mask(terms, B, Hq, L, L))
-            ok_ring &= np.abs(O.numpy() - ref["O"][:, rank * n:(rank + 1) * n]).max() < 1e-10
-            ok_ring &= np.abs(lse.numpy() - ref["lse"][:, :, rank * n:(rank + 1) * n]).max() < 1e-10
-            # backward round the same ring: dK / dV accumulators travel with their chunk and come home
-            dO = torch.from_numpy(np.random.default_rng(1).standard_normal((B, L, Hq, d)))
-            sl = slice(rank * n, (rank + 1) * n)
-            grads = S.ring_attention_backward(Q[:, sl], K[:, sl], V[:, sl], O, lse, dO[:, sl], rank=rank, world=world,
-                                              terms=terms, backward=_oracle_backward)
-            full = ao.dense_attention(Q.numpy(), K.numpy(), V.numpy(), _terms_mask(terms, B, Hq, L, L), dO.numpy())
-            for got, name in zip(grads, ("dQ", "dK", "dV")):
-                ok_bwd &= np.abs(got.numpy() - full[name][:, sl]).max() < 1e-5     # float32 accumulators
+        dO = torch.from_numpy(np.random.default_rng(1).standard_normal((B, L, Hq, d)))
+        for make_layout in (S.contiguous_layout, S.zigzag_layout):
+            layout = make_layout(n)
+            idx = torch.cat([torch.arange(g0, g0 + m) for g0, m in layout(rank, world)])   # global ids of the local tokens
+            for terms in (M.MaskTerms(causal=True), M.MaskTerms(band=(20, 5)), M.MaskTerms(causal=True, band=(17, 1 << 20))):
+                O, lse = S.ring_attention_forward(Q[:, idx], K[:, idx], V[:, idx], rank=rank, world=world, terms=terms,
+                                                  attend=_oracle_attend, merge=_oracle_merge, layout=layout)
+                ref = ao.dense_attention(Q.numpy(), K.numpy(), V.numpy(), _terms_mask(terms, B, Hq, L, L), dO.numpy())
+                ok_ring &= np.abs(O.numpy() - ref["O"][:, idx]).max() < 1e-10
+                ok_ring &= np.abs(lse.numpy() - ref["lse"][:, :, idx]).max() < 1e-10
+                # backward round the same ring: dK / dV accumulators travel with their tokens and come home
+                grads = S.ring_attention_backward(Q[:, idx], K[:, idx], V[:, idx], O, lse, dO[:, idx], rank=rank, world=world,
+                                                  terms=terms, backward=_oracle_backward, layout=layout)
+                for got, name in zip(grads, ("dQ", "dK", "dV")):
+                    ok_bwd &= np.abs(got.numpy() - ref[name][:, idx]).max() < 1e-5     # float32 accumulators
         results[rank] = (bool(ok_shard), bool(ok_ring), bool(ok_bwd))
     finally:
         dist.destroy_process_group()
