@@ -166,15 +166,18 @@ def attention_forward(Q, K, V, terms: _masks.MaskTerms, *, out_dtype=torch.float
         a = _make_args(Q, K, V, backend, scale)
         be, tq, tk = plan(Q, K, V, backend)
         dmask = _masks.to_device_mask(terms, N, L, dev)
+        # when the backward pass will walk the same tile size, build its q-side lists in the same launches
+        both_sides = need_q_side and plan(Q, K, V, backend, backward=True)[1:] == (tq, tk)
         with _Span(_profile_sink, "mask_compile", dev):
-            ready = lists_fn(tq, tk, False) if lists_fn is not None else None
-            lists, lt = ready if ready is not None else compile_block_lists(dmask, B, Hq, N, L, tq, tk, dev, q_side=False)
+            ready = lists_fn(tq, tk, both_sides) if lists_fn is not None else None
+            lists, lt = ready if ready is not None else compile_block_lists(dmask, B, Hq, N, L, tq, tk, dev, q_side=both_sides)
         O = torch.empty((B, N, Hq, d), dtype=out_dtype, device=dev)
         lse = torch.empty((B, Hq, N), dtype=torch.float32, device=dev)
         a.o, a.lse = _tensor(O), lse.data_ptr()
         with _Span(_profile_sink, "fwd", dev):
             nat.check(lib.bma_attn_fwd(C.byref(a), C.byref(dmask.spec), C.byref(lists), _stream(dev)), "bma_attn_fwd")
-    ctx = dict(dmask=dmask, lists=lists, list_tensors=lt, backend=be, scale=scale, lists_fn=lists_fn)
+    ctx = dict(dmask=dmask, lists=lists, list_tensors=lt, backend=be, scale=scale, lists_fn=lists_fn,
+               lists_tile=(tq, tk), lists_have_q_side=both_sides)
     return O, lse, ctx
 
 
@@ -188,9 +191,12 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
         a = _make_args(Q, K, V, backend, ctx.get("scale"))
         be, tq, tk = plan(Q, K, V, backend, backward=True)
         with _Span(_profile_sink, "mask_compile_bwd", dev):
-            lists_fn = ctx.get("lists_fn")
-            ready = lists_fn(tq, tk, True) if lists_fn is not None else None
-            lists, lt = ready if ready is not None else compile_block_lists(ctx["dmask"], B, Hq, N, L, tq, tk, dev, q_side=True)
+            if ctx.get("lists_have_q_side") and ctx.get("lists_tile") == (tq, tk):
+                lists, lt = ctx["lists"], ctx["list_tensors"]      # built by the forward pass
+            else:
+                lists_fn = ctx.get("lists_fn")
+                ready = lists_fn(tq, tk, True) if lists_fn is not None else None
+                lists, lt = ready if ready is not None else compile_block_lists(ctx["dmask"], B, Hq, N, L, tq, tk, dev, q_side=True)
         if dO.stride(-1) != 1:
             dO = dO.contiguous()
         delta = torch.empty((B, Hq, N), dtype=torch.float32, device=dev)

@@ -115,6 +115,20 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     fence_barrier_init();
   }
   __syncthreads();
+  if (warp == 8 && lane == 0) {
+    // Q and dO of the two query tiles do not depend on the block lists: their loads run under the
+    // list build.  (Rows past the end are zero-filled by TMA.)
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_do);
+    mbar_expect_tx(&sm.bar[BAR_Q], 4 * kTileBytes);
+#pragma unroll
+    for (int x = 0; x < 2; ++x)
+#pragma unroll
+      for (int box = 0; box < HD / 64; ++box) {
+        tma_load_4d(sm.q[x] + box * kHalfTile, &map_q, &sm.bar[BAR_Q], box * 64, h, (pair * 2 + x) * BM, b);
+        tma_load_4d(sm.d_o[x] + box * kHalfTile, &map_do, &sm.bar[BAR_Q], box * 64, h, (pair * 2 + x) * BM, b);
+      }
+  }
   for (int x = 0; x < 2; ++x) {
     const int qi = pair * 2 + x;
     if (qi >= NQ) break;
@@ -152,19 +166,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     setmaxnreg_dec_96();
     if (warp == 8 && lane == 0 && T > 0) {
       // ---------------------------------------------------------------- TMA producer
-      prefetch_tensormap(&map_q);
       prefetch_tensormap(&map_k);
       prefetch_tensormap(&map_v);
-      prefetch_tensormap(&map_do);
       auto load_tile = [&](const CUtensorMap* m, uint8_t* dst, uint64_t* bar, int head, int row0) {
 #pragma unroll
         for (int box = 0; box < HD / 64; ++box) tma_load_4d(dst + box * kHalfTile, m, bar, box * 64, head, row0, b);
       };
-      mbar_expect_tx(&sm.bar[BAR_Q], 4 * kTileBytes);  // rows past the end are zero-filled by TMA
-      load_tile(&map_q, sm.q[0], &sm.bar[BAR_Q], h, pair * 2 * BM);
-      load_tile(&map_q, sm.q[1], &sm.bar[BAR_Q], h, (pair * 2 + 1) * BM);
-      load_tile(&map_do, sm.d_o[0], &sm.bar[BAR_Q], h, pair * 2 * BM);
-      load_tile(&map_do, sm.d_o[1], &sm.bar[BAR_Q], h, (pair * 2 + 1) * BM);
       bool ok = true;
       for (int n = 0; n < T && ok; ++n) {
         const int st = n & 1;
@@ -379,6 +386,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     }
   }
 
+  if (T == 0 && warp == 8 && lane == 0 && !mbar_wait(&sm.bar[BAR_Q], 0))   // nobody consumed Q / dO: let the loads land before the CTA ends
+    report_device_error(p.status, 440);
   tc_fence_before();
   __syncthreads();
   if (warp == 8) tmem_dealloc(tmem, kTmemCols);
