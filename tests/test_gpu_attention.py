@@ -210,6 +210,47 @@ def test_full_size_properties_config2():
     assert (lhs - rhs).abs().max() / rhs.abs().max() < 2e-2
 
 
+FULL_SIZE = {
+    # BASELINE configs 3 and 4 and the L=8192 causal target shape, at their full sizes
+    "config3_sliding": dict(B=4, L=8192, H=16, kw=lambda seg: dict(mask_fn=M.sliding_window_mask(256, 256), window_size=(256, 256), block_size=128),
+                            dense=lambda seg, b, q, k: (k >= q - 256) & (k <= q + 256)),
+    "config4_documents": dict(B=4, L=16384, H=16, kw=lambda seg: dict(mask_fn=M.document_mask(seg, causal=True), block_size=128),
+                              dense=lambda seg, b, q, k: (seg[b][q] == seg[b][k]) & (k <= q)),
+    "target_causal_8192": dict(B=4, L=8192, H=32, kw=lambda seg: dict(is_causal=True, block_size=128),
+                               dense=lambda seg, b, q, k: k <= q),
+}
+
+
+@pytest.mark.parametrize("name", list(FULL_SIZE))
+def test_full_size_slices_against_dense_fp32(name):
+    """Full-size runs of the BASELINE shapes; two (batch, head) slices of the result — slices are
+    independent of one another — are compared with a dense float32 torch attention (autograd for the
+    gradients) of the same slice on the GPU.  bf16 tolerances as above."""
+    c = FULL_SIZE[name]
+    B, L, H, d = c["B"], c["L"], c["H"], 128
+    g = torch.Generator(device="cuda").manual_seed(1)
+    Q, K, V = (torch.randn(B, L, H, d, device="cuda", generator=g).to(torch.bfloat16).requires_grad_(True) for _ in range(3))
+    dO = torch.randn(B, L, H, d, device="cuda", generator=g)
+    seg_np = document_segments(B, L, 256, 4096, 4)
+    O = jm.masked_attention_via_map(Q, K, V, **c["kw"](seg_np))
+    O.backward(dO)
+    seg = torch.from_numpy(seg_np).cuda()
+    qi, ki = torch.arange(L, device="cuda")[:, None], torch.arange(L, device="cuda")[None, :]
+    for b, h in ((0, 0), (B - 1, H - 1)):
+        q, k, v = (t[b, :, h].detach().float().requires_grad_(True) for t in (Q, K, V))
+        mask = c["dense"](seg, b, qi, ki)
+        s = (q @ k.T) / math.sqrt(d)
+        p = torch.softmax(s.masked_fill(~mask, float("-inf")), dim=-1)
+        o = p @ v
+        o.backward(dO[b, :, h])
+        for got, ref, what in ((O[b, :, h], o, "O"), (Q.grad[b, :, h], q.grad, "dQ"), (K.grad[b, :, h], k.grad, "dK"),
+                               (V.grad[b, :, h], v.grad, "dV")):
+            err = (got.detach().float() - ref.detach()).abs()
+            scaled = err / ref.detach().abs().clamp(min=1.0)
+            assert scaled.max() <= 2e-2 and err.mean() <= 2e-3, (name, b, h, what, float(scaled.max()), float(err.mean()))
+        del s, p, o, mask
+
+
 def test_virtual_ring_offsets_and_merge():
     """The sequence-partition path on one GPU: every (query chunk, key chunk) pair is attended with
     global offsets in the mask description and merged with bma_attn_merge, exactly what the ring
