@@ -137,7 +137,8 @@ struct QTileIter {  // flattened walk over (group head, listed q tile)
 template <int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const BwdParams p) {
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                const __grid_constant__ CUtensorMap map_dk, const __grid_constant__ CUtensorMap map_dv, const BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr uint32_t kTileBytes = kTileBytesOf<HD>;
   BwdSmem<HD>& sm = *reinterpret_cast<BwdSmem<HD>*>(smem_raw);
@@ -445,11 +446,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       report_device_error(p.status, 320 + warp);
     } else {
       tc_fence_after();
-      // every lane takes part in the collective TMEM loads; only rows inside the tensor store
-      const bool store = k < a.L;
-      const int ks = store ? k : 0;
-      __nv_bfloat16* dk = static_cast<__nv_bfloat16*>(a.dk.ptr) + (int64_t)b * a.dk.stride_b + (int64_t)ks * a.dk.stride_l + (int64_t)hk * a.dk.stride_h + half * (HD / 2);
-      __nv_bfloat16* dv = static_cast<__nv_bfloat16*>(a.dv.ptr) + (int64_t)b * a.dv.stride_b + (int64_t)ks * a.dv.stride_l + (int64_t)hk * a.dv.stride_h + half * (HD / 2);
+      // dK (scaled) and dV go through shared memory — the K and V tiles are dead now — in the 128-byte-swizzled
+      // box layout and leave as TMA stores of whole lines (rows past the end of the tensor are clipped by the
+      // tensor map).  Thread (row, half) owns HD/2 columns of key row `row`.
+      uint8_t* k_row = sm.k + (HD == 128 ? half * kHalfTile : 0) + row * 128;
+      uint8_t* v_row = sm.v + (HD == 128 ? half * kHalfTile : 0) + row * 128;
 #pragma unroll
       for (int c = 0; c < HD / 64; ++c) {
         uint32_t rk[32], rv[32];
@@ -461,22 +462,35 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
           for (int j = 0; j < 32; ++j) { rk[j] = 0u; rv[j] = 0u; }
         }
-        if (store) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint4 ok4, ov4;
-            ok4.x = pack_bf16(__uint_as_float(rk[j]) * a.scale, __uint_as_float(rk[j + 1]) * a.scale);
-            ok4.y = pack_bf16(__uint_as_float(rk[j + 2]) * a.scale, __uint_as_float(rk[j + 3]) * a.scale);
-            ok4.z = pack_bf16(__uint_as_float(rk[j + 4]) * a.scale, __uint_as_float(rk[j + 5]) * a.scale);
-            ok4.w = pack_bf16(__uint_as_float(rk[j + 6]) * a.scale, __uint_as_float(rk[j + 7]) * a.scale);
-            ov4.x = pack_bf16(__uint_as_float(rv[j]), __uint_as_float(rv[j + 1]));
-            ov4.y = pack_bf16(__uint_as_float(rv[j + 2]), __uint_as_float(rv[j + 3]));
-            ov4.z = pack_bf16(__uint_as_float(rv[j + 4]), __uint_as_float(rv[j + 5]));
-            ov4.w = pack_bf16(__uint_as_float(rv[j + 6]), __uint_as_float(rv[j + 7]));
-            *reinterpret_cast<uint4*>(dk + c * 32 + j) = ok4;
-            *reinterpret_cast<uint4*>(dv + c * 32 + j) = ov4;
-          }
+        for (int u = 0; u < 4; ++u) {
+          const int j = u * 8;
+          uint4 ok4, ov4;
+          ok4.x = pack_bf16(__uint_as_float(rk[j]) * a.scale, __uint_as_float(rk[j + 1]) * a.scale);
+          ok4.y = pack_bf16(__uint_as_float(rk[j + 2]) * a.scale, __uint_as_float(rk[j + 3]) * a.scale);
+          ok4.z = pack_bf16(__uint_as_float(rk[j + 4]) * a.scale, __uint_as_float(rk[j + 5]) * a.scale);
+          ok4.w = pack_bf16(__uint_as_float(rk[j + 6]) * a.scale, __uint_as_float(rk[j + 7]) * a.scale);
+          ov4.x = pack_bf16(__uint_as_float(rv[j]), __uint_as_float(rv[j + 1]));
+          ov4.y = pack_bf16(__uint_as_float(rv[j + 2]), __uint_as_float(rv[j + 3]));
+          ov4.z = pack_bf16(__uint_as_float(rv[j + 4]), __uint_as_float(rv[j + 5]));
+          ov4.w = pack_bf16(__uint_as_float(rv[j + 6]), __uint_as_float(rv[j + 7]));
+          const int chunk = ((HD == 128 ? c * 4 : half * 4) + u) ^ (row & 7);
+          *reinterpret_cast<uint4*>(k_row + chunk * 16) = ok4;
+          *reinterpret_cast<uint4*>(v_row + chunk * 16) = ov4;
         }
+      }
+      fence_proxy_async();  // the TMA engine reads the staged tiles through the async proxy
+      ok = consumer_sync(&sm.bar[BAR_SYNC2], total & 1);
+      if (!ok) {
+        report_device_error(p.status, 340 + warp);
+      } else if (threadIdx.x == 0) {
+#pragma unroll
+        for (int box = 0; box < HD / 64; ++box) {
+          tma_store_4d(&map_dk, sm.k + box * kHalfTile, box * 64, hk, k0, b);
+          tma_store_4d(&map_dv, sm.v + box * kHalfTile, box * 64, hk, k0, b);
+        }
+        bulk_commit();
+        bulk_wait_read0();  // shared memory must stay intact until the stores have read it
       }
     }
   }
@@ -512,6 +526,9 @@ int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   if ((rc = make_tile_map_bf16(&mk, a.k.ptr, a.B, a.L, a.Hkv, a.d, a.k.stride_b, a.k.stride_l, a.k.stride_h, BT))) return rc;
   if ((rc = make_tile_map_bf16(&mv, a.v.ptr, a.B, a.L, a.Hkv, a.d, a.v.stride_b, a.v.stride_l, a.v.stride_h, BT))) return rc;
   if ((rc = make_tile_map_bf16(&mdo, a.d_o.ptr, a.B, a.N, a.Hq, a.d, a.d_o.stride_b, a.d_o.stride_l, a.d_o.stride_h, BT))) return rc;
+  CUtensorMap mdk, mdv;
+  if ((rc = make_tile_map_bf16(&mdk, a.dk.ptr, a.B, a.L, a.Hkv, a.d, a.dk.stride_b, a.dk.stride_l, a.dk.stride_h, BT))) return rc;
+  if ((rc = make_tile_map_bf16(&mdv, a.dv.ptr, a.B, a.L, a.Hkv, a.d, a.dv.stride_b, a.dv.stride_l, a.dv.stride_h, BT))) return rc;
 
   BwdParams p;
   p.a = a; p.spec = spec; p.l = lists;
@@ -523,11 +540,11 @@ int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   if (a.d == 128) {
     const size_t smem = sizeof(BwdSmem<128>);
     BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dkdv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    bwd_dkdv_kernel<128><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, p);
+    bwd_dkdv_kernel<128><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
   } else {
     const size_t smem = sizeof(BwdSmem<64>);
     BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dkdv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    bwd_dkdv_kernel<64><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, p);
+    bwd_dkdv_kernel<64><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
   }
   count_launches(1);
   BMA_CUDA_TRY(cudaGetLastError());

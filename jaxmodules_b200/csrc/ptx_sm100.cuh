@@ -69,6 +69,18 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// 4-D tiled store shared -> global of one box (rows / columns outside the tensor are clipped);
+// completion is tracked by the bulk async-group of the issuing thread.  The source must have been
+// written before a fence.proxy.async, and c0 must keep the destination 16-byte aligned.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until the committed bulk groups have finished READING their shared-memory sources
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
 // ---- tensor memory -------------------------------------------------------------------------
 // Executed by one full warp.  ncols: power of two >= 32.  The base address lands in *smem_out.
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_out, uint32_t ncols) {
