@@ -36,7 +36,7 @@ constexpr int kMaxKvTiles = 1024;  // merged kv list (16-bit entries) kept in sh
 enum {
   BAR_Q = 0,
   BAR_K_FULL0, BAR_K_FULL1, BAR_K_FREE0, BAR_K_FREE1, BAR_V_FULL, BAR_V_FREE,
-  BAR_S0, BAR_S1, BAR_LS0, BAR_LS1, BAR_DP0, BAR_DP1, BAR_DS0, BAR_DS1, BAR_DQ0, BAR_DQ1,
+  BAR_S0, BAR_S1, BAR_LS0, BAR_LS1, BAR_DP0, BAR_DP1, BAR_DS0, BAR_DS1, BAR_DQ0, BAR_DQ1, BAR_EPI0, BAR_EPI1,
   NUM_BARS
 };
 
@@ -84,7 +84,8 @@ __device__ __forceinline__ void row_interval(const MaskView& m, int q, int k0, i
 template <int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-              const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const DqParams p) {
+              const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+              const __grid_constant__ CUtensorMap map_dq, const DqParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr uint32_t kTileBytes = kTileBytesOf<HD>;
   DqSmem<HD>& sm = *reinterpret_cast<DqSmem<HD>*>(smem_raw);
@@ -109,7 +110,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   for (int i = threadIdx.x; i < NKV; i += kThreads) { cls0[i] = 0; cls1[i] = 0; }
   if (threadIdx.x == 0) {
     for (int i = 0; i < NUM_BARS; ++i) {
-      const bool wide = i == BAR_LS0 || i == BAR_LS1 || i == BAR_DS0 || i == BAR_DS1;
+      const bool wide = i == BAR_LS0 || i == BAR_LS1 || i == BAR_DS0 || i == BAR_DS1 || i == BAR_EPI0 || i == BAR_EPI1;
       mbar_init(&sm.bar[i], wide ? 128 : 1);
     }
     fence_barrier_init();
@@ -357,10 +358,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     if (!ok) {
       report_device_error(p.status, 430 + warp);
     } else if (qi < NQ) {
+      // dQ goes through shared memory — the tile's own Q buffer, which no MMA reads any more — in the
+      // 128-byte-swizzled box layout and leaves as TMA stores of whole lines (rows past the end of the
+      // tensor are clipped by the tensor map).  A tile without any key block must first let the Q load land.
+      if (cnt == 0) ok = mbar_wait(&sm.bar[BAR_Q], 0);
       tc_fence_after();
-      const bool store = q < a.N;
-      const int qs = store ? q : 0;
-      __nv_bfloat16* dq = static_cast<__nv_bfloat16*>(a.dq.ptr) + (int64_t)b * a.dq.stride_b + (int64_t)qs * a.dq.stride_l + (int64_t)h * a.dq.stride_h;
+      uint8_t* q_row = sm.q[x] + row * 128;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t r[32];
@@ -371,17 +374,28 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        if (store) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint4 v4;
-            v4.x = pack_bf16(__uint_as_float(r[j]) * a.scale, __uint_as_float(r[j + 1]) * a.scale);
-            v4.y = pack_bf16(__uint_as_float(r[j + 2]) * a.scale, __uint_as_float(r[j + 3]) * a.scale);
-            v4.z = pack_bf16(__uint_as_float(r[j + 4]) * a.scale, __uint_as_float(r[j + 5]) * a.scale);
-            v4.w = pack_bf16(__uint_as_float(r[j + 6]) * a.scale, __uint_as_float(r[j + 7]) * a.scale);
-            *reinterpret_cast<uint4*>(dq + c * 32 + j) = v4;
-          }
+        for (int u = 0; u < 4; ++u) {
+          const int j = u * 8;
+          uint4 v4;
+          v4.x = pack_bf16(__uint_as_float(r[j]) * a.scale, __uint_as_float(r[j + 1]) * a.scale);
+          v4.y = pack_bf16(__uint_as_float(r[j + 2]) * a.scale, __uint_as_float(r[j + 3]) * a.scale);
+          v4.z = pack_bf16(__uint_as_float(r[j + 4]) * a.scale, __uint_as_float(r[j + 5]) * a.scale);
+          v4.w = pack_bf16(__uint_as_float(r[j + 6]) * a.scale, __uint_as_float(r[j + 7]) * a.scale);
+          const int chunk = ((c & 1) * 4 + u) ^ (row & 7);            // 32 columns = four 16-byte chunks of a box row
+          *reinterpret_cast<uint4*>(q_row + (c >> 1) * kHalfTile + chunk * 16) = v4;
         }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the TMA engine reads the staged tile through the async proxy
+      mbar_arrive(&sm.bar[BAR_EPI0 + x]);
+      ok = ok && mbar_wait(&sm.bar[BAR_EPI0 + x], 0);
+      if (!ok) {
+        report_device_error(p.status, 450 + warp);
+      } else if (row == 0) {
+#pragma unroll
+        for (int box = 0; box < HD / 64; ++box) tma_store_4d(&map_dq, sm.q[x] + box * kHalfTile, box * 64, h, qi * BM, b);
+        bulk_commit();
+        bulk_wait_read0();  // shared memory must stay intact until the stores have read it
       }
     }
   }
@@ -397,12 +411,13 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 
 int sm100_bwd_dq(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, cudaStream_t st) {
   BMA_REQUIRE(lists.NKV <= kMaxKvTiles, BMA_ERR_LIMIT);
-  CUtensorMap mq, mk, mv, mdo;
+  CUtensorMap mq, mk, mv, mdo, mdq;
   int rc;
   if ((rc = make_tile_map_bf16(&mq, a.q.ptr, a.B, a.N, a.Hq, a.d, a.q.stride_b, a.q.stride_l, a.q.stride_h, BM))) return rc;
   if ((rc = make_tile_map_bf16(&mk, a.k.ptr, a.B, a.L, a.Hkv, a.d, a.k.stride_b, a.k.stride_l, a.k.stride_h, BN))) return rc;
   if ((rc = make_tile_map_bf16(&mv, a.v.ptr, a.B, a.L, a.Hkv, a.d, a.v.stride_b, a.v.stride_l, a.v.stride_h, BN))) return rc;
   if ((rc = make_tile_map_bf16(&mdo, a.d_o.ptr, a.B, a.N, a.Hq, a.d, a.d_o.stride_b, a.d_o.stride_l, a.d_o.stride_h, BM))) return rc;
+  if ((rc = make_tile_map_bf16(&mdq, a.dq.ptr, a.B, a.N, a.Hq, a.d, a.dq.stride_b, a.dq.stride_l, a.dq.stride_h, BM))) return rc;
   DqParams p;
   p.a = a; p.spec = spec; p.l = lists;
   p.scale_log2 = a.scale * kLog2e;
@@ -414,11 +429,11 @@ int sm100_bwd_dq(const bma_attn_args& a, const bma_mask_spec& spec, const bma_bl
   if (a.d == 128) {
     const size_t smem = sizeof(DqSmem<128>);
     BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    bwd_dq_kernel<128><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, p);
+    bwd_dq_kernel<128><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, mdq, p);
   } else {
     const size_t smem = sizeof(DqSmem<64>);
     BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    bwd_dq_kernel<64><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, p);
+    bwd_dq_kernel<64><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, mdq, p);
   }
   count_launches(1);
   BMA_CUDA_TRY(cudaGetLastError());
