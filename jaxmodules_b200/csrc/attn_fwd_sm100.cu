@@ -42,7 +42,7 @@ enum {
   BAR_Q = 0,
   BAR_K_FULL0, BAR_K_FULL1, BAR_K_FREE0, BAR_K_FREE1,
   BAR_V_FULL0, BAR_V_FULL1, BAR_V_FREE0, BAR_V_FREE1,
-  BAR_S0, BAR_S1, BAR_PH0, BAR_PH1, BAR_P0, BAR_P1, BAR_O0, BAR_O1,
+  BAR_S0, BAR_S1, BAR_PH0, BAR_PH1, BAR_P0, BAR_P1, BAR_O0, BAR_O1, BAR_EPI0, BAR_EPI1,
   NUM_BARS
 };
 
@@ -95,7 +95,7 @@ __device__ __forceinline__ void row_interval(const MaskView& m, int q, int k0, i
 template <int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-           const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
+           const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, const FwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr uint32_t kTileBytes = kTileBytesOf<HD>;
   FwdSmem<HD>& sm = *reinterpret_cast<FwdSmem<HD>*>(smem_raw);
@@ -119,7 +119,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   if (threadIdx.x == 0) {
     mbar_init(&sm.bar[BAR_Q], 1);
     for (int i = BAR_K_FULL0; i < NUM_BARS; ++i)
-      mbar_init(&sm.bar[i], (i == BAR_P0 || i == BAR_P1 || i == BAR_PH0 || i == BAR_PH1) ? 128 : 1);
+      mbar_init(&sm.bar[i], (i == BAR_P0 || i == BAR_P1 || i == BAR_PH0 || i == BAR_PH1 || i == BAR_EPI0 || i == BAR_EPI1) ? 128 : 1);
     fence_barrier_init();
   }
   __syncthreads();
@@ -389,48 +389,85 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     if (!ok) {
       report_device_error(p.status, 200 + warp);
     } else if (qi < NQ) {
+      // O goes through shared memory — the tile's own Q buffer, which no MMA reads any more — in the
+      // 128-byte-swizzled box layout and leaves as TMA stores of whole lines (rows past the end of the
+      // tensor are clipped by the tensor map).  The buffer holds a bf16 tile of HD columns, i.e. HD/2 float32
+      // columns at a time (two passes).  A tile without any key block must first let the Q load land.
+      if (cnt == 0) ok = mbar_wait(&sm.bar[BAR_Q], 0);
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      const bool store = q < a.N;
-      const int qs = store ? q : 0;
-      float* of = nullptr;
-      __nv_bfloat16* ob = nullptr;
-      if (a.o.dtype == BMA_DTYPE_F32)
-        of = static_cast<float*>(a.o.ptr) + (int64_t)b * a.o.stride_b + (int64_t)qs * a.o.stride_l + (int64_t)h * a.o.stride_h;
-      else
-        ob = static_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)b * a.o.stride_b + (int64_t)qs * a.o.stride_l + (int64_t)h * a.o.stride_h;
+      uint8_t* q_row = sm.q[x] + row * 128;
+      uint32_t syncs = 0;
+      auto rendezvous = [&]() {  // the 128 threads of this tile
+        mbar_arrive(&sm.bar[BAR_EPI0 + x]);
+        ok = ok && mbar_wait(&sm.bar[BAR_EPI0 + x], syncs & 1);
+        ++syncs;
+      };
+      if (a.o.dtype == BMA_DTYPE_F32) {
+        constexpr int kBoxes = HD / 64;    // boxes of [128 rows x 32 floats] the buffer holds
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t r[32];
-        if (cnt > 0) {
-          tmem_ld32(tmem_o + c * 32, r);
-          tmem_wait_ld();
-        } else {
+        for (int pass = 0; pass < 2; ++pass) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = 0u;
-        }
-        if (store) {
-          if (of) {
+          for (int cc = 0; cc < kBoxes; ++cc) {
+            uint32_t r[32];
+            if (cnt > 0) {
+              tmem_ld32(tmem_o + (pass * kBoxes + cc) * 32, r);
+              tmem_wait_ld();
+            } else {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 v4 = make_float4(__uint_as_float(r[j]) * inv, __uint_as_float(r[j + 1]) * inv,
-                                      __uint_as_float(r[j + 2]) * inv, __uint_as_float(r[j + 3]) * inv);
-              *reinterpret_cast<float4*>(of + c * 32 + j) = v4;
+              for (int j = 0; j < 32; ++j) r[j] = 0u;
             }
-          } else {
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 v4;
-              v4.x = pack_bf16(__uint_as_float(r[j]) * inv, __uint_as_float(r[j + 1]) * inv);
-              v4.y = pack_bf16(__uint_as_float(r[j + 2]) * inv, __uint_as_float(r[j + 3]) * inv);
-              v4.z = pack_bf16(__uint_as_float(r[j + 4]) * inv, __uint_as_float(r[j + 5]) * inv);
-              v4.w = pack_bf16(__uint_as_float(r[j + 6]) * inv, __uint_as_float(r[j + 7]) * inv);
-              *reinterpret_cast<uint4*>(ob + c * 32 + j) = v4;
+            for (int u = 0; u < 8; ++u) {
+              const float4 v4 = make_float4(__uint_as_float(r[u * 4]) * inv, __uint_as_float(r[u * 4 + 1]) * inv,
+                                            __uint_as_float(r[u * 4 + 2]) * inv, __uint_as_float(r[u * 4 + 3]) * inv);
+              *reinterpret_cast<float4*>(q_row + cc * kHalfTile + ((u ^ (row & 7)) * 16)) = v4;
             }
           }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the TMA engine reads through the async proxy
+          rendezvous();
+          if (ok && row == 0) {
+#pragma unroll
+            for (int cc = 0; cc < kBoxes; ++cc) tma_store_4d(&map_o, sm.q[x] + cc * kHalfTile, (pass * kBoxes + cc) * 32, h, qi * BM, b);
+            bulk_commit();
+            bulk_wait_read0();  // the buffer is reused by the next pass / must outlive the reads
+          }
+          if (pass == 0) rendezvous();  // nobody overwrites the buffer before the stores have read it
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t r[32];
+          if (cnt > 0) {
+            tmem_ld32(tmem_o + c * 32, r);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int j = u * 8;
+            uint4 v4;
+            v4.x = pack_bf16(__uint_as_float(r[j]) * inv, __uint_as_float(r[j + 1]) * inv);
+            v4.y = pack_bf16(__uint_as_float(r[j + 2]) * inv, __uint_as_float(r[j + 3]) * inv);
+            v4.z = pack_bf16(__uint_as_float(r[j + 4]) * inv, __uint_as_float(r[j + 5]) * inv);
+            v4.w = pack_bf16(__uint_as_float(r[j + 6]) * inv, __uint_as_float(r[j + 7]) * inv);
+            const int chunk = ((c & 1) * 4 + u) ^ (row & 7);
+            *reinterpret_cast<uint4*>(q_row + (c >> 1) * kHalfTile + chunk * 16) = v4;
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        rendezvous();
+        if (ok && row == 0) {
+#pragma unroll
+          for (int box = 0; box < HD / 64; ++box) tma_store_4d(&map_o, sm.q[x] + box * kHalfTile, box * 64, h, qi * BM, b);
+          bulk_commit();
+          bulk_wait_read0();
         }
       }
-      if (store && a.lse)
+      if (!ok) report_device_error(p.status, 230 + warp);
+      if (q < a.N && a.lse)
         a.lse[((int64_t)b * a.Hq + h) * a.N + q] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
     }
   }
@@ -478,6 +515,22 @@ int make_tile_map_bf16(CUtensorMap* out, const void* base, int B, int L, int H, 
   return BMA_OK;
 }
 
+// Same for a float32 tensor: boxes of [box_rows x 32 columns] (128 bytes per row).
+static int make_tile_map_f32(CUtensorMap* out, const void* base, int B, int L, int H, int d, int64_t stride_b,
+                             int64_t stride_l, int64_t stride_h, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) { set_last_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point"); return BMA_ERR_CUDA; }
+  const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)H, (cuuint64_t)L, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {(cuuint64_t)stride_h * 4, (cuuint64_t)stride_l * 4, (cuuint64_t)stride_b * 4};
+  const cuuint32_t box[4] = {32, 1, (cuuint32_t)box_rows, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_last_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled"); return BMA_ERR_CUDA; }
+  return BMA_OK;
+}
+
 static bool tma_compatible(const bma_tensor& t) {
   return t.ptr && t.dtype == BMA_DTYPE_BF16 && (reinterpret_cast<uintptr_t>(t.ptr) & 15) == 0 &&
          t.stride_b % 8 == 0 && t.stride_l % 8 == 0 && t.stride_h % 8 == 0 && t.stride_b > 0 && t.stride_l > 0 &&
@@ -504,11 +557,16 @@ int sm100_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   BMA_REQUIRE((reinterpret_cast<uintptr_t>(a.o.ptr) & 15) == 0 && a.o.stride_b % 8 == 0 && a.o.stride_l % 8 == 0 &&
                   a.o.stride_h % 8 == 0,
               BMA_ERR_UNSUPPORTED);
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   int rc;
   if ((rc = make_tile_map_bf16(&mq, a.q.ptr, a.B, a.N, a.Hq, a.d, a.q.stride_b, a.q.stride_l, a.q.stride_h, BM))) return rc;
   if ((rc = make_tile_map_bf16(&mk, a.k.ptr, a.B, a.L, a.Hkv, a.d, a.k.stride_b, a.k.stride_l, a.k.stride_h, BN))) return rc;
   if ((rc = make_tile_map_bf16(&mv, a.v.ptr, a.B, a.L, a.Hkv, a.d, a.v.stride_b, a.v.stride_l, a.v.stride_h, BN))) return rc;
+  if (a.o.dtype == BMA_DTYPE_F32)
+    rc = make_tile_map_f32(&mo, a.o.ptr, a.B, a.N, a.Hq, a.d, a.o.stride_b, a.o.stride_l, a.o.stride_h, BM);
+  else
+    rc = make_tile_map_bf16(&mo, a.o.ptr, a.B, a.N, a.Hq, a.d, a.o.stride_b, a.o.stride_l, a.o.stride_h, BM);
+  if (rc) return rc;
   FwdParams p;
   p.a = a; p.spec = spec; p.l = lists;
   p.scale_log2 = a.scale * kLog2e;
@@ -519,11 +577,11 @@ int sm100_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   if (a.d == 128) {
     const size_t smem = sizeof(FwdSmem<128>);
     BMA_CUDA_TRY(cudaFuncSetAttribute(fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    fwd_kernel<128><<<grid, kThreads, smem, st>>>(mq, mk, mv, p);
+    fwd_kernel<128><<<grid, kThreads, smem, st>>>(mq, mk, mv, mo, p);
   } else {
     const size_t smem = sizeof(FwdSmem<64>);
     BMA_CUDA_TRY(cudaFuncSetAttribute(fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    fwd_kernel<64><<<grid, kThreads, smem, st>>>(mq, mk, mv, p);
+    fwd_kernel<64><<<grid, kThreads, smem, st>>>(mq, mk, mv, mo, p);
   }
   count_launches(1);
   BMA_CUDA_TRY(cudaGetLastError());

@@ -174,6 +174,24 @@ def test_bf16_configs(name):
     check(got, oracle(Q, K, V, dO, **kw), torch.bfloat16, name)
 
 
+@pytest.mark.parametrize("d", [128, 64])
+def test_bf16_output_option(d):
+    """out_dtype=torch.bfloat16 (the tensor-core kernel stores O through its other staging path):
+    equal to the float32 output rounded to bf16, ragged tail included; gradients unchanged in kind."""
+    B, N, L, H = 2, 333, 700, 2
+    Q = gen((B, N, H, d), 0, torch.bfloat16).cuda().requires_grad_(True)
+    K, V = (gen((B, L, H, d), i, torch.bfloat16).cuda().requires_grad_(True) for i in (1, 2))
+    kw = dict(mask_fn=M.sliding_window_mask(200, 30), block_size=64)
+    o32 = jm.masked_attention_via_map(Q, K, V, **kw)
+    o16 = jm.masked_attention_via_map(Q, K, V, out_dtype=torch.bfloat16, **kw)
+    assert o16.dtype == torch.bfloat16 and o16.shape == o32.shape
+    assert (o16.float() - o32).abs().max() <= 2 ** -8 * o32.abs().max().clamp(min=1.0)
+    o16.backward(torch.ones_like(o16))
+    g16 = Q.grad.clone(); Q.grad = None
+    o32.backward(torch.ones_like(o32))
+    assert torch.isfinite(g16).all() and (g16.float() - Q.grad.float()).abs().max() < 3e-2
+
+
 def test_simt_and_auto_backends_agree_bf16():
     """The exact-FP32 SIMT kernels cross-check whatever backend AUTO selects."""
     Q, K, V = (gen((1, 512, 2, 128), i, torch.bfloat16) for i in range(3))
