@@ -155,14 +155,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     return;
   }
 
-  int total = 0;  // q tiles this CTA visits
-  for (int g = 0; g < G; ++g) {
-    const int h = hk * G + g;
-    const int lb = p.l.B == 1 ? 0 : b, lh = p.l.H == 1 ? 0 : h;
-    const int64_t row = ((int64_t)lb * p.l.H + lh) * p.l.NKV + kj;
-    total += p.l.full_q_num[row] + p.l.q_num[row];
-  }
-
   if (threadIdx.x == 0) {
     for (int i = 0; i < NUM_BARS; ++i) {
       uint32_t count = 1;
@@ -171,6 +163,24 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_init(&sm.bar[i], count);
     }
     fence_barrier_init();
+    // K and V of this kv tile do not depend on the block lists: the same thread that initialised the
+    // barriers starts their loads at once, under the list reads and the TMEM allocation below
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+    mbar_expect_tx(&sm.bar[BAR_KV], 2 * kTileBytes);
+#pragma unroll
+    for (int box = 0; box < HD / 64; ++box) {
+      tma_load_4d(sm.k + box * kHalfTile, &map_k, &sm.bar[BAR_KV], box * 64, hk, k0, b);
+      tma_load_4d(sm.v + box * kHalfTile, &map_v, &sm.bar[BAR_KV], box * 64, hk, k0, b);
+    }
+  }
+
+  int total = 0;  // q tiles this CTA visits
+  for (int g = 0; g < G; ++g) {
+    const int h = hk * G + g;
+    const int lb = p.l.B == 1 ? 0 : b, lh = p.l.H == 1 ? 0 : h;
+    const int64_t row = ((int64_t)lb * p.l.H + lh) * p.l.NKV + kj;
+    total += p.l.full_q_num[row] + p.l.q_num[row];
   }
   if (warp == 8) {
     tmem_alloc(&sm.tmem_base, kTmemCols);
@@ -186,16 +196,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (warp == 8 && lane == 0 && total > 0) {
       // ---------------------------------------------------------------- TMA producer
       prefetch_tensormap(&map_q);
-      prefetch_tensormap(&map_k);
-      prefetch_tensormap(&map_v);
       prefetch_tensormap(&map_do);
       auto load_tile = [&](const CUtensorMap* m, uint8_t* dst, uint64_t* bar, int head, int row0) {
 #pragma unroll
         for (int box = 0; box < HD / 64; ++box) tma_load_4d(dst + box * kHalfTile, m, bar, box * 64, head, row0, b);
       };
-      mbar_expect_tx(&sm.bar[BAR_KV], 2 * kTileBytes);
-      load_tile(&map_k, sm.k, &sm.bar[BAR_KV], hk, k0);
-      load_tile(&map_v, sm.v, &sm.bar[BAR_KV], hk, k0);
       QTileIter loader(p.l, b, hk, G, kj);
       bool ok = true;
       for (int n = 0; n < total && ok; ++n) {
@@ -442,6 +447,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
     // ---- epilogue: dK (scaled) and dV of this kv tile
     if (ok && total > 0) ok = mbar_wait(&sm.bar[BAR_D], (total - 1) & 1);
+    if (ok && total == 0) ok = mbar_wait(&sm.bar[BAR_KV], 0);  // the K/V loads must land before their buffers are reused below
     if (!ok) {
       report_device_error(p.status, 320 + warp);
     } else {
