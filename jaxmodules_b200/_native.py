@@ -79,6 +79,7 @@ class AttnArgs(C.Structure):
         ("o", Tensor), ("lse", C.c_void_p),
         ("d_o", Tensor), ("delta", C.c_void_p),
         ("dq", Tensor), ("dk", Tensor), ("dv", Tensor),
+        ("key_bias", C.c_void_p),
     ]
 
 

@@ -96,13 +96,15 @@ def _tensor(t: Optional[torch.Tensor]) -> nat.Tensor:
     return out
 
 
-def _make_args(Q, K, V, backend=nat.BMA_BACKEND_AUTO, scale=None) -> nat.AttnArgs:
+def _make_args(Q, K, V, backend=nat.BMA_BACKEND_AUTO, scale=None, key_bias=None) -> nat.AttnArgs:
     a = nat.AttnArgs()
     a.B, a.N, a.Hq, a.d = Q.shape
     a.L, a.Hkv = K.shape[1], K.shape[2]
     a.scale = 1.0 / math.sqrt(K.shape[-1]) if scale is None else float(scale)
     a.backend = backend
     a.q, a.k, a.v = _tensor(Q), _tensor(K), _tensor(V)
+    if key_bias is not None:   # [Hq] float32 on the device, kept alive by the caller
+        a.key_bias = key_bias.data_ptr()
     return a
 
 
@@ -110,9 +112,9 @@ def _stream(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def plan(Q, K, V, backend=nat.BMA_BACKEND_AUTO, backward: bool = False):
+def plan(Q, K, V, backend=nat.BMA_BACKEND_AUTO, backward: bool = False, key_bias=None):
     """(backend, q_tile, kv_tile) the library will use for the forward (or backward) pass."""
-    a = _make_args(Q, K, V, backend)
+    a = _make_args(Q, K, V, backend, key_bias=key_bias)
     be, tq, tk = C.c_int32(), C.c_int32(), C.c_int32()
     fn = nat.lib().bma_attn_bwd_plan if backward else nat.lib().bma_attn_plan
     nat.check(fn(C.byref(a), C.byref(be), C.byref(tq), C.byref(tk)), "bma_attn_plan")
@@ -151,23 +153,24 @@ def set_profile_sink(sink):
 
 
 def attention_forward(Q, K, V, terms: _masks.MaskTerms, *, out_dtype=torch.float32, backend=nat.BMA_BACKEND_AUTO,
-                      need_q_side: bool = False, scale=None, lists_fn=None):
+                      need_q_side: bool = False, scale=None, lists_fn=None, key_bias=None):
     """One forward launch sequence: mask compile at the kernel's tile size, then attention.
     Returns (O, lse, ctx) where ctx carries what the backward needs.
 
     ``scale`` replaces 1/sqrt(d).  ``lists_fn(q_tile, kv_tile, q_side)`` supplies ready-made
     block lists (struct, tensors) instead of compiling them from the mask terms; it returns
-    None when it has none for that tile size."""
+    None when it has none for that tile size.  ``key_bias``: float32 ``[Hq]`` on the device, the
+    logits get ``+ key_bias[h] * k`` (see ``bma_attn_args.key_bias``)."""
     lib = nat.lib()
     dev = Q.device
     B, N, Hq, d = Q.shape
     L = K.shape[1]
     with torch.cuda.device(dev):
-        a = _make_args(Q, K, V, backend, scale)
-        be, tq, tk = plan(Q, K, V, backend)
+        a = _make_args(Q, K, V, backend, scale, key_bias)
+        be, tq, tk = plan(Q, K, V, backend, key_bias=key_bias)
         dmask = _masks.to_device_mask(terms, N, L, dev)
         # when the backward pass will walk the same tile size, build its q-side lists in the same launches
-        both_sides = need_q_side and plan(Q, K, V, backend, backward=True)[1:] == (tq, tk)
+        both_sides = need_q_side and plan(Q, K, V, backend, backward=True, key_bias=key_bias)[1:] == (tq, tk)
         with _Span(_profile_sink, "mask_compile", dev):
             ready = lists_fn(tq, tk, both_sides) if lists_fn is not None else None
             lists, lt = ready if ready is not None else compile_block_lists(dmask, B, Hq, N, L, tq, tk, dev, q_side=both_sides)
@@ -177,7 +180,7 @@ def attention_forward(Q, K, V, terms: _masks.MaskTerms, *, out_dtype=torch.float
         with _Span(_profile_sink, "fwd", dev):
             nat.check(lib.bma_attn_fwd(C.byref(a), C.byref(dmask.spec), C.byref(lists), _stream(dev)), "bma_attn_fwd")
     ctx = dict(dmask=dmask, lists=lists, list_tensors=lt, backend=be, scale=scale, lists_fn=lists_fn,
-               lists_tile=(tq, tk), lists_have_q_side=both_sides)
+               lists_tile=(tq, tk), lists_have_q_side=both_sides, key_bias=key_bias)
     return O, lse, ctx
 
 
@@ -188,8 +191,8 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
     B, N, Hq, d = Q.shape
     L = K.shape[1]
     with torch.cuda.device(dev):
-        a = _make_args(Q, K, V, backend, ctx.get("scale"))
-        be, tq, tk = plan(Q, K, V, backend, backward=True)
+        a = _make_args(Q, K, V, backend, ctx.get("scale"), ctx.get("key_bias"))
+        be, tq, tk = plan(Q, K, V, backend, backward=True, key_bias=ctx.get("key_bias"))
         with _Span(_profile_sink, "mask_compile_bwd", dev):
             if ctx.get("lists_have_q_side") and ctx.get("lists_tile") == (tq, tk):
                 lists, lt = ctx["lists"], ctx["list_tensors"]      # built by the forward pass
@@ -222,10 +225,10 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
 
 class _MaskedAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, Q, K, V, terms, out_dtype, backend, scale=None, lists_fn=None):
+    def forward(ctx, Q, K, V, terms, out_dtype, backend, scale=None, lists_fn=None, key_bias=None):
         need_grad = any(ctx.needs_input_grad[:3])
         O, lse, fctx = attention_forward(Q, K, V, terms, out_dtype=out_dtype, backend=backend, need_q_side=need_grad,
-                                         scale=scale, lists_fn=lists_fn)
+                                         scale=scale, lists_fn=lists_fn, key_bias=key_bias)
         ctx.save_for_backward(Q, K, V, O, lse)
         ctx.fctx, ctx.backend = fctx, backend
         ctx.mark_non_differentiable(lse)
@@ -235,7 +238,7 @@ class _MaskedAttention(torch.autograd.Function):
     def backward(ctx, dO, _dlse):
         Q, K, V, O, lse = ctx.saved_tensors
         dQ, dK, dV = attention_backward(Q, K, V, O, lse, dO, ctx.fctx, ctx.backend)
-        return dQ, dK, dV, None, None, None, None, None
+        return dQ, dK, dV, None, None, None, None, None, None
 
 
 def masked_attention_via_map(

@@ -127,6 +127,7 @@ __global__ void __launch_bounds__(NT) simt_fwd_kernel(const SimtParams p) {
   const int q0 = qi * TQ;
   const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
   const MaskView mv = make_mask_view(p.spec, b, h);
+  const float kb2 = p.a.key_bias ? __ldg(p.a.key_bias + h) * kLog2e : 0.f;  // per-head key bias in log2 units
   const ListRow lr = list_row<false>(p.l, b, h, qi);
 
   stage_natural<T, DP>(Qs, a.q, b, q0, h, a.N, a.d);
@@ -157,7 +158,7 @@ __global__ void __launch_bounds__(NT) simt_fwd_kernel(const SimtParams p) {
       mx[i] = -INFINITY;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        float v = s[i][j] * p.scale_log2;
+        float v = fmaf(s[i][j], p.scale_log2, kb2 * (float)(mv.k_offset + k0 + tx * 4 + j));
         if (partial && !mask_allowed(mv, q0 + ty * 4 + i, k0 + tx * 4 + j)) v = -INFINITY;
         s[i][j] = v;
         mx[i] = fmaxf(mx[i], v);
@@ -223,7 +224,7 @@ __global__ void __launch_bounds__(NT) simt_fwd_kernel(const SimtParams p) {
 // s[i][j] holds q.k on entry and p on exit; dp[i][j] holds dO.v on entry and ds on exit.
 __device__ __forceinline__ void softmax_grad_tile(float s[4][4], float dp[4][4], const float* lse2, const float* delta,
                                                   int ty, int tx, bool partial, const MaskView& mv, int q0, int k0,
-                                                  float scale_log2) {
+                                                  float scale_log2, float kb2) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const float l2 = lse2[ty * 4 + i], dl = delta[ty * 4 + i];
@@ -231,7 +232,7 @@ __device__ __forceinline__ void softmax_grad_tile(float s[4][4], float dp[4][4],
     for (int j = 0; j < 4; ++j) {
       bool ok = l2 != -INFINITY;
       if (partial) ok = ok && mask_allowed(mv, q0 + ty * 4 + i, k0 + tx * 4 + j);
-      const float pr = ok ? exp2f(s[i][j] * scale_log2 - l2) : 0.f;
+      const float pr = ok ? exp2f(fmaf(s[i][j], scale_log2, kb2 * (float)(mv.k_offset + k0 + tx * 4 + j)) - l2) : 0.f;
       s[i][j] = pr;
       dp[i][j] = pr * (dp[i][j] - dl);
     }
@@ -287,6 +288,7 @@ __global__ void __launch_bounds__(NT) simt_bwd_dkdv_kernel(const SimtParams p) {
   for (int g = 0; g < G; ++g) {
     const int h = hk * G + g;
     const MaskView mv = make_mask_view(p.spec, b, h);
+    const float kb2 = p.a.key_bias ? __ldg(p.a.key_bias + h) * kLog2e : 0.f;  // per-head key bias in log2 units
     const ListRow lr = list_row<true>(p.l, b, h, kj);
     const int ntiles = lr.nfull + lr.npart;
     for (int it = 0; it < ntiles; ++it) {
@@ -301,7 +303,7 @@ __global__ void __launch_bounds__(NT) simt_bwd_dkdv_kernel(const SimtParams p) {
       float s[4][4] = {}, dp[4][4] = {};
       tile_dot<DP>(Qs, Kt, ty, tx, s);
       tile_dot<DP>(dOs, Vt, ty, tx, dp);
-      softmax_grad_tile(s, dp, lse2, dlt, ty, tx, partial, mv, q0, k0, p.scale_log2);
+      softmax_grad_tile(s, dp, lse2, dlt, ty, tx, partial, mv, q0, k0, p.scale_log2, kb2);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         *reinterpret_cast<float4*>(Ps + (ty * 4 + i) * PS + tx * 4) = make_float4(s[i][0], s[i][1], s[i][2], s[i][3]);
@@ -362,6 +364,7 @@ __global__ void __launch_bounds__(NT) simt_bwd_dq_kernel(const SimtParams p) {
   const int q0 = qi * TQ;
   const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
   const MaskView mv = make_mask_view(p.spec, b, h);
+  const float kb2 = p.a.key_bias ? __ldg(p.a.key_bias + h) * kLog2e : 0.f;  // per-head key bias in log2 units
   const ListRow lr = list_row<false>(p.l, b, h, qi);
 
   stage_natural<T, DP>(Qs, a.q, b, q0, h, a.N, a.d);
@@ -387,7 +390,7 @@ __global__ void __launch_bounds__(NT) simt_bwd_dq_kernel(const SimtParams p) {
     float s[4][4] = {}, dp[4][4] = {};
     tile_dot<DP>(Qs, Kt, ty, tx, s);
     tile_dot<DP>(dOs, Vt, ty, tx, dp);
-    softmax_grad_tile(s, dp, lse2, dlt, ty, tx, partial, mv, q0, k0, p.scale_log2);
+    softmax_grad_tile(s, dp, lse2, dlt, ty, tx, partial, mv, q0, k0, p.scale_log2, kb2);
 #pragma unroll
     for (int i = 0; i < 4; ++i)
       *reinterpret_cast<float4*>(dSs + (ty * 4 + i) * PS + tx * 4) = make_float4(dp[i][0], dp[i][1], dp[i][2], dp[i][3]);

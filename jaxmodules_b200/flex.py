@@ -11,12 +11,13 @@ them as it is (route "lists").  Other block sizes take one of two routes:
 * "table"  — anything else: the element mask the reference would apply
   (``full_block | partial_block & mask_mod``) is evaluated once on the host into a bit table.
 
-Differences from the reference, all deliberate: ``score_mod`` is not implemented (it is an
-arbitrary traced function in the reference); a block that appears twice in a row's lists is
-visited once.  Like the reference (:615-622), a row whose listed blocks allow no key returns 0.
+Differences from the reference, all deliberate: ``score_mod`` is limited to the affine family
+``a * score + w[h] * k`` plus terms constant along k (ALiBi and relative-position biases); a block
+that appears twice in a row's lists is visited once.  Like the reference (:615-622), a row whose listed blocks allow no key returns 0.
 """
 from __future__ import annotations
 
+import math
 from typing import Callable, Optional
 
 import numpy as np
@@ -177,6 +178,43 @@ def flex_route(block_mask: Optional[BlockMask], B: int, Hq: int, tiles, device) 
     return "terms" if _lists_match_terms(block_mask, terms, B, Hq, device) else "table"
 
 
+def score_mod_affine(score_mod: Callable, B: int, Hq: int, L: int, S: int):
+    """(a, w) with ``score_mod(score, b, h, q, k) == a * score + w[h] * k + (terms constant along k)``.
+
+    Terms that do not vary with the key index cancel in the softmax, so such a score_mod — ALiBi
+    ``score + slope[h] * (k - q)``, the relative-position bias of the reference's
+    tests/test_attention.py:131-132 — is a logit scale ``a`` plus a per-head key bias ``w``,
+    which the kernels apply (``bma_attn_args.key_bias``).  The function is probed with Python
+    numbers on a few scores and index pairs per head; anything that is not of this form (not
+    affine in the score, not linear in k, or a key slope that depends on the batch index or the
+    query index) raises NotImplementedError."""
+    def f(s, b, h, q, k):
+        return float(score_mod(np.float64(s), b, h, q, k))
+    qs = sorted({0, L // 3, L - 1})
+    ks = sorted({0, S // 2, S - 1}) if S > 2 else list(range(S))
+    a_ref, w = None, np.zeros(Hq, dtype=np.float64)
+    for b in sorted({0, B - 1}):
+        for h in range(Hq):
+            base = f(0.0, b, h, qs[0], ks[0])
+            a = f(1.0, b, h, qs[0], ks[0]) - base
+            slope = (f(0.0, b, h, qs[0], ks[-1]) - base) / (ks[-1] - ks[0]) if len(ks) > 1 else 0.0
+            a_ref = a if a_ref is None else a_ref
+            for q in qs:
+                row0 = f(0.0, b, h, q, ks[0])
+                for k in ks:
+                    for sc in (-1.5, 0.0, 2.0):
+                        want = a_ref * sc + row0 + slope * (k - ks[0])
+                        if abs(f(sc, b, h, q, k) - want) > 1e-6 * (1.0 + abs(want)):
+                            raise NotImplementedError(
+                                "score_mod must be a * score + w[h] * k + (terms constant along k); other score "
+                                "modifications are not implemented on the CUDA path")
+            if b == 0:
+                w[h] = slope
+            elif abs(w[h] - slope) > 1e-6 * (1.0 + abs(slope)):
+                raise NotImplementedError("score_mod: the key slope must not depend on the batch index")
+    return float(a_ref), w
+
+
 def flex_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, score_mod: Optional[Callable] = None,
                    block_mask: Optional[BlockMask] = None, scale: Optional[float] = None, enable_gqa: bool = False,
                    return_lse: bool = False, *, out_dtype: Optional[torch.dtype] = None,
@@ -187,11 +225,11 @@ def flex_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, 
     last dimension; nothing is copied).  Returns ``[B, Hq, L, E]`` float32 like the reference
     (``out_dtype=torch.bfloat16`` halves the output traffic).  Differentiable in query, key and
     value.  Shape checks and their messages follow jaxmodules/attention.py:501-531;
-    ``return_lse`` raises NotImplementedError as there (:491-492)."""
+    ``return_lse`` raises NotImplementedError as there (:491-492).  ``score_mod``: functions of the form
+    ``a * score + w[h] * k_idx + (terms constant along k_idx)`` (see ``score_mod_affine``) run on the FP32
+    SIMT kernels; others raise NotImplementedError."""
     if return_lse:
         raise NotImplementedError("return_lse is not supported yet")
-    if score_mod is not None:
-        raise NotImplementedError("score_mod is not implemented on the CUDA path; express masking through block_mask")
     if query.ndim != 4 or key.ndim != 4 or value.ndim != 4:
         raise ValueError("query, key and value must be [B, H, L, E]")
     B, Hq, L, E = query.shape
@@ -215,6 +253,7 @@ def flex_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, 
     if block_mask is not None:
         if block_mask.B not in (1, B) or block_mask.H not in (1, Hq):
             raise ValueError("block_mask batch / head extents must be 1 or match the query")
+    affine = None if score_mod is None else score_mod_affine(score_mod, B, Hq, L, S)   # raises for other forms
     if not (query.is_cuda and key.is_cuda and value.is_cuda):
         raise RuntimeError("flex_attention needs CUDA tensors; there is no CPU path")
     if query.dtype not in (torch.float32, torch.bfloat16) or key.dtype != query.dtype or value.dtype != query.dtype:
@@ -224,13 +263,18 @@ def flex_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, 
     Q, K, V = fix(query).transpose(1, 2), fix(key).transpose(1, 2), fix(value).transpose(1, 2)
     dev = Q.device
     lists_fn = None
+    key_bias = None
+    if affine is not None:
+        scale = affine[0] * (1.0 / math.sqrt(E) if scale is None else float(scale))
+        if np.any(affine[1] != 0.0):
+            key_bias = torch.from_numpy(affine[1].astype(np.float32)).to(dev)
     with torch.cuda.device(dev):
         if block_mask is None:
             terms = _masks.MaskTerms()
         else:
-            tiles = [_att.plan(Q, K, V, backend)[1:]]
+            tiles = [_att.plan(Q, K, V, backend, key_bias=key_bias)[1:]]
             if torch.is_grad_enabled() and (query.requires_grad or key.requires_grad or value.requires_grad):
-                tiles.append(_att.plan(Q, K, V, backend, backward=True)[1:])
+                tiles.append(_att.plan(Q, K, V, backend, backward=True, key_bias=key_bias)[1:])
             route = flex_route(block_mask, B, Hq, tiles, dev)
             if route == "table":
                 terms = _masks.MaskTerms(bitmap=_effective_table(block_mask, Hq // Hkv, Hq))
@@ -239,5 +283,5 @@ def flex_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, 
                 if route == "lists":
                     lists_fn = _ReadyLists(block_mask, dev)
         O, _ = _att._MaskedAttention.apply(Q, K, V, terms, out_dtype or torch.float32, backend,
-                                           None if scale is None else float(scale), lists_fn)
+                                           None if scale is None else float(scale), lists_fn, key_bias)
     return O.transpose(1, 2)

@@ -34,7 +34,7 @@ def test_argument_checks_come_first():
     with pytest.raises(NotImplementedError):
         flex_attention(q, q, q, return_lse=True)
     with pytest.raises(NotImplementedError):
-        flex_attention(q, q, q, score_mod=lambda s, b, h, qi, ki: s)
+        flex_attention(q, q, q, score_mod=lambda s, b, h, qi, ki: s * s)
     with pytest.raises(AssertionError, match="same sequence length"):
         flex_attention(q, q, q[:, :, :7])
     with pytest.raises(AssertionError, match="enable_gqa"):
@@ -103,3 +103,18 @@ def test_route_without_structure_is_table():
     seg = M.document_mask(np.zeros((2, 256), dtype=np.int32))
     bm.mask_mod = seg
     assert flex_route(bm, 2, 1, [(128, 128)], "cpu") == "table"    # batch-broadcast lists, per-batch mask
+
+
+def test_score_mod_affine_family():
+    """score_mod = a * score + w[h] * k + (constant along k) is recognised by probing; the rest is refused."""
+    from jaxmodules_b200.flex import score_mod_affine
+    a, w = score_mod_affine(lambda s, b, h, q, k: s + 0.1 * (q - k), 2, 4, 8, 8)       # tests/test_attention.py:131-132
+    assert a == pytest.approx(1.0) and np.allclose(w, -0.1)
+    slopes = np.array([0.5, 0.25, 0.125, 0.0625])
+    a, w = score_mod_affine(lambda s, b, h, q, k: 2 * s + slopes[h] * (k - q) + b, 2, 4, 64, 64)   # ALiBi with a batch offset
+    assert a == pytest.approx(2.0) and np.allclose(w, slopes)
+    for bad in (lambda s, b, h, q, k: s * s, lambda s, b, h, q, k: s + 0.01 * k * k,
+                lambda s, b, h, q, k: s + 0.1 * b * k, lambda s, b, h, q, k: s + 0.01 * q * k,
+                lambda s, b, h, q, k: np.tanh(s)):
+        with pytest.raises(NotImplementedError):
+            score_mod_affine(bad, 2, 2, 16, 16)
