@@ -122,8 +122,7 @@ typedef struct bma_attn_args {
   bma_tensor dq, dk, dv;   /* outputs (bwd), dtype of q/k/v                      */
   const float* key_bias;   /* [Hq] or null: logits get + key_bias[h] * k (k = global key index incl. the mask's
                               k_offset) before the softmax -- the part of an affine score_mod
-                              (jaxmodules/attention.py:543-554), e.g. ALiBi, that does not cancel in the softmax.
-                              Runs on the FP32 SIMT kernels only (bma_attn_plan reports that backend). */
+                              (jaxmodules/attention.py:543-554), e.g. ALiBi, that does not cancel in the softmax. */
 } bma_attn_args;
 
 enum { BMA_BACKEND_AUTO = 0, BMA_BACKEND_SIMT = 1, BMA_BACKEND_TCGEN05 = 2 };

@@ -81,7 +81,7 @@ __device__ __forceinline__ void row_interval(const MaskView& m, int q, int k0, i
   jhi = min(hi - m.k_offset, m.k_valid - 1) - k0;
 }
 
-template <int HD>
+template <int HD, bool KB>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -270,6 +270,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tmem_sd = tmem + x * 128 + lane_base, tmem_dq = tmem + 256 + x * 128 + lane_base;
     const MaskView mv = make_mask_view(p.spec, b, h);
+    const float kb2 = KB ? __ldg(a.key_bias + h) * kLog2e : 0.f;  // per-head key bias, log2 units
     float lse2 = INFINITY, delta = 0.f;  // +inf: rows outside the tensor or without any key get P = 0
     if (qi < NQ && q < a.N) {
       const int64_t off = ((int64_t)b * a.Hq + h) * a.N + q;
@@ -298,6 +299,16 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(&sm.bar[BAR_LS0 + x]);  // dO V^T may overwrite the columns now
+if constexpr (KB) {  // key bias: + kb2 * (global key index) on every column
+          const float base = fmaf(kb2, (float)(mv.k_offset + k0), -lse2);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            pr[j] = ex2(fmaf(__uint_as_float(r0[j]), p.scale_log2, fmaf((float)j, kb2, base)));
+            pr[32 + j] = ex2(fmaf(__uint_as_float(r1[j]), p.scale_log2, fmaf((float)(32 + j), kb2, base)));
+            pr[64 + j] = ex2(fmaf(__uint_as_float(r2[j]), p.scale_log2, fmaf((float)(64 + j), kb2, base)));
+            pr[96 + j] = ex2(fmaf(__uint_as_float(r3[j]), p.scale_log2, fmaf((float)(96 + j), kb2, base)));
+          }
+        } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           pr[j] = ex2(fmaf(__uint_as_float(r0[j]), p.scale_log2, -lse2));
@@ -308,6 +319,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 #else
           pr[96 + j] = ex2(fmaf(__uint_as_float(r3[j]), p.scale_log2, -lse2));
 #endif
+        }
         }
       }
       if (cls == 1) {
@@ -426,15 +438,14 @@ int sm100_bwd_dq(const bma_attn_args& a, const bma_mask_spec& spec, const bma_bl
   BMA_REQUIRE(p.status != nullptr, BMA_ERR_CUDA);
 
   dim3 grid(ceil_div(ceil_div(a.N, BM), 2), a.Hq, a.B);
-  if (a.d == 128) {
-    const size_t smem = sizeof(DqSmem<128>);
-    BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    bwd_dq_kernel<128><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, mdq, p);
-  } else {
-    const size_t smem = sizeof(DqSmem<64>);
-    BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    bwd_dq_kernel<64><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, mdq, p);
-  }
+  auto launch = [&](auto kernel, size_t smem) -> int {
+    BMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, mdq, p);
+    return BMA_OK;
+  };
+  if (a.d == 128) rc = a.key_bias ? launch(bwd_dq_kernel<128, true>, sizeof(DqSmem<128>)) : launch(bwd_dq_kernel<128, false>, sizeof(DqSmem<128>));
+  else rc = a.key_bias ? launch(bwd_dq_kernel<64, true>, sizeof(DqSmem<64>)) : launch(bwd_dq_kernel<64, false>, sizeof(DqSmem<64>));
+  if (rc) return rc;
   count_launches(1);
   BMA_CUDA_TRY(cudaGetLastError());
   return BMA_OK;

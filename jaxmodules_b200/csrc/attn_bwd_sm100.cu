@@ -134,7 +134,7 @@ struct QTileIter {  // flattened walk over (group head, listed q tile)
   }
 };
 
-template <int HD>
+template <int HD, bool KB>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -320,6 +320,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     auto exp_phase = [&](int n, int h_, int qi_, bool partial_) -> bool {
       const int st = n & 1;
       const int q0 = qi_ * BT;
+      // per-head key bias times this thread's global key index, in log2 units (0 without a bias)
+      const float kbk = KB ? __ldg(a.key_bias + h_) * kLog2e * (float)(p.spec.k_offset + k) : 0.f;
       uint32_t bits[2] = {0xffffffffu, 0xffffffffu};
       if (partial_) {
         const MaskView mv = make_mask_view(p.spec, b, h_);
@@ -353,7 +355,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       for (int j4 = 0; j4 < 8; ++j4) {
         const float4 la = *reinterpret_cast<const float4*>(&sm.lse2[st][(half * 2) * 32 + j4 * 4]);
         const float4 lb = *reinterpret_cast<const float4*>(&sm.lse2[st][(half * 2 + 1) * 32 + j4 * 4]);
-        const float lav[4] = {la.x, la.y, la.z, la.w}, lbv[4] = {lb.x, lb.y, lb.z, lb.w};
+        float lav[4] = {la.x, la.y, la.z, la.w}, lbv[4] = {lb.x, lb.y, lb.z, lb.w};
+        if constexpr (KB) {  // key bias of this thread's key row: the same shift for every query column
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { lav[e] -= kbk; lbv[e] -= kbk; }
+        }
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int j = j4 * 4 + e;
@@ -543,15 +549,14 @@ int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   p.status = device_status_ptr();
   BMA_REQUIRE(p.status != nullptr, BMA_ERR_CUDA);
   dim3 grid(ceil_div(a.L, BT), a.Hkv, a.B);
-  if (a.d == 128) {
-    const size_t smem = sizeof(BwdSmem<128>);
-    BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dkdv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    bwd_dkdv_kernel<128><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
-  } else {
-    const size_t smem = sizeof(BwdSmem<64>);
-    BMA_CUDA_TRY(cudaFuncSetAttribute(bwd_dkdv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    bwd_dkdv_kernel<64><<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
-  }
+  auto launch = [&](auto kernel, size_t smem) -> int {
+    BMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
+    return BMA_OK;
+  };
+  if (a.d == 128) rc = a.key_bias ? launch(bwd_dkdv_kernel<128, true>, sizeof(BwdSmem<128>)) : launch(bwd_dkdv_kernel<128, false>, sizeof(BwdSmem<128>));
+  else rc = a.key_bias ? launch(bwd_dkdv_kernel<64, true>, sizeof(BwdSmem<64>)) : launch(bwd_dkdv_kernel<64, false>, sizeof(BwdSmem<64>));
+  if (rc) return rc;
   count_launches(1);
   BMA_CUDA_TRY(cudaGetLastError());
   return sm100_bwd_dq(a, spec, lists, st);

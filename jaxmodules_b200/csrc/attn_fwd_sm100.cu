@@ -92,7 +92,8 @@ __device__ __forceinline__ void row_interval(const MaskView& m, int q, int k0, i
   jhi = min(hi - m.k_offset, m.k_valid - 1) - k0;
 }
 
-template <int HD>
+// KB: the per-head key bias (bma_attn_args.key_bias) is compiled in only where it is used
+template <int HD, bool KB>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, const FwdParams p) {
@@ -272,6 +273,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tmem_s = tmem + x * 128 + lane_base, tmem_o = tmem + 256 + x * 128 + lane_base;
     const MaskView mv = make_mask_view(p.spec, b, h);
+    const float kb2 = KB ? __ldg(a.key_bias + h) * kLog2e : 0.f;  // per-head key bias, log2 units
     float m_ref = -INFINITY;  // reference max (log2 domain) the exponentials are taken against
     float l = 0.f;
     bool ok = true;
@@ -301,6 +303,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           s[96 + j] = __uint_as_float(r3[j]);
         }
       }
+      const float sc = KB ? 1.f : p.scale_log2;
+      if constexpr (KB) {  // key bias: fold the scale and kb2 * (global key index) into the scores once
+        const float base = kb2 * (float)(mv.k_offset + k0);
+#pragma unroll
+        for (int j = 0; j < BN; ++j) s[j] = fmaf(s[j], p.scale_log2, fmaf((float)j, kb2, base));
+      }
       if (cls == 1) {  // partial tile: masked scores become -inf (their exponential is exactly 0)
         uint32_t bits[4];
         {
@@ -329,7 +337,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         mx3 = max3(mx3, s[j + 6], s[j + 7]);
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      const float m_cand = fmaxf(m_ref, mx * p.scale_log2);
+      const float m_cand = fmaxf(m_ref, mx * sc);
       // lazy rescale: keep the old reference unless the maximum grew by more than 2^threshold
       const bool grow = (m_cand - m_ref) > kRescaleThreshold;  // also true when m_ref == -inf and m_cand is finite
       float alpha = 1.f;
@@ -359,17 +367,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         uint32_t pk[32];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          const float e0 = ex2(fmaf(s[c * 64 + 2 * j], p.scale_log2, -m_sub));
-          const float e1 = ex2(fmaf(s[c * 64 + 2 * j + 1], p.scale_log2, -m_sub));
+          const float e0 = ex2(fmaf(s[c * 64 + 2 * j], sc, -m_sub));
+          const float e1 = ex2(fmaf(s[c * 64 + 2 * j + 1], sc, -m_sub));
 #if BMA_FWD_POLY >= 2
-          const float e2 = exp2_fma(fmaf(s[c * 64 + 2 * j + 2], p.scale_log2, -m_sub));
+          const float e2 = exp2_fma(fmaf(s[c * 64 + 2 * j + 2], sc, -m_sub));
 #else
-          const float e2 = ex2(fmaf(s[c * 64 + 2 * j + 2], p.scale_log2, -m_sub));
+          const float e2 = ex2(fmaf(s[c * 64 + 2 * j + 2], sc, -m_sub));
 #endif
 #if BMA_FWD_POLY >= 1
-          const float e3 = exp2_fma(fmaf(s[c * 64 + 2 * j + 3], p.scale_log2, -m_sub));
+          const float e3 = exp2_fma(fmaf(s[c * 64 + 2 * j + 3], sc, -m_sub));
 #else
-          const float e3 = ex2(fmaf(s[c * 64 + 2 * j + 3], p.scale_log2, -m_sub));
+          const float e3 = ex2(fmaf(s[c * 64 + 2 * j + 3], sc, -m_sub));
 #endif
           rs0 += e0; rs1 += e1; rs2 += e2; rs3 += e3;
           pk[j] = pack_bf16(e0, e1);
@@ -574,15 +582,14 @@ int sm100_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   p.status = device_status_ptr();
   BMA_REQUIRE(p.status != nullptr, BMA_ERR_CUDA);
   dim3 grid(ceil_div(ceil_div(a.N, BM), 2), a.Hq, a.B);
-  if (a.d == 128) {
-    const size_t smem = sizeof(FwdSmem<128>);
-    BMA_CUDA_TRY(cudaFuncSetAttribute(fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    fwd_kernel<128><<<grid, kThreads, smem, st>>>(mq, mk, mv, mo, p);
-  } else {
-    const size_t smem = sizeof(FwdSmem<64>);
-    BMA_CUDA_TRY(cudaFuncSetAttribute(fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    fwd_kernel<64><<<grid, kThreads, smem, st>>>(mq, mk, mv, mo, p);
-  }
+  auto launch = [&](auto kernel, size_t smem) -> int {
+    BMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<grid, kThreads, smem, st>>>(mq, mk, mv, mo, p);
+    return BMA_OK;
+  };
+  if (a.d == 128) rc = a.key_bias ? launch(fwd_kernel<128, true>, sizeof(FwdSmem<128>)) : launch(fwd_kernel<128, false>, sizeof(FwdSmem<128>));
+  else rc = a.key_bias ? launch(fwd_kernel<64, true>, sizeof(FwdSmem<64>)) : launch(fwd_kernel<64, false>, sizeof(FwdSmem<64>));
+  if (rc) return rc;
   count_launches(1);
   BMA_CUDA_TRY(cudaGetLastError());
   return BMA_OK;

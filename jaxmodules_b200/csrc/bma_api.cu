@@ -213,7 +213,6 @@ int validate_lists(const bma_attn_args* a, const bma_block_lists* l, int tile, b
 
 int pick_backend(const bma_attn_args* a) {
   if (a->backend == BMA_BACKEND_SIMT) return BMA_BACKEND_SIMT;
-  if (a->key_bias) return a->backend == BMA_BACKEND_TCGEN05 ? -1 : BMA_BACKEND_SIMT;  // the key bias exists on the SIMT kernels only
   if (sm100_supported(*a)) return BMA_BACKEND_TCGEN05;
   if (a->backend == BMA_BACKEND_TCGEN05) return -1;
   return BMA_BACKEND_SIMT;
@@ -221,7 +220,6 @@ int pick_backend(const bma_attn_args* a) {
 
 int pick_backend_bwd(const bma_attn_args* a) {
   if (a->backend == BMA_BACKEND_SIMT) return BMA_BACKEND_SIMT;
-  if (a->key_bias) return a->backend == BMA_BACKEND_TCGEN05 ? -1 : BMA_BACKEND_SIMT;
   if (sm100_bwd_supported(*a)) return BMA_BACKEND_TCGEN05;
   if (a->backend == BMA_BACKEND_TCGEN05) return -1;
   return BMA_BACKEND_SIMT;

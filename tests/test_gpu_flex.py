@@ -104,22 +104,23 @@ def test_score_mod_affine():
     q, k, v = qkv(11)
     rel = lambda score, b, h, qi, ki: score + 0.1 * (qi - ki)
     close(flex_attention(q, k, v, score_mod=rel), flex_attention_oracle(q, k, v, score_mod=rel))
-    b, h, l, e = 2, 4, 128, 32
-    q, k, v = qkv(12, hq=h, hkv=h, l=l, e=e, b=b)
-    slopes = [2.0 ** -(i + 1) for i in range(h)]
-    alibi = lambda score, b_, h_, qi, ki: score + slopes[h_] * (ki - qi)
-    bm = jm.create_block_mask(M.causal_mask(), 1, 1, l, l, 64)
-    d_out = torch.randn(b, h, l, e, generator=torch.Generator().manual_seed(3)).cuda()
-    got = run_with_grads(q, k, v, d_out, block_mask=bm, score_mod=alibi)
-    qd, kd, vd = (t.double().cpu().requires_grad_(True) for t in (q, k, v))
-    idx = torch.arange(l, dtype=torch.float64)
-    bias = torch.tensor(slopes, dtype=torch.float64)[None, :, None, None] * (idx[None, None, None, :] - idx[None, None, :, None])
-    s = qd @ kd.transpose(-1, -2) / math.sqrt(e) + bias
-    s = s.masked_fill(~torch.tril(torch.ones(l, l, dtype=torch.bool)), -math.inf)
-    ref = torch.softmax(s, dim=-1) @ vd
-    ref.backward(d_out.double().cpu())
-    for x, r in zip(got, (ref.detach(), qd.grad, kd.grad, vd.grad)):
-        close(x, r)
+    for dtype, e, l, block in ((torch.float32, 32, 128, 64), (torch.bfloat16, 128, 384, 128), (torch.bfloat16, 64, 384, 128)):
+        b, h = 2, 4
+        q, k, v = qkv(12, hq=h, hkv=h, l=l, e=e, b=b, dtype=dtype)
+        slopes = [2.0 ** -(i + 3) for i in range(h)]
+        alibi = lambda score, b_, h_, qi, ki: score + slopes[h_] * (ki - qi)
+        bm = jm.create_block_mask(M.causal_mask(), 1, 1, l, l, block)
+        d_out = torch.randn(b, h, l, e, generator=torch.Generator().manual_seed(3)).cuda()
+        got = run_with_grads(q, k, v, d_out, block_mask=bm, score_mod=alibi)
+        qd, kd, vd = (t.double().cpu().requires_grad_(True) for t in (q, k, v))
+        idx = torch.arange(l, dtype=torch.float64)
+        bias = torch.tensor(slopes, dtype=torch.float64)[None, :, None, None] * (idx[None, None, None, :] - idx[None, None, :, None])
+        s = qd @ kd.transpose(-1, -2) / math.sqrt(e) + bias
+        s = s.masked_fill(~torch.tril(torch.ones(l, l, dtype=torch.bool)), -math.inf)
+        ref = torch.softmax(s, dim=-1) @ vd
+        ref.backward(d_out.double().cpu())
+        for x, r in zip(got, (ref.detach(), qd.grad, kd.grad, vd.grad)):
+            close(x, r, dtype)
 
 
 def dense_reference_grads(q, k, v, dense, d_out, scale=None):
