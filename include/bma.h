@@ -64,7 +64,13 @@ enum {
   BMA_MASK_BAND = 2,
   BMA_MASK_BLOCK_WINDOW = 4,
   BMA_MASK_SEGMENT = 8,
-  BMA_MASK_BITMAP = 16
+  BMA_MASK_BITMAP = 16,
+  /* Not a mask term but a request to bma_mask_compile: segment-id blocks that the per-block id ranges
+   * cannot decide are reported PARTIAL without scanning their elements.  The lists then may name a block
+   * whose exact class is empty (never the reverse, and full blocks stay exact), which is harmless for the
+   * attention kernels -- they evaluate the predicate on every partial block -- and saves the scan.
+   * create_block_mask never sets it: its arrays are exact (jaxmodules/block_mask.py:471-481). */
+  BMA_MASK_COMPILE_CONSERVATIVE = 256
 };
 
 typedef struct bma_mask_spec {

@@ -16,6 +16,7 @@ BMA_ERR_ARG, BMA_ERR_UNSUPPORTED, BMA_ERR_WORKSPACE, BMA_ERR_CUDA, BMA_ERR_LIMIT
 BMA_ERR_DEVICE_CHECK = 1
 BMA_DTYPE_F32, BMA_DTYPE_BF16 = 0, 1
 BMA_MASK_CAUSAL, BMA_MASK_BAND, BMA_MASK_BLOCK_WINDOW, BMA_MASK_SEGMENT, BMA_MASK_BITMAP = 1, 2, 4, 8, 16
+BMA_MASK_COMPILE_CONSERVATIVE = 256
 BMA_BACKEND_AUTO, BMA_BACKEND_SIMT, BMA_BACKEND_TCGEN05 = 0, 1, 2
 
 

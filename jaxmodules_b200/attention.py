@@ -173,7 +173,7 @@ def attention_forward(Q, K, V, terms: _masks.MaskTerms, *, out_dtype=torch.float
         both_sides = need_q_side and plan(Q, K, V, backend, backward=True, key_bias=key_bias)[1:] == (tq, tk)
         with _Span(_profile_sink, "mask_compile", dev):
             ready = lists_fn(tq, tk, both_sides) if lists_fn is not None else None
-            lists, lt = ready if ready is not None else compile_block_lists(dmask, B, Hq, N, L, tq, tk, dev, q_side=both_sides)
+            lists, lt = ready if ready is not None else compile_block_lists(dmask, B, Hq, N, L, tq, tk, dev, q_side=both_sides, conservative=True)
         O = torch.empty((B, N, Hq, d), dtype=out_dtype, device=dev)
         lse = torch.empty((B, Hq, N), dtype=torch.float32, device=dev)
         a.o, a.lse = _tensor(O), lse.data_ptr()
@@ -199,7 +199,7 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
             else:
                 lists_fn = ctx.get("lists_fn")
                 ready = lists_fn(tq, tk, True) if lists_fn is not None else None
-                lists, lt = ready if ready is not None else compile_block_lists(ctx["dmask"], B, Hq, N, L, tq, tk, dev, q_side=True)
+                lists, lt = ready if ready is not None else compile_block_lists(ctx["dmask"], B, Hq, N, L, tq, tk, dev, q_side=True, conservative=True)
         if dO.stride(-1) != 1:
             dO = dO.contiguous()
         delta = torch.empty((B, Hq, N), dtype=torch.float32, device=dev)

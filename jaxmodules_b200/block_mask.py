@@ -235,13 +235,15 @@ def get_dense_from_kv_blocks(B, H, NUM_Q_BLOCKS, NUM_KV_BLOCKS, kv_num_blocks, k
 
 def compile_block_lists(dmask: "_masks.DeviceMask", B: int, H: int, N: int, L: int, q_block: int, kv_block: int,
                         device, *, out_B: Optional[int] = None, out_H: Optional[int] = None, q_side: bool = True,
-                        floor_blocks: bool = False, stream=None):
+                        floor_blocks: bool = False, stream=None, conservative: bool = False):
     """Runs ``bma_mask_compile`` and returns (lists struct, dict of tensors).
 
     ``floor_blocks`` reproduces create_block_mask's ``LEN // BLOCK`` block counts
     (jaxmodules/block_mask.py:468-469); the attention kernels use ceil so that ragged tails
     are covered.  out_B/out_H default to the smallest extents the mask allows (1 where it does
-    not depend on the index)."""
+    not depend on the index).  ``conservative`` sets BMA_MASK_COMPILE_CONSERVATIVE: segment-id blocks
+    that the per-block id ranges cannot decide are listed as partial without an element scan — fine
+    for lists the attention kernels consume, never used for the arrays ``create_block_mask`` returns."""
     lib = nat.lib()
     if floor_blocks:
         NQ, NKV = N // q_block, L // kv_block
@@ -252,9 +254,12 @@ def compile_block_lists(dmask: "_masks.DeviceMask", B: int, H: int, N: int, L: i
     LB = out_B if out_B is not None else (B if dmask.depends_b else 1)
     LH = out_H if out_H is not None else (H if dmask.depends_h else 1)
     spec = dmask.spec
-    if floor_blocks:
+    if floor_blocks or conservative:
         spec = nat.MaskSpec.from_buffer_copy(spec)
+    if floor_blocks:
         spec.q_valid, spec.k_valid = min(spec.q_valid, NQ * q_block), min(spec.k_valid, NKV * kv_block)
+    if conservative:
+        spec.flags |= nat.BMA_MASK_COMPILE_CONSERVATIVE
     i32 = dict(dtype=torch.int32, device=device)
     t = dict(
         kv_num_blocks=torch.empty((LB, LH, NQ), **i32), kv_indices=torch.empty((LB, LH, NQ, NKV), **i32),

@@ -122,7 +122,10 @@ __global__ void classify_kernel(bma_mask_spec spec, int CB, int CH, int NQ, int 
       const int qmn = seg.qmin[(int64_t)cb * NQ + qi], qmx = seg.qmax[(int64_t)cb * NQ + qi];
       const int kmn = seg.kmin[(int64_t)cb * NKV + kj], kmx = seg.kmax[(int64_t)cb * NKV + kj];
       if (qmx < kmn || qmn > kmx) { any = false; all = false; }          // ids never meet
-      else if (!(qmn == qmx && kmn == kmx && qmn == kmn)) scan = true;      // a boundary crosses the block
+      else if (!(qmn == qmx && kmn == kmx && qmn == kmn)) {                 // a boundary crosses the block
+        if (spec.flags & BMA_MASK_COMPILE_CONSERVATIVE) all = false;        // "partial" without looking closer
+        else scan = true;
+      }
     }
     if (decided && any && (spec.flags & BMA_MASK_BITMAP)) scan = true;
 

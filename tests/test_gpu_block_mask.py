@@ -112,3 +112,26 @@ def test_properties_at_long_context():
     rows = bm.full_kv_indices[0, 1]
     assert torch.equal(rows[n - 1, : n - 1], ar[: n - 1]) and int(rows[n - 1, n - 1]) == n - 1
     assert torch.equal(bm.full_q_indices[0, 0, 0, : n - 1], ar[1:])
+
+
+def test_conservative_lists_cover_the_exact_ones():
+    """BMA_MASK_COMPILE_CONSERVATIVE (used for the lists the attention kernels walk): full blocks are
+    exact, every exactly-partial block is listed, and the only extra entries are undecided segment blocks."""
+    from jaxmodules_b200.block_mask import compile_block_lists, get_dense_from_kv_blocks
+    rng = np.random.default_rng(0)
+    B, H, L, blk = 2, 1, 2048, 128
+    seg = np.sort(rng.integers(0, 9, size=(B, L)), axis=1).astype(np.int32)
+    for causal in (False, True):
+        terms = M.document_mask(seg, causal=causal).terms
+        dmask = M.to_device_mask(terms, L, L, "cuda")
+        dense = {}
+        for mode in (False, True):
+            _, t = compile_block_lists(dmask, B, H, L, L, blk, blk, "cuda", q_side=False, conservative=mode)
+            n = L // blk
+            dense[mode] = (get_dense_from_kv_blocks(t["kv_num_blocks"].shape[0], 1, n, n, t["full_kv_num_blocks"], t["full_kv_indices"]),
+                           get_dense_from_kv_blocks(t["kv_num_blocks"].shape[0], 1, n, n, t["kv_num_blocks"], t["kv_indices"]))
+        (full_e, part_e), (full_c, part_c) = dense[False], dense[True]
+        assert torch.equal(full_e, full_c)
+        assert bool((part_c | ~part_e).all())            # exact partial blocks are a subset
+        extra = part_c & ~part_e
+        assert int(extra.sum()) < int(part_e.sum())      # and only a few undecided blocks are added
