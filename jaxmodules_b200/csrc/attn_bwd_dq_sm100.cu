@@ -94,7 +94,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest causal tiles first
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (a.Hq / a.Hkv);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;  // provably warp-uniform
   const int wg = warp >> 2;
   const int NQ = p.l.NQ, NKV = p.l.NKV;
 
@@ -187,24 +187,30 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         load_tile(&map_v, sm.v, &sm.bar[BAR_V_FULL], hk, row0);
       }
       if (!ok) report_device_error(p.status, 410);
-    } else if (warp == 9 && lane == 0 && T > 0) {
-      // ---------------------------------------------------------------- MMA issuer
+    } else if (warp == 9 && T > 0) {
+      // ---------------------------------------------------------------- MMA issuer: the whole warp runs the loop
+      // (warp-uniform control flow and descriptors), one elected lane issues the tcgen05 instructions.  A loop run
+      // by lane 0 alone costs ~60-70 cycles of issue per MMA under load — no slack against the 64 cycles an MMA takes.
+      const bool leader = elect_one();
       constexpr uint32_t idesc_kk = make_idesc_bf16(BM, BN, 0, 0);
       constexpr uint32_t idesc_kn = make_idesc_bf16(BM, HD, 0, 1);
-      const uint32_t q_addr[2] = {smem_u32(sm.q[0]), smem_u32(sm.q[1])};
-      const uint32_t do_addr[2] = {smem_u32(sm.d_o[0]), smem_u32(sm.d_o[1])};
-      const uint32_t k_addr[2] = {smem_u32(sm.k[0]), smem_u32(sm.k[1])};
-      const uint32_t v_addr = smem_u32(sm.v);
-      int cnt[2] = {0, 0};  // tiles of x already folded into dQ_x (phase counter of the per-tile barriers)
+      // descriptors are built once; per MMA only the 16-byte-unit start address moves
+      const uint64_t dq0 = make_smem_desc(smem_u32(sm.q[0]), 16, 1024), dq1 = make_smem_desc(smem_u32(sm.q[1]), 16, 1024);
+      const uint64_t ddo0 = make_smem_desc(smem_u32(sm.d_o[0]), 16, 1024), ddo1 = make_smem_desc(smem_u32(sm.d_o[1]), 16, 1024);
+      const uint64_t dk0 = make_smem_desc(smem_u32(sm.k[0]), 16, 1024);            // K-major (S = Q K^T)
+      const uint64_t dkm0 = make_smem_desc(smem_u32(sm.k[0]), kHalfTile, 1024);    // MN-major (dQ += dS K)
+      const uint64_t dv = make_smem_desc(smem_u32(sm.v), 16, 1024);
+      constexpr uint32_t kStageUnits = kTileBytes >> 4;
+      int cnt0 = 0, cnt1 = 0;  // tiles of x already folded into dQ_x (phase counter of the per-tile barriers)
       bool ok = mbar_wait(&sm.bar[BAR_Q], 0);
 
       auto issue_s = [&](int x, int st) {  // S_x = Q_x K^T
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * kHalfTile + (ks & 3) * 32;
-          mma_ss(tmem + x * 128, make_smem_desc(q_addr[x] + off, 16, 1024), make_smem_desc(k_addr[st] + off, 16, 1024), idesc_kk, ks > 0);
+          const uint32_t off = ((ks >> 2) * kHalfTile + (ks & 3) * 32) >> 4;
+          if (leader) mma_ss(tmem + x * 128, (x == 0 ? dq0 : dq1) + off, dk0 + (uint32_t)(st * kStageUnits + off), idesc_kk, ks > 0);
         }
-        mma_commit(&sm.bar[BAR_S0 + x]);
+        if (leader) mma_commit(&sm.bar[BAR_S0 + x]);
       };
       if (ok) ok = mbar_wait(&sm.bar[BAR_K_FULL0], 0);
       if (ok) {
@@ -223,18 +229,18 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (!((e >> (12 + 2 * x)) & 3u)) continue;
-          ok = mbar_wait(&sm.bar[BAR_LS0 + x], cnt[x] & 1);
+          ok = mbar_wait(&sm.bar[BAR_LS0 + x], (x == 0 ? cnt0 : cnt1) & 1);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < HD / 16; ++ks) {
-            const uint32_t off = (ks >> 2) * kHalfTile + (ks & 3) * 32;
-            mma_ss(tmem + x * 128, make_smem_desc(do_addr[x] + off, 16, 1024), make_smem_desc(v_addr + off, 16, 1024), idesc_kk, ks > 0);
+            const uint32_t off = ((ks >> 2) * kHalfTile + (ks & 3) * 32) >> 4;
+            if (leader) mma_ss(tmem + x * 128, (x == 0 ? ddo0 : ddo1) + off, dv + off, idesc_kk, ks > 0);
           }
-          mma_commit(&sm.bar[BAR_DP0 + x]);
+          if (leader) mma_commit(&sm.bar[BAR_DP0 + x]);
         }
         if (!ok) break;
-        mma_commit(&sm.bar[BAR_V_FREE]);
+        if (leader) mma_commit(&sm.bar[BAR_V_FREE]);
         if (n + 1 < T) {
           ok = mbar_wait(&sm.bar[BAR_K_FULL0 + (st ^ 1)], ((n + 1) >> 1) & 1);
           if (!ok) break;
@@ -243,22 +249,24 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if ((e >> (12 + 2 * x)) & 3u) {
-            ok = mbar_wait(&sm.bar[BAR_DS0 + x], cnt[x] & 1);
+            int& cnt = x == 0 ? cnt0 : cnt1;
+            ok = mbar_wait(&sm.bar[BAR_DS0 + x], cnt & 1);
             if (!ok) break;
             tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < BN / 16; ++ks)
-              mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, make_smem_desc(k_addr[st] + ks * 2048, kHalfTile, 1024),
-                     idesc_kn, (cnt[x] > 0) || (ks > 0));
-            mma_commit(&sm.bar[BAR_DQ0 + x]);
-            ++cnt[x];
+              if (leader)
+                mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, dkm0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)),
+                       idesc_kn, (cnt > 0) || (ks > 0));
+            if (leader) mma_commit(&sm.bar[BAR_DQ0 + x]);
+            ++cnt;
           }
           if ((e_next >> (12 + 2 * x)) & 3u) { tc_fence_after(); issue_s(x, st ^ 1); }
         }
         if (!ok) break;
-        mma_commit(&sm.bar[BAR_K_FREE0 + st]);
+        if (leader) mma_commit(&sm.bar[BAR_K_FREE0 + st]);
       }
-      if (!ok) report_device_error(p.status, 420);
+      if (!ok && leader) report_device_error(p.status, 420);
     }
   } else {
     // ------------------------------------------------------------------ element-wise warpgroups

@@ -148,7 +148,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int hk = blockIdx.y, b = blockIdx.z;
   const int G = a.Hq / a.Hkv;
   const int k0 = kj * BT;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;  // provably warp-uniform
 
   if ((smem_u32(smem_raw) & 1023u) != 0u) {  // the swizzled tiles need 1024-byte alignment
     if (threadIdx.x == 0) report_device_error(p.status, 301);
@@ -216,44 +216,50 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         load_tile(&map_do, sm.d_o[st], &sm.bar[BAR_FULLDO0 + st], h, qi * BT);
       }
       if (!ok) report_device_error(p.status, 305);
-    } else if (warp == 9 && lane == 0 && total > 0) {
-      // ---------------------------------------------------------------- MMA issuer
+    } else if (warp == 9 && total > 0) {
+      // ---------------------------------------------------------------- MMA issuer: the whole warp runs the loop
+      // (warp-uniform control flow and descriptors), one elected lane issues the tcgen05 instructions.  A loop run
+      // by lane 0 alone costs ~60-70 cycles of issue per MMA under load — no slack against the 64 cycles an MMA takes.
+      const bool leader = elect_one();
       constexpr uint32_t idesc_kk = make_idesc_bf16(BT, BT, 0, 0);  // both operands K-major
       constexpr uint32_t idesc_kn = make_idesc_bf16(BT, HD, 0, 1);  // B MN-major
-      const uint32_t k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v), ds_addr = smem_u32(sm.ds);
-      auto gemm_st = [&](uint32_t q_addr) {  // St = K Q^T
+      // descriptors are built once; per MMA only the 16-byte-unit start address moves
+      const uint64_t dk = make_smem_desc(smem_u32(sm.k), 16, 1024), dv = make_smem_desc(smem_u32(sm.v), 16, 1024);
+      const uint64_t dds = make_smem_desc(smem_u32(sm.ds), 16, 1024);
+      const uint64_t dq0 = make_smem_desc(smem_u32(sm.q[0]), 16, 1024), ddo0 = make_smem_desc(smem_u32(sm.d_o[0]), 16, 1024);
+      const uint64_t dqm0 = make_smem_desc(smem_u32(sm.q[0]), kHalfTile, 1024), ddom0 = make_smem_desc(smem_u32(sm.d_o[0]), kHalfTile, 1024);
+      constexpr uint32_t kStageUnits = kTileBytes >> 4;
+      auto gemm_st = [&](int st) {  // St = K Q^T
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * kHalfTile + (ks & 3) * 32;
-          mma_ss(tmem + COL_ST, make_smem_desc(k_addr + off, 16, 1024), make_smem_desc(q_addr + off, 16, 1024), idesc_kk, ks > 0);
+          const uint32_t off = ((ks >> 2) * kHalfTile + (ks & 3) * 32) >> 4;
+          if (leader) mma_ss(tmem + COL_ST, dk + off, dq0 + (uint32_t)(st * kStageUnits + off), idesc_kk, ks > 0);
         }
-        mma_commit(&sm.bar[BAR_S1]);
+        if (leader) mma_commit(&sm.bar[BAR_S1]);
       };
-      auto gemm_dpt = [&](uint32_t do_addr) {  // dPt = V dO^T
+      auto gemm_dpt = [&](int st) {  // dPt = V dO^T
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * kHalfTile + (ks & 3) * 32;
-          mma_ss(tmem + COL_DPT, make_smem_desc(v_addr + off, 16, 1024), make_smem_desc(do_addr + off, 16, 1024), idesc_kk, ks > 0);
+          const uint32_t off = ((ks >> 2) * kHalfTile + (ks & 3) * 32) >> 4;
+          if (leader) mma_ss(tmem + COL_DPT, dv + off, ddo0 + (uint32_t)(st * kStageUnits + off), idesc_kk, ks > 0);
         }
-        mma_commit(&sm.bar[BAR_S2]);
+        if (leader) mma_commit(&sm.bar[BAR_S2]);
       };
       bool ok = mbar_wait(&sm.bar[BAR_KV], 0) && mbar_wait(&sm.bar[BAR_FULLQ0], 0);
       if (ok) {
         tc_fence_after();
-        gemm_st(smem_u32(sm.q[0]));
+        gemm_st(0);
         ok = mbar_wait(&sm.bar[BAR_FULLDO0], 0);
-        if (ok) { tc_fence_after(); gemm_dpt(smem_u32(sm.d_o[0])); }
+        if (ok) { tc_fence_after(); gemm_dpt(0); }
       }
       for (int n = 0; n < total && ok; ++n) {
         const int st = n & 1;
         const uint32_t ph = n & 1;
-        const uint32_t q_addr = smem_u32(sm.q[st]), do_addr = smem_u32(sm.d_o[st]);
-        const uint32_t q_next = smem_u32(sm.q[st ^ 1]), do_next = smem_u32(sm.d_o[st ^ 1]);
         // St columns are free as soon as the consumers hold them in registers
         ok = mbar_wait(&sm.bar[BAR_LS], ph);
         if (ok && n + 1 < total) {
           ok = mbar_wait(&sm.bar[BAR_FULLQ0 + (st ^ 1)], ((n + 1) >> 1) & 1);
-          if (ok) { tc_fence_after(); gemm_st(q_next); }
+          if (ok) { tc_fence_after(); gemm_st(st ^ 1); }
         }
         if (ok) ok = mbar_wait(&sm.bar[BAR_P], ph);
         if (!ok) break;
@@ -261,23 +267,25 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // dV += Pt dO      (A from TMEM, 8 columns per 16-query k-step; B = dO rows as K)
 #pragma unroll
         for (int ks = 0; ks < BT / 16; ++ks)
-          mma_ts(tmem + COL_DV, tmem + COL_PT + ks * 8, make_smem_desc(do_addr + ks * 2048, kHalfTile, 1024), idesc_kn, (n > 0) || (ks > 0));
+          if (leader)
+            mma_ts(tmem + COL_DV, tmem + COL_PT + ks * 8, ddom0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)), idesc_kn, (n > 0) || (ks > 0));
         // dK += dSt Q      (A = dSt in shared memory, K-major over queries)
 #pragma unroll
         for (int ks = 0; ks < BT / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * kHalfTile + (ks & 3) * 32;
-          mma_ss(tmem + COL_DK, make_smem_desc(ds_addr + off, 16, 1024), make_smem_desc(q_addr + ks * 2048, kHalfTile, 1024), idesc_kn, (n > 0) || (ks > 0));
+          const uint32_t off = ((ks >> 2) * kHalfTile + (ks & 3) * 32) >> 4;
+          if (leader)
+            mma_ss(tmem + COL_DK, dds + off, dqm0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)), idesc_kn, (n > 0) || (ks > 0));
         }
-        mma_commit(&sm.bar[BAR_D]);
+        if (leader) mma_commit(&sm.bar[BAR_D]);
         // the next dPt overwrites the columns Pt was read from; it is queued behind dV += Pt dO
         if (n + 1 < total) {
           ok = mbar_wait(&sm.bar[BAR_FULLDO0 + (st ^ 1)], ((n + 1) >> 1) & 1);
           if (!ok) break;
           tc_fence_after();
-          gemm_dpt(do_next);
+          gemm_dpt(st ^ 1);
         }
       }
-      if (!ok) report_device_error(p.status, 310);
+      if (!ok && leader) report_device_error(p.status, 310);
     } else if (warp == 10 && total > 0) {
       // ---------------------------------------------------------------- row statistics of the coming q tiles
       QTileIter loader(p.l, b, hk, G, kj);
