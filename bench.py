@@ -62,8 +62,8 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
 # profiles/tensor_core_kernels_c2_small.md (taken on a quarter of c2 and scaled by the units processed)
 NCU_TRAFFIC_BYTES = {
-    "c2": {"fwd": 4 * (201.4e6 + 103.7e6), "bwd": 4 * (271.4e6 + 109.4e6 + 270.7e6 + 52.9e6)},
-    "c2_small": {"fwd": 201.4e6 + 103.7e6, "bwd": 271.4e6 + 109.4e6 + 270.7e6 + 52.9e6},
+    "c2": {"fwd": 4 * (201.4e6 + 103.8e6), "bwd": 4 * (271.3e6 + 109.3e6 + 270.9e6 + 51.8e6)},
+    "c2_small": {"fwd": 201.4e6 + 103.8e6, "bwd": 271.3e6 + 109.3e6 + 270.9e6 + 51.8e6},
 }
 
 
