@@ -246,9 +246,23 @@ int bma_attn_bwd_preprocess(const bma_attn_args* args, void* d_o_bf16, bma_strea
  * accumulated on chip); the query stays so that a backend with scratch can be added. */
 size_t bma_attn_bwd_workspace_bytes(const bma_attn_args* args);
 
+/* Optional scratch of bma_attn_bwd (0 when the backend has no use for it).  Given a workspace of
+ * at least this size, the tensor-core backward hands every bf16 dS tile (32 KB per visited
+ * 128x128 block, slots addressed densely over [B, Hq, N/128, L/128]) from the dK/dV kernel to the
+ * dQ kernel through that buffer instead of recomputing S and dP there: 5 instead of 7 MMAs per
+ * block, for 32 KB of HBM traffic each way.  Only valid when the q-side and kv-side arrays of
+ * `lists` name the same blocks (they do when both come from one bma_mask_compile call): a slot is
+ * read only if it was written during the same call.  A workspace that holds at least one
+ * (batch, kv head) unit — bma_attn_bwd_scratch_bytes() / (B * Hkv) — still takes this path: the
+ * backward then runs as consecutive launches over ranges of units that reuse the buffer.  With
+ * a smaller or NULL workspace the dQ kernel recomputes S and dP; results agree to the bf16
+ * rounding of dS either way. */
+size_t bma_attn_bwd_scratch_bytes(const bma_attn_args* args);
+
 /* Backward: dQ, dK, dV from (Q, K, V, O, dO, lse, delta).  Replaces
  * _masked_attention_via_map_bwd, jaxmodules/attention.py:266-342.  `lists` must carry the
- * q-side arrays. */
+ * q-side arrays.  `workspace` must hold bma_attn_bwd_workspace_bytes(); one of
+ * bma_attn_bwd_scratch_bytes() selects the hand-over variant described above. */
 int bma_attn_bwd(const bma_attn_args* args, const bma_mask_spec* spec,
                  const bma_block_lists* lists, void* workspace, size_t workspace_bytes,
                  bma_stream_t stream);

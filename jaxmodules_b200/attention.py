@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -216,11 +217,48 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
         if do_bf16 is not None:
             a.d_o = _tensor(do_bf16)
         ws_bytes = lib.bma_attn_bwd_workspace_bytes(C.byref(a))
-        ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=dev)
+        # dS hand-over between the two backward kernels: only for lists whose two sides name the same blocks
+        lists_fn = ctx.get("lists_fn")
+        scratch = lib.bma_attn_bwd_scratch_bytes(C.byref(a)) if (lists_fn is None or getattr(lists_fn, "consistent", False)) else 0
+        if scratch > _scratch_limit:       # below the whole problem: whole (batch, kv head) units, processed range by range
+            unit = scratch // (B * K.shape[-2])
+            scratch = (_scratch_limit // unit) * unit
+        if scratch > 0:
+            ws, ws_bytes = _backward_scratch(dev, max(scratch, ws_bytes)), max(scratch, ws_bytes)
+        else:
+            ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=dev)
         with _Span(_profile_sink, "bwd", dev):
             nat.check(lib.bma_attn_bwd(C.byref(a), C.byref(ctx["dmask"].spec), C.byref(lists), ws.data_ptr(), ws_bytes, st),
                       "bma_attn_bwd")
     return dQ, dK, dV
+
+
+# Scratch of the tensor-core backward (the dS tiles handed from the dK/dV kernel to the dQ kernel): one
+# grow-only buffer per (device, stream), reused by every call in that stream's order.  A problem whose
+# scratch exceeds the limit runs range by range over (batch, kv head) units; when not even one unit fits
+# (32 KB x Hq/Hkv x N/128 x L/128), the dQ kernel recomputes S and dP instead.
+_scratch_limit = int(float(os.environ.get("BMA_BWD_SCRATCH_GB", "16")) * (1 << 30))   # environment override, in GiB
+_scratch_buffers = {}
+
+
+def set_backward_scratch_limit(nbytes: int) -> None:
+    """Upper bound in bytes of the backward scratch buffer (32 KB per 128x128 block of the dense
+    [B, Hq, N/128, L/128] grid); 0 switches the dS hand-over off.  Frees buffers above the new limit."""
+    global _scratch_limit
+    _scratch_limit = int(nbytes)
+    for key in [k for k, t in _scratch_buffers.items() if t.numel() > _scratch_limit]:
+        del _scratch_buffers[key]
+
+
+def _backward_scratch(dev: torch.device, nbytes: int) -> torch.Tensor:
+    # keyed by stream too: two backward passes in flight on different streams must not share slots
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), torch.cuda.current_stream(dev).cuda_stream)
+    buf = _scratch_buffers.get(key)
+    if buf is None or buf.numel() < nbytes:
+        _scratch_buffers.pop(key, None)   # drop the old buffer before asking for the larger one
+        buf = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
+        _scratch_buffers[key] = buf
+    return buf
 
 
 class _MaskedAttention(torch.autograd.Function):

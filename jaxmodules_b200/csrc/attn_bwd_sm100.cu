@@ -19,6 +19,11 @@
 // while the MMAs of tile n run.  Pt is written over the dPt columns once every consumer has read
 // them; the next V dO^T is issued behind dV += Pt dO (MMAs of one issuing thread execute in order).
 // Warp 10 stages lse*log2e and delta of the coming q tiles in shared memory.
+//
+// With a scratch buffer (BwdParams::ds_out) the kernel also hands every dSt tile to the dQ kernel:
+// warp 11 copies the 32 KB shared-memory image (already in MMA operand layout) to its slot in
+// global memory with one bulk store per tile, and dQ += dS K then needs no recomputation of S and
+// dP (5 instead of 7 MMAs per block for the whole backward, paid with 32 KB of HBM traffic each way).
 // Every mbarrier wait is bounded; on a timeout the thread records an error code and unwinds.
 #include "common.cuh"
 #include "ptx_sm100.cuh"
@@ -30,6 +35,8 @@
 namespace bma {
 
 int sm100_bwd_dq(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, cudaStream_t st);
+int sm100_bwd_dq_from_ds(const bma_attn_args& a, const bma_block_lists& lists, const void* ds, int b0, int nb, int hk0, int nhk,
+                         cudaStream_t st);
 
 namespace {
 
@@ -37,7 +44,7 @@ using namespace ptx;
 
 constexpr int BT = kSm100Tile;  // the head dimension HD (64 or 128) is a template parameter
 constexpr int kConsumers = 256;
-constexpr int kThreads = kConsumers + 128;  // + one warpgroup: warp 8 TMA, warp 9 MMA issue, warp 10 row statistics
+constexpr int kThreads = kConsumers + 128;  // + one warpgroup: warp 8 TMA, warp 9 MMA issue, warp 10 row statistics, warp 11 dSt hand-over
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kHalfTile = BT * 64 * 2;
 template <int HD> constexpr uint32_t kTileBytesOf = (HD / 64) * kHalfTile;  // a [128 x HD] operand tile
@@ -46,7 +53,7 @@ constexpr uint32_t COL_DV = 0, COL_DK = 128, COL_ST = 256, COL_DPT = 384, COL_PT
 
 enum {
   BAR_KV = 0, BAR_FULLQ0, BAR_FULLQ1, BAR_FULLDO0, BAR_FULLDO1, BAR_STAT0, BAR_STAT1,
-  BAR_S1, BAR_S2, BAR_LS, BAR_P, BAR_D, BAR_SYNC2,
+  BAR_S1, BAR_S2, BAR_LS, BAR_P, BAR_D, BAR_SYNC2, BAR_DSR,
   NUM_BARS
 };
 
@@ -70,6 +77,9 @@ struct BwdParams {
   float scale_log2;
   int interval_mask;
   int* status;
+  uint8_t* ds_out;  // null, or [nb, nhk * G, NQ, NKV] slots of kDsBytes: the dSt image of every visited block
+  int b0, hk0;      // first batch / kv head of this launch (the grid covers a range when the scratch is smaller
+  int nhk;          // than the whole problem), and the number of kv heads in the range
 };
 
 // Rendezvous of the 256 consumer threads on an mbarrier: arrive, then a bounded wait (a plain
@@ -145,7 +155,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   const bma_attn_args& a = p.a;
   const int kj = blockIdx.x;  // causal: kv tile 0 sees the most q tiles, so launch order is already heavy-first
-  const int hk = blockIdx.y, b = blockIdx.z;
+  const int hk = blockIdx.y + p.hk0, b = blockIdx.z + p.b0;
   const int G = a.Hq / a.Hkv;
   const int k0 = kj * BT;
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;  // provably warp-uniform
@@ -310,6 +320,28 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         mbar_arrive(&sm.bar[BAR_STAT0 + st]);
       }
       if (!ok && lane == 0) report_device_error(p.status, 315);
+    } else if (warp == 11 && p.ds_out != nullptr && total > 0) {
+      // ---------------------------------------------------------------- dSt hand-over to the dQ kernel
+      // BAR_P says that all consumers have written (and fenced) the dSt image of tile n; one bulk store
+      // moves it to its slot, and BAR_DSR tells the consumers that the buffer has been read.
+      QTileIter loader(p.l, b, hk, G, kj);
+      const uint64_t policy = l2_evict_first();
+      bool ok = true;
+      for (int n = 0; n < total && ok; ++n) {
+        int h, qi; bool partial;
+        loader.next(h, qi, partial);
+        ok = mbar_wait(&sm.bar[BAR_P], n & 1);
+        if (!ok) break;
+        if (lane == 0) {
+          const int64_t slot = (((int64_t)(b - p.b0) * (p.nhk * G) + (h - p.hk0 * G)) * p.l.NQ + qi) * p.l.NKV + kj;
+          bulk_store_1d(p.ds_out + slot * (int64_t)kDsBytes, sm.ds, kDsBytes, policy);
+          bulk_commit();
+          bulk_wait_read0();
+          mbar_arrive(&sm.bar[BAR_DSR]);
+        }
+        __syncwarp();
+      }
+      if (!ok && lane == 0) report_device_error(p.status, 318);
     }
   } else {
     // ------------------------------------------------------------------ softmax-gradient warps
@@ -435,6 +467,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       ok = consumer_sync(&sm.bar[BAR_SYNC2], ph);
       // the dSt buffer is still being read by dK += dSt Q of the previous tile until BAR_D completes
       if (ok && n > 0) ok = mbar_wait(&sm.bar[BAR_D], (n - 1) & 1);
+      // ... and, when dSt tiles are handed to the dQ kernel, until the bulk store of the previous one has read it
+      if (ok && n > 0 && p.ds_out != nullptr) ok = mbar_wait(&sm.bar[BAR_DSR], (n - 1) & 1);
       if (!ok) break;
       tmem_st32(tmem + COL_PT + lane_base + half * 32, pk);  // 64 queries = 32 packed columns per half
       {
@@ -531,7 +565,13 @@ bool sm100_bwd_supported(const bma_attn_args& a) { return sm100_supported(a) && 
 
 size_t sm100_bwd_workspace_bytes(const bma_attn_args&) { return 0; }
 
-int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, void*, size_t,
+// one dSt image per (query head of the group, q tile, kv tile) of a (batch, kv head) unit, addressed densely
+static size_t scratch_unit_bytes(const bma_attn_args& a) {
+  return (size_t)(a.Hq / a.Hkv) * ceil_div(a.N, BT) * ceil_div(a.L, BT) * kDsBytes;
+}
+size_t sm100_bwd_scratch_bytes(const bma_attn_args& a) { return (size_t)a.B * a.Hkv * scratch_unit_bytes(a); }
+
+int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, void* ws, size_t ws_bytes,
               cudaStream_t st) {
   BMA_REQUIRE(lists.q_block == BT && lists.kv_block == BT && lists.q_num, BMA_ERR_ARG);
   BMA_REQUIRE(a.d_o.dtype == BMA_DTYPE_BF16, BMA_ERR_UNSUPPORTED);  // bma_attn_bwd_preprocess provides the bf16 copy
@@ -556,18 +596,37 @@ int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   p.interval_mask = interval;
   p.status = device_status_ptr();
   BMA_REQUIRE(p.status != nullptr, BMA_ERR_CUDA);
-  dim3 grid(ceil_div(a.L, BT), a.Hkv, a.B);
-  auto launch = [&](auto kernel, size_t smem) -> int {
-    BMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kernel<<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
-    return BMA_OK;
-  };
-  if (a.d == 128) rc = a.key_bias ? launch(bwd_dkdv_kernel<128, true>, sizeof(BwdSmem<128>)) : launch(bwd_dkdv_kernel<128, false>, sizeof(BwdSmem<128>));
-  else rc = a.key_bias ? launch(bwd_dkdv_kernel<64, true>, sizeof(BwdSmem<64>)) : launch(bwd_dkdv_kernel<64, false>, sizeof(BwdSmem<64>));
-  if (rc) return rc;
-  count_launches(1);
-  BMA_CUDA_TRY(cudaGetLastError());
-  return sm100_bwd_dq(a, spec, lists, st);
+  // A scratch buffer switches the dQ pass from recomputation to replaying the dSt tiles.  It must hold at least
+  // one (batch, kv head) unit; when it is smaller than the whole problem the backward runs as consecutive
+  // launches over ranges of batches (or, below one batch, of kv heads) that reuse the buffer.
+  const size_t unit = scratch_unit_bytes(a);
+  const size_t units = (ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 15) == 0) ? ws_bytes / unit : 0;
+  const bool hand_over = units >= 1 && lists.NQ == ceil_div(a.N, BT) && lists.NKV == ceil_div(a.L, BT);
+  p.ds_out = hand_over ? static_cast<uint8_t*>(ws) : nullptr;
+  int step_b = a.B, step_hk = a.Hkv;
+  if (hand_over && units < (size_t)a.B * a.Hkv) {
+    if (units >= (size_t)a.Hkv) step_b = (int)(units / a.Hkv);
+    else { step_b = 1; step_hk = (int)units; }
+  }
+  for (int b0 = 0; b0 < a.B; b0 += step_b) {
+    for (int hk0 = 0; hk0 < a.Hkv; hk0 += step_hk) {
+      const int nb = a.B - b0 < step_b ? a.B - b0 : step_b, nhk = a.Hkv - hk0 < step_hk ? a.Hkv - hk0 : step_hk;
+      p.b0 = b0; p.hk0 = hk0; p.nhk = nhk;
+      dim3 grid(ceil_div(a.L, BT), nhk, nb);
+      auto launch = [&](auto kernel, size_t smem) -> int {
+        BMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kernel<<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
+        return BMA_OK;
+      };
+      if (a.d == 128) rc = a.key_bias ? launch(bwd_dkdv_kernel<128, true>, sizeof(BwdSmem<128>)) : launch(bwd_dkdv_kernel<128, false>, sizeof(BwdSmem<128>));
+      else rc = a.key_bias ? launch(bwd_dkdv_kernel<64, true>, sizeof(BwdSmem<64>)) : launch(bwd_dkdv_kernel<64, false>, sizeof(BwdSmem<64>));
+      if (rc) return rc;
+      count_launches(1);
+      BMA_CUDA_TRY(cudaGetLastError());
+      if (hand_over && (rc = sm100_bwd_dq_from_ds(a, lists, ws, b0, nb, hk0, nhk, st))) return rc;
+    }
+  }
+  return hand_over ? BMA_OK : sm100_bwd_dq(a, spec, lists, st);
 }
 
 }  // namespace bma

@@ -357,6 +357,11 @@ size_t bma_attn_bwd_workspace_bytes(const bma_attn_args* args) {
   return pick_backend_bwd(args) == BMA_BACKEND_TCGEN05 ? sm100_bwd_workspace_bytes(*args) : 0;
 }
 
+size_t bma_attn_bwd_scratch_bytes(const bma_attn_args* args) {
+  if (validate_common(args) != BMA_OK) return 0;
+  return pick_backend_bwd(args) == BMA_BACKEND_TCGEN05 ? sm100_bwd_scratch_bytes(*args) : 0;
+}
+
 int bma_attn_bwd(const bma_attn_args* args, const bma_mask_spec* spec, const bma_block_lists* lists, void* workspace,
                  size_t workspace_bytes, bma_stream_t stream) {
   int rc = validate_common(args);

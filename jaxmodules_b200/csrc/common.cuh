@@ -174,6 +174,7 @@ int sm100_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
 int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, void* ws,
               size_t ws_bytes, cudaStream_t st);
 size_t sm100_bwd_workspace_bytes(const bma_attn_args& a);
+size_t sm100_bwd_scratch_bytes(const bma_attn_args& a);
 bool sm100_supported(const bma_attn_args& a);
 bool sm100_bwd_supported(const bma_attn_args& a);
 

@@ -81,6 +81,27 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 // waits until the committed bulk groups have finished READING their shared-memory sources
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
+// Untiled bulk copies of a contiguous byte range (both addresses 16-byte aligned, size a multiple
+// of 16).  They move the raw shared-memory image of a swizzled operand tile to global memory and
+// back, so a tile written for one MMA can be replayed by another kernel without re-deriving the
+// layout.  `policy` is an L2 eviction policy (see l2_evict_first()).
+__device__ __forceinline__ uint64_t l2_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      ::"r"(smem_u32(smem_dst)), "l"(__cvta_generic_to_global(gsrc)), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_store_1d(void* gdst, const void* smem_src, uint32_t bytes, uint64_t policy) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;"
+               ::"l"(__cvta_generic_to_global(gdst)), "r"(smem_u32(smem_src)), "r"(bytes), "l"(policy)
+               : "memory");
+}
+
 // ---- tensor memory -------------------------------------------------------------------------
 // Executed by one full warp.  ncols: power of two >= 32.  The base address lands in *smem_out.
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_out, uint32_t ncols) {

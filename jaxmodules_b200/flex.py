@@ -56,7 +56,7 @@ class _ReadyLists:
     def __init__(self, bm: BlockMask, device):
         self.bm, self.device = bm, device
         self.NQ, self.NKV = bm.Q_LEN // bm.Q_BLOCK_SIZE, bm.KV_LEN // bm.KV_BLOCK_SIZE
-        self._kv = self._q = None
+        self._kv = self._q = self._consistent = None
 
     def _fit(self, num, idx, width):
         num = num.to(device=self.device, dtype=torch.int32)
@@ -85,6 +85,21 @@ class _ReadyLists:
                 self._q = (*get_sparse_q_data_from_blocks(part), *get_sparse_q_data_from_blocks(full))
                 self._q = tuple(t.contiguous() for t in self._q)
         return self._q
+
+    @property
+    def consistent(self) -> bool:
+        """True when the q-side and the kv-side arrays name the same blocks (checked once, on the device);
+        the backward then may hand dS tiles from the kv-major kernel to the query-major one."""
+        if self._consistent is None:
+            bm = self.bm
+            kv_num, kv_idx, fkv_num, fkv_idx = self._kv_side()
+            q_num, q_idx, fq_num, fq_idx = self._q_side()
+            kv = (get_dense_from_kv_blocks(bm.B, bm.H, self.NQ, self.NKV, kv_num, kv_idx)
+                  | get_dense_from_kv_blocks(bm.B, bm.H, self.NQ, self.NKV, fkv_num, fkv_idx))
+            q = (get_dense_from_kv_blocks(bm.B, bm.H, self.NKV, self.NQ, q_num, q_idx)
+                 | get_dense_from_kv_blocks(bm.B, bm.H, self.NKV, self.NQ, fq_num, fq_idx))
+            self._consistent = bool(torch.equal(kv, q.transpose(-1, -2)))
+        return self._consistent
 
     def __call__(self, q_tile: int, kv_tile: int, q_side: bool):
         bm = self.bm
@@ -281,7 +296,15 @@ def flex_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, 
             else:
                 terms = _structured_terms(block_mask.mask_mod)
                 if route == "lists":
-                    lists_fn = _ReadyLists(block_mask, dev)
+                    # fitted once per BlockMask and device (the reference's BlockMask is immutable as well)
+                    cached = getattr(block_mask, "_ready_lists", None)
+                    if cached is None or cached.device != dev:
+                        cached = _ReadyLists(block_mask, dev)
+                        try:
+                            block_mask._ready_lists = cached
+                        except AttributeError:
+                            pass
+                    lists_fn = cached
         O, _ = _att._MaskedAttention.apply(Q, K, V, terms, out_dtype or torch.float32, backend,
                                            None if scale is None else float(scale), lists_fn, key_bias)
     return O.transpose(1, 2)

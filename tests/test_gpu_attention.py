@@ -202,6 +202,42 @@ def test_simt_and_auto_backends_agree_bf16():
         assert (x.float() - y.float()).abs().max() <= 2e-2
 
 
+@pytest.mark.parametrize("d,G,mask", [(128, 1, "causal"), (128, 2, "band"), (64, 1, "segments"), (128, 1, "ragged")])
+def test_backward_ds_hand_over_matches_recompute(d, G, mask):
+    """The tensor-core backward with the scratch buffer (dK/dV kernel stores every dS tile, the dQ kernel
+    replays them) against the same backward without it (dQ kernel recomputes S and dP), and both against
+    the exact-FP32 SIMT kernels."""
+    from jaxmodules_b200 import attention as A
+    N = L = 640 if mask != "ragged" else 600
+    Q = gen((2, N, 2 * G, d), 0, torch.bfloat16)
+    K, V = (gen((2, L, 2, d), i, torch.bfloat16) for i in (1, 2))
+    dO = gen((2, N, 2 * G, d), 3, torch.float32)
+    kw = dict(is_causal=True)
+    if mask == "band":
+        kw = dict(mask_fn=M.sliding_window_mask(100, 30))
+    if mask == "segments":
+        seg = np.sort(np.random.Generator(np.random.PCG64(5)).integers(0, 4, size=(2, L)), axis=1).astype(np.int32)
+        kw = dict(mask_fn=M.and_masks(M.document_mask(seg), M.causal_mask()))
+    limit = A._scratch_limit
+    unit = 32768 * G * 5 * 5                      # one (batch, kv head) unit of this shape
+    try:
+        with_scratch = run(Q, K, V, dO, **kw)
+        for small in (3 * unit, unit + 5):        # 4 units in all: one batch (2 kv heads) per range; then one unit per range
+            A.set_backward_scratch_limit(small)
+            in_ranges = run(Q, K, V, dO, **kw)
+            assert all(torch.equal(x, y) for x, y in zip(with_scratch, in_ranges))
+        A.set_backward_scratch_limit(0)
+        recomputed = run(Q, K, V, dO, **kw)
+    finally:
+        A.set_backward_scratch_limit(limit)
+    exact = run(Q, K, V, dO, backend=nat.BMA_BACKEND_SIMT, **kw)
+    for x, y, z in zip(with_scratch, recomputed, exact):
+        assert torch.isfinite(x.float()).all()
+        assert (x.float() - y.float()).abs().max() <= 2e-2 * max(1.0, float(z.float().abs().max()))
+        assert (x.float() - z.float()).abs().max() <= 2e-2 * max(1.0, float(z.float().abs().max()))
+        assert (x.float() - z.float()).abs().mean() <= 2e-3
+
+
 def test_full_size_properties_config2():
     """BASELINE config 2 at full size (B=8, L=4096, H=32, d=128, bf16 causal): properties that do
     not need the oracle — row 0 attends only key 0 so O[:,0] == V[:,0]; the output is a convex
