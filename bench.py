@@ -62,8 +62,9 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
 # profiles/tensor_core_kernels_c2_small.md (taken on a quarter of c2 and scaled by the units processed)
 NCU_TRAFFIC_BYTES = {
-    "c2": {"fwd": 4 * (201.4e6 + 103.8e6), "bwd": 4 * (271.3e6 + 109.3e6 + 270.9e6 + 51.8e6)},
-    "c2_small": {"fwd": 201.4e6 + 103.8e6, "bwd": 271.3e6 + 109.3e6 + 270.9e6 + 51.8e6},
+    # bwd = bwd_dkdv_kernel (read + write, the write includes 1.107 GB of dS tiles) + bwd_dq_replay_kernel (read + write)
+    "c2": {"fwd": 4 * (201.4e6 + 103.8e6), "bwd": 4 * (290.0e6 + 1183.5e6 + 1174.5e6 + 40.4e6)},
+    "c2_small": {"fwd": 201.4e6 + 103.8e6, "bwd": 290.0e6 + 1183.5e6 + 1174.5e6 + 40.4e6},
 }
 
 
@@ -485,7 +486,7 @@ def main():
                        "flop_model": "fwd 4*bq*bk*d per non-empty block, bwd 2.5x fwd"},
             "fwd_tflops": fwd_tf, "bwd_tflops": bwd_tf,
             "kernel_ms": per_kernel,
-            "roofline": {"bound": "tensor", "kernel": "backward (bwd_dkdv_kernel + bwd_dq_kernel)", "achieved": bwd_tf, "peak": sustained,
+            "roofline": {"bound": "tensor", "kernel": "backward (bwd_dkdv_kernel + bwd_dq_replay_kernel)", "achieved": bwd_tf, "peak": sustained,
                          "unit": "TFLOP/s", "frac": (bwd_tf / sustained) if bwd_tf else None, "traffic": traffic.get("bwd"),
                          "peak_kind": f"{peak_kind} sustained dense bf16 (kernel timed inside a long step)"},
             "roofline_fwd": {"bound": "tensor", "kernel": "forward", "achieved": fwd_tf, "peak": sustained, "unit": "TFLOP/s",
