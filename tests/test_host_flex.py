@@ -118,3 +118,17 @@ def test_score_mod_affine_family():
                 lambda s, b, h, q, k: np.tanh(s)):
         with pytest.raises(NotImplementedError):
             score_mod_affine(bad, 2, 2, 16, 16)
+
+
+def test_ready_lists_consistency_check():
+    """The backward may hand dS tiles from the kv-major to the query-major kernel only when both list
+    sides name the same blocks; user-made q-side arrays are compared with the kv side once."""
+    bm = jm.BlockMask.causal_mask(1, 1, 512, 512, 128)
+    assert _ReadyLists(bm, "cpu").consistent
+    tampered = jm.BlockMask.causal_mask(1, 1, 512, 512, 128)
+    tampered.q_num_blocks = tampered.q_num_blocks.clone()
+    tampered.q_num_blocks[0, 0, 1] = 0                         # a partial block the kv side still lists
+    assert not _ReadyLists(tampered, "cpu").consistent
+    kv_only = jm.BlockMask.from_kv_blocks(bm.kv_num_blocks, bm.kv_indices, bm.full_kv_num_blocks, bm.full_kv_indices,
+                                          BLOCK_SIZE=128, mask_mod=bm.mask_mod, seq_lengths=(512, 512))
+    assert _ReadyLists(kv_only, "cpu").consistent              # q side derived from the kv side
