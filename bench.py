@@ -63,8 +63,10 @@ WORKLOADS = {
 # profiles/tensor_core_kernels_c2_small.md (taken on a quarter of c2 and scaled by the units processed)
 NCU_TRAFFIC_BYTES = {
     # bwd = bwd_dkdv_kernel (read + write, the write includes 1.107 GB of dS tiles) + bwd_dq_replay_kernel (read + write)
-    "c2": {"fwd": 4 * (201.4e6 + 103.8e6), "bwd": 4 * (290.0e6 + 1183.5e6 + 1174.5e6 + 40.4e6)},
-    "c2_small": {"fwd": 201.4e6 + 103.8e6, "bwd": 290.0e6 + 1183.5e6 + 1174.5e6 + 40.4e6},
+    "c2": {"fwd": 4 * (201.4e6 + 103.8e6), "bwd": 4 * (290.0e6 + 1183.5e6 + 1174.5e6 + 40.4e6),
+           "bwd_dkdv": 4 * (290.0e6 + 1183.5e6), "bwd_dq_replay": 4 * (1174.5e6 + 40.4e6)},
+    "c2_small": {"fwd": 201.4e6 + 103.8e6, "bwd": 290.0e6 + 1183.5e6 + 1174.5e6 + 40.4e6,
+                 "bwd_dkdv": 290.0e6 + 1183.5e6, "bwd_dq_replay": 1174.5e6 + 40.4e6},
 }
 
 
@@ -495,13 +497,30 @@ def main():
                        "flop_model": "fwd 4*bq*bk*d per non-empty block, bwd 2.5x fwd"},
             "fwd_tflops": fwd_tf, "bwd_tflops": bwd_tf,
             "kernel_ms": per_kernel,
-            "roofline": {"bound": "tensor", "kernel": "backward (bwd_dkdv_kernel + bwd_dq_replay_kernel)", "achieved": bwd_tf, "peak": sustained,
+            "roofline": {"bound": "tensor", "kernel": "backward (bwd_dkdv_kernel + dQ kernel)", "achieved": bwd_tf, "peak": sustained,
                          "unit": "TFLOP/s", "frac": (bwd_tf / sustained) if bwd_tf else None, "traffic": traffic.get("bwd"),
                          "peak_kind": f"{peak_kind} sustained dense bf16 (kernel timed inside a long step)"},
             "roofline_fwd": {"bound": "tensor", "kernel": "forward", "achieved": fwd_tf, "peak": sustained, "unit": "TFLOP/s",
                              "frac": (fwd_tf / sustained) if fwd_tf else None, "traffic": traffic.get("fwd")},
             "clocks": clocks, "gpu_launches": int(launches),
         }
+        dkdv_ms, replay_ms = per_kernel.get("bwd_dkdv"), per_kernel.get("bwd_dq_replay")
+        if dkdv_ms and replay_ms:
+            # The two backward kernels timed separately (the library records an event between them).  The dK/dV kernel
+            # runs 4 of the 5 algorithmic MMAs of the backward; the replay kernel runs the fifth and is bound by the HBM
+            # stream of the dS tiles: 32 KB per non-empty block, plus K read once and dQ written once.
+            dkdv_tf = 0.8 * (step_flops - fwd_flops) / (dkdv_ms * 1e-3) / 1e12
+            line["roofline"] = {"bound": "tensor", "kernel": "bwd_dkdv_kernel (dominant: %.0f %% of the step)" % (100 * dkdv_ms / ms_step),
+                                "achieved": dkdv_tf, "peak": sustained, "unit": "TFLOP/s", "frac": dkdv_tf / sustained,
+                                "traffic": traffic.get("bwd_dkdv"),
+                                "peak_kind": f"{peak_kind} sustained dense bf16 (kernel timed inside a long step)"}
+            replay_bytes = blocks * 32768 + 2 * B * L * H * d * 2
+            replay_gbs = replay_bytes / (replay_ms * 1e-3) / 1e9
+            line["roofline_dq_replay"] = {"bound": "hbm", "kernel": "bwd_dq_replay_kernel", "achieved": replay_gbs, "peak": hbm,
+                                          "unit": "GB/s", "frac": replay_gbs / hbm, "traffic": traffic.get("bwd_dq_replay")}
+            line["roofline_bwd"] = {"bound": "tensor", "kernel": "backward (bwd_dkdv_kernel + bwd_dq_replay_kernel)", "achieved": bwd_tf,
+                                    "peak": sustained, "unit": "TFLOP/s", "frac": (bwd_tf / sustained) if bwd_tf else None,
+                                    "traffic": traffic.get("bwd")}
         if e2e:
             line["e2e"] = {"value": total_flops / (e2e[0] * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e[0],
                            "h2d_bytes_per_step": e2e[1], "d2h_bytes_per_step": e2e[2]}

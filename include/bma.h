@@ -259,6 +259,12 @@ size_t bma_attn_bwd_workspace_bytes(const bma_attn_args* args);
  * rounding of dS either way. */
 size_t bma_attn_bwd_scratch_bytes(const bma_attn_args* args);
 
+/* Profiling aid: the next bma_attn_bwd call of the calling thread records `cuda_event` (a
+ * cudaEvent_t created with timing enabled) on its stream between the dK/dV pass and the dQ
+ * pass, so that the two kernels can be timed separately with CUDA events.  Used once, then
+ * forgotten; ignored by the SIMT backend and when the backward runs in several ranges. */
+void bma_attn_bwd_mark(void* cuda_event);
+
 /* Backward: dQ, dK, dV from (Q, K, V, O, dO, lse, delta).  Replaces
  * _masked_attention_via_map_bwd, jaxmodules/attention.py:266-342.  `lists` must carry the
  * q-side arrays.  `workspace` must hold bma_attn_bwd_workspace_bytes(); one of

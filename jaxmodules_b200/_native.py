@@ -102,6 +102,7 @@ SIGNATURES = {
     "bma_attn_bwd_preprocess": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p]),
     "bma_attn_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
     "bma_attn_bwd_scratch_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
+    "bma_attn_bwd_mark": (None, [C.c_void_p]),
     "bma_attn_bwd": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(MaskSpec), C.POINTER(BlockLists), C.c_void_p, C.c_size_t,
                                C.c_void_p]),
     "bma_attn_merge": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),

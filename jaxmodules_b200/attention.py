@@ -220,16 +220,26 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
         # dS hand-over between the two backward kernels: only for lists whose two sides name the same blocks
         lists_fn = ctx.get("lists_fn")
         scratch = lib.bma_attn_bwd_scratch_bytes(C.byref(a)) if (lists_fn is None or getattr(lists_fn, "consistent", False)) else 0
-        if scratch > _scratch_limit:       # below the whole problem: whole (batch, kv head) units, processed range by range
+        ranges = scratch > _scratch_limit
+        if ranges:                         # below the whole problem: whole (batch, kv head) units, processed range by range
             unit = scratch // (B * K.shape[-2])
             scratch = (_scratch_limit // unit) * unit
         if scratch > 0:
             ws, ws_bytes = _backward_scratch(dev, max(scratch, ws_bytes)), max(scratch, ws_bytes)
         else:
             ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=dev)
-        with _Span(_profile_sink, "bwd", dev):
+        mid = None
+        if _profile_sink is not None and be == nat.BMA_BACKEND_TCGEN05 and not (ranges and scratch > 0):
+            # the library re-records this event between its dK/dV pass and its dQ pass
+            mid = torch.cuda.Event(enable_timing=True)
+            mid.record(torch.cuda.current_stream(dev))
+            lib.bma_attn_bwd_mark(mid.cuda_event)
+        with _Span(_profile_sink, "bwd", dev) as span:
             nat.check(lib.bma_attn_bwd(C.byref(a), C.byref(ctx["dmask"].spec), C.byref(lists), ws.data_ptr(), ws_bytes, st),
                       "bma_attn_bwd")
+        if mid is not None:
+            _profile_sink.setdefault("bwd_dkdv", []).append((span.t0, mid))
+            _profile_sink.setdefault("bwd_dq_replay" if scratch > 0 else "bwd_dq_recompute", []).append((mid, span.t1))
     return dQ, dK, dV
 
 

@@ -572,7 +572,7 @@ static size_t scratch_unit_bytes(const bma_attn_args& a) {
 size_t sm100_bwd_scratch_bytes(const bma_attn_args& a) { return (size_t)a.B * a.Hkv * scratch_unit_bytes(a); }
 
 int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, void* ws, size_t ws_bytes,
-              cudaStream_t st) {
+              cudaEvent_t mark, cudaStream_t st) {
   BMA_REQUIRE(lists.q_block == BT && lists.kv_block == BT && lists.q_num, BMA_ERR_ARG);
   BMA_REQUIRE(a.d_o.dtype == BMA_DTYPE_BF16, BMA_ERR_UNSUPPORTED);  // bma_attn_bwd_preprocess provides the bf16 copy
   BMA_REQUIRE(aligned16(a.d_o) && aligned16(a.dq) && aligned16(a.dk) && aligned16(a.dv), BMA_ERR_UNSUPPORTED);
@@ -608,6 +608,7 @@ int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
     if (units >= (size_t)a.Hkv) step_b = (int)(units / a.Hkv);
     else { step_b = 1; step_hk = (int)units; }
   }
+  if (step_b < a.B || step_hk < a.Hkv) mark = nullptr;  // several ranges: no single boundary between the passes
   for (int b0 = 0; b0 < a.B; b0 += step_b) {
     for (int hk0 = 0; hk0 < a.Hkv; hk0 += step_hk) {
       const int nb = a.B - b0 < step_b ? a.B - b0 : step_b, nhk = a.Hkv - hk0 < step_hk ? a.Hkv - hk0 : step_hk;
@@ -623,6 +624,7 @@ int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
       if (rc) return rc;
       count_launches(1);
       BMA_CUDA_TRY(cudaGetLastError());
+      if (mark) BMA_CUDA_TRY(cudaEventRecord(mark, st));
       if (hand_over && (rc = sm100_bwd_dq_from_ds(a, lists, ws, b0, nb, hk0, nhk, st))) return rc;
     }
   }

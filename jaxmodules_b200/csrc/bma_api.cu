@@ -27,6 +27,12 @@ std::mutex g_status_mutex;
 std::atomic<unsigned long long> g_launches{0};
 }  // namespace
 
+static thread_local cudaEvent_t g_bwd_mark = nullptr;
+static cudaEvent_t take_bwd_mark() {
+  cudaEvent_t ev = g_bwd_mark;
+  g_bwd_mark = nullptr;
+  return ev;
+}
 void count_launches(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
 void set_last_cuda_error(cudaError_t e, const char* where) {
@@ -357,6 +363,8 @@ size_t bma_attn_bwd_workspace_bytes(const bma_attn_args* args) {
   return pick_backend_bwd(args) == BMA_BACKEND_TCGEN05 ? sm100_bwd_workspace_bytes(*args) : 0;
 }
 
+void bma_attn_bwd_mark(void* cuda_event) { g_bwd_mark = static_cast<cudaEvent_t>(cuda_event); }
+
 size_t bma_attn_bwd_scratch_bytes(const bma_attn_args* args) {
   if (validate_common(args) != BMA_OK) return 0;
   return pick_backend_bwd(args) == BMA_BACKEND_TCGEN05 ? sm100_bwd_scratch_bytes(*args) : 0;
@@ -364,6 +372,7 @@ size_t bma_attn_bwd_scratch_bytes(const bma_attn_args* args) {
 
 int bma_attn_bwd(const bma_attn_args* args, const bma_mask_spec* spec, const bma_block_lists* lists, void* workspace,
                  size_t workspace_bytes, bma_stream_t stream) {
+  cudaEvent_t mark = take_bwd_mark();  // consumed by this call whatever its outcome
   int rc = validate_common(args);
   if (rc != BMA_OK) return rc;
   BMA_REQUIRE(spec != nullptr, BMA_ERR_ARG);
@@ -385,7 +394,7 @@ int bma_attn_bwd(const bma_attn_args* args, const bma_mask_spec* spec, const bma
   if (be == BMA_BACKEND_TCGEN05) {
     const size_t need = sm100_bwd_workspace_bytes(*args);
     BMA_REQUIRE(need == 0 || (workspace && workspace_bytes >= need), BMA_ERR_WORKSPACE);
-    return sm100_bwd(*args, *spec, *lists, workspace, workspace_bytes, st);
+    return sm100_bwd(*args, *spec, *lists, workspace, workspace_bytes, mark, st);
   }
   return simt_bwd(*args, *spec, *lists, st);
 }

@@ -172,7 +172,7 @@ int simt_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_
 int simt_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, cudaStream_t st);
 int sm100_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, cudaStream_t st);
 int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, void* ws,
-              size_t ws_bytes, cudaStream_t st);
+              size_t ws_bytes, cudaEvent_t mark, cudaStream_t st);
 size_t sm100_bwd_workspace_bytes(const bma_attn_args& a);
 size_t sm100_bwd_scratch_bytes(const bma_attn_args& a);
 bool sm100_supported(const bma_attn_args& a);
