@@ -230,6 +230,45 @@ def run_reference(args, w, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_block_mask_build(args, w, rank, world, dev, warmup):
+    """The BlockMask builder alone: create_block_mask with full [B, H] extents, as the reference's
+    create_block_mask returns them.  HBM-write bound: both list sides are 4*(2*B*H*NQ + 2*B*H*NQ*NKV) bytes each."""
+    import jaxmodules_b200 as jm
+    from jaxmodules_b200 import _native as nat, masks as M
+    B, L, H, bs = w["B"], w["L"], w["H"], w["bs"]
+    if w["mask"] == "causal":
+        mask_mod = M.causal_mask()
+    elif w["mask"] == "sliding256":
+        mask_mod = M.sliding_window_mask(256, 256)
+    else:
+        mask_mod = M.document_mask(document_segments(B, L), causal=True)
+    build = lambda: jm.create_block_mask(mask_mod, B, H, L, L, bs, device=dev)
+    for _ in range(warmup):
+        bm = build()
+    torch.cuda.synchronize(dev)
+    launches0 = nat.lib().bma_launch_count()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        bm = build()
+    t1.record()
+    torch.cuda.synchronize(dev)
+    ms = t0.elapsed_time(t1) / args.steps
+    NQ = NKV = L // bs
+    out_bytes = 2 * 4 * (2 * B * H * NQ + 2 * B * H * NQ * NKV)
+    _, _, hbm, peak_kind = peaks()
+    gbs = out_bytes / (ms * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": "block_mask_build_bandwidth", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms, "higher_is_better": True, "dtype": "int32", "data": "synthetic",
+            "config": {"workload": "create_block_mask, " + w["desc"], "list_bytes_per_build": out_bytes,
+                       "l2": "each build writes fresh output arrays" + (" larger than the 126 MB L2" if out_bytes > 126e6 else " (they fit in L2: latency-bound)")},
+            "roofline": {"bound": "hbm", "kernel": "classify_kernel + compact_kernel<0> + compact_kernel<1>", "achieved": gbs, "peak": hbm,
+                         "unit": "GB/s", "frac": gbs / hbm, "traffic": None, "peak_kind": peak_kind},
+            "gpu_launches": int(nat.lib().bma_launch_count() - launches0)}), flush=True)
+
+
 def run_ring(args, w, rank, world, local_rank, dev, dist, warmup):
     """Sequence-partition mode: forward and backward of one causal sequence set split over the ranks."""
     from jaxmodules_b200 import _native as nat, masks as M, sharding as S
@@ -308,6 +347,8 @@ def main():
     ap.add_argument("--ring", default=None, choices=["contiguous", "zigzag"],
                     help="sequence partition instead of batch x head shards: every rank holds L/N tokens of ONE sequence "
                          "set (strong scaling); K/V and the dK/dV accumulators travel round the ring")
+    ap.add_argument("--block-mask", action="store_true",
+                    help="time create_block_mask (the BlockMask builder) at the workload's geometry instead of attention")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -334,6 +375,9 @@ def main():
     warmup = max(args.warmup, 3)
     if args.ring:
         run_ring(args, w, rank, world, local_rank, dev, dist, warmup)
+        return
+    if args.block_mask:
+        run_block_mask_build(args, w, rank, world, dev, warmup)
         return
 
     B, L, H, d = w["B"], w["L"], w["H"], w["d"]

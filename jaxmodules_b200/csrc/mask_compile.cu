@@ -101,49 +101,86 @@ __device__ __forceinline__ bool interval_classify(const bma_mask_spec& s, int q0
   return true;
 }
 
-// pass 1: one warp per block.
+// pass 1a: one THREAD per block.  Interval terms and the per-block segment-id ranges decide almost every
+// block in closed form; flags leave as coalesced bytes.  The few blocks that stay open (a segment boundary,
+// a bit table or a change of the block window inside the block) are appended to a work list for pass 1b.
+// The list and its counter live in output arrays that pass 2 overwrites afterwards (`todo` = kv_idx, one
+// int32 per block at least; `todo_count` = kv_num[0]), so the scratch stays at one byte per block.
+struct BlockCoord { int cb, ch, qi, kj; };
+__device__ __forceinline__ BlockCoord block_coord(int64_t w, int CH, int NQ, int NKV) {
+  BlockCoord c;
+  const int64_t row = w / NKV;
+  c.kj = (int)(w - row * NKV);
+  uint32_t r = (uint32_t)row;
+  c.qi = (int)(r % (uint32_t)NQ);
+  r /= (uint32_t)NQ;
+  c.ch = (int)(r % (uint32_t)CH);
+  c.cb = (int)(r / (uint32_t)CH);
+  return c;
+}
+
 __global__ void classify_kernel(bma_mask_spec spec, int CB, int CH, int NQ, int NKV, int QB, int KVB,
-                                SegSummary seg, uint8_t* __restrict__ flags) {
+                                SegSummary seg, uint8_t* __restrict__ flags, int32_t* __restrict__ todo,
+                                int32_t* __restrict__ todo_count) {
+  const int lane = threadIdx.x & 31;
+  const int64_t total = (int64_t)CB * CH * NQ * NKV;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  // `base` is the warp's first block: uniform across the warp, so the ballot below sees all 32 lanes
+  for (int64_t base = (int64_t)blockIdx.x * blockDim.x + (threadIdx.x & ~31); base < total; base += stride) {
+    const int64_t w = base + lane;
+    const bool valid = w < total;
+    bool any = false, all = false, scan = false;
+    if (valid) {
+      const BlockCoord c = block_coord(w, CH, NQ, NKV);
+      const bool decided = interval_classify(spec, c.qi * QB, c.kj * KVB, QB, KVB, any, all);
+      scan = !decided;
+      if (decided && any && (spec.flags & BMA_MASK_SEGMENT)) {
+        const int qmn = seg.qmin[(int64_t)c.cb * NQ + c.qi], qmx = seg.qmax[(int64_t)c.cb * NQ + c.qi];
+        const int kmn = seg.kmin[(int64_t)c.cb * NKV + c.kj], kmx = seg.kmax[(int64_t)c.cb * NKV + c.kj];
+        if (qmx < kmn || qmn > kmx) { any = false; all = false; }          // ids never meet
+        else if (!(qmn == qmx && kmn == kmx && qmn == kmn)) {                 // a boundary crosses the block
+          if (spec.flags & BMA_MASK_COMPILE_CONSERVATIVE) all = false;        // "partial" without looking closer
+          else scan = true;
+        }
+      }
+      if (decided && any && (spec.flags & BMA_MASK_BITMAP)) scan = true;
+      flags[w] = all ? 2 : (any ? 1 : 0);   // rewritten by pass 1b when `scan`
+    }
+    const unsigned m = __ballot_sync(0xffffffffu, scan);
+    if (m != 0u) {  // one atomic per warp
+      const int leader = __ffs(m) - 1;
+      int pos = 0;
+      if (lane == leader) pos = atomicAdd(todo_count, __popc(m));
+      pos = __shfl_sync(0xffffffffu, pos, leader);
+      if (scan) todo[pos + __popc(m & ((1u << lane) - 1u))] = (int32_t)w;
+    }
+  }
+}
+
+// pass 1b: one WARP per listed block: exact any/all by evaluating the mask on every element
+// (stops as soon as the block is known to be partial).
+__global__ void scan_kernel(bma_mask_spec spec, int CH, int NQ, int NKV, int QB, int KVB, uint8_t* __restrict__ flags,
+                            const int32_t* __restrict__ todo, const int32_t* __restrict__ todo_count) {
   const int lane = threadIdx.x & 31;
   const int warps_per_cta = blockDim.x >> 5;
-  const int64_t total = (int64_t)CB * CH * NQ * NKV;
-  for (int64_t w = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5); w < total;
-       w += (int64_t)gridDim.x * warps_per_cta) {
-    const int kj = (int)(w % NKV);
-    const int qi = (int)((w / NKV) % NQ);
-    const int ch = (int)((w / ((int64_t)NKV * NQ)) % CH);
-    const int cb = (int)(w / ((int64_t)NKV * NQ * CH));
-    const int q0 = qi * QB, k0 = kj * KVB;
-
-    bool any, all;
-    bool decided = interval_classify(spec, q0, k0, QB, KVB, any, all);
-    bool scan = !decided;
-    if (decided && any && (spec.flags & BMA_MASK_SEGMENT)) {
-      const int qmn = seg.qmin[(int64_t)cb * NQ + qi], qmx = seg.qmax[(int64_t)cb * NQ + qi];
-      const int kmn = seg.kmin[(int64_t)cb * NKV + kj], kmx = seg.kmax[(int64_t)cb * NKV + kj];
-      if (qmx < kmn || qmn > kmx) { any = false; all = false; }          // ids never meet
-      else if (!(qmn == qmx && kmn == kmx && qmn == kmn)) {                 // a boundary crosses the block
-        if (spec.flags & BMA_MASK_COMPILE_CONSERVATIVE) all = false;        // "partial" without looking closer
-        else scan = true;
-      }
-    }
-    if (decided && any && (spec.flags & BMA_MASK_BITMAP)) scan = true;
-
-    if (scan) {
-      const MaskView m = make_mask_view(spec, cb, ch);
-      const int qb_end = min(q0 + QB, spec.q_valid), kb_end = min(k0 + KVB, spec.k_valid);
-      any = false;
-      all = (q0 + QB <= spec.q_valid) && (k0 + KVB <= spec.k_valid);
-      for (int q = q0; q < qb_end && !(any && !all); ++q) {
-        for (int kb = k0; kb < kb_end; kb += 32) {
-          const int k = kb + lane;
-          const bool in = k < kb_end;
-          const bool ok = in && mask_allowed(m, q, k);
-          const unsigned okb = __ballot_sync(0xffffffffu, ok);
-          const unsigned inb = __ballot_sync(0xffffffffu, in);
-          any |= (okb != 0u);
-          all &= (okb == inb);
-        }
+  const int count = *todo_count;
+  for (int i = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); i < count; i += gridDim.x * warps_per_cta) {
+    const int64_t w = todo[i];
+    const BlockCoord c = block_coord(w, CH, NQ, NKV);
+    const MaskView m = make_mask_view(spec, c.cb, c.ch);
+    const int q0 = c.qi * QB, k0 = c.kj * KVB;
+    const int qb_end = min(q0 + QB, spec.q_valid), kb_end = min(k0 + KVB, spec.k_valid);
+    bool any = false;
+    bool all = (q0 + QB <= spec.q_valid) && (k0 + KVB <= spec.k_valid);
+    for (int q = q0; q < qb_end && !(any && !all); ++q) {
+      for (int kb = k0; kb < kb_end; kb += 32) {
+        const int k = kb + lane;
+        const bool in = k < kb_end;
+        const bool ok = in && mask_allowed(m, q, k);
+        const unsigned okb = __ballot_sync(0xffffffffu, ok);
+        const unsigned inb = __ballot_sync(0xffffffffu, in);
+        any |= (okb != 0u);
+        all &= (okb == inb);
       }
     }
     if (lane == 0) flags[w] = all ? 2 : (any ? 1 : 0);
@@ -151,7 +188,7 @@ __global__ void classify_kernel(bma_mask_spec spec, int CB, int CH, int NQ, int 
 }
 
 // pass 2: one CTA per (classification row, replica chunk).  TRANSPOSED = q-side lists.
-// Shared memory: 2 index rows of `NC` int32 + scan scratch.
+// Shared memory: 2 index rows of `NC` int32, the row's `NC` flag bytes, + scan scratch.
 template <bool TRANSPOSED>
 __global__ void compact_kernel(const uint8_t* __restrict__ flags, int CB, int CH, int NQ, int NKV, int out_B,
                                int out_H, int32_t* __restrict__ part_num, int32_t* __restrict__ part_idx,
@@ -168,9 +205,12 @@ __global__ void compact_kernel(const uint8_t* __restrict__ flags, int CB, int CH
   const int ch = (blockIdx.x / NR) % CH;
   const int cb = blockIdx.x / (NR * CH);
   const uint8_t* fbase = flags + (int64_t)(cb * CH + ch) * NQ * NKV;
-  auto flag_at = [&](int c) -> int {
-    return TRANSPOSED ? fbase[(int64_t)c * NKV + r] : fbase[(int64_t)r * NKV + c];
-  };
+  // the row's flags go to shared memory first: all loads of a thread are in flight together (a column of the
+  // flag grid, for the q-side lists, is one byte per 32-byte sector), and both passes below read them twice
+  uint8_t* fl = reinterpret_cast<uint8_t*>(smem + 2 * NC);
+  for (int c = threadIdx.x; c < NC; c += kThreads) fl[c] = TRANSPOSED ? fbase[(int64_t)c * NKV + r] : fbase[(int64_t)r * NKV + c];
+  __syncthreads();
+  auto flag_at = [&](int c) -> int { return fl[c]; };
 
   const int per = (NC + kThreads - 1) / kThreads;
   const int c0 = min(NC, (int)threadIdx.x * per), c1 = min(NC, c0 + per);
@@ -300,10 +340,18 @@ int mask_compile_launch(const bma_mask_spec& spec, int B, int H, const bma_block
     count_launches(1);
   }
   {
-    const int64_t warps = (int64_t)p.CB * p.CH * l.NQ * l.NKV;
-    const int grid = (int)std::min<int64_t>((warps + 7) / 8, (int64_t)sm_count * 16);
-    classify_kernel<<<grid, kThreads, 0, st>>>(spec, p.CB, p.CH, l.NQ, l.NKV, l.q_block, l.kv_block, seg, flags);
+    const int64_t blocks = (int64_t)p.CB * p.CH * l.NQ * l.NKV;
+    const int grid = (int)std::min<int64_t>((blocks + kThreads - 1) / kThreads, (int64_t)sm_count * 16);
+    // blocks that closed forms cannot decide exist only with these terms; without them pass 1b is not launched
+    const bool may_scan = (spec.flags & (BMA_MASK_BITMAP | BMA_MASK_BLOCK_WINDOW)) ||
+                          ((spec.flags & BMA_MASK_SEGMENT) && !(spec.flags & BMA_MASK_COMPILE_CONSERVATIVE));
+    if (may_scan) BMA_CUDA_TRY(cudaMemsetAsync(l.kv_num, 0, sizeof(int32_t), st));
+    classify_kernel<<<grid, kThreads, 0, st>>>(spec, p.CB, p.CH, l.NQ, l.NKV, l.q_block, l.kv_block, seg, flags, l.kv_idx, l.kv_num);
     count_launches(1);
+    if (may_scan) {
+      scan_kernel<<<sm_count * 8, kThreads, 0, st>>>(spec, p.CH, l.NQ, l.NKV, l.q_block, l.kv_block, flags, l.kv_idx, l.kv_num);
+      count_launches(1);
+    }
   }
   auto launch_compact = [&](bool transposed) -> int {
     const int NR = transposed ? l.NKV : l.NQ, NC = transposed ? l.NQ : l.NKV;
@@ -311,7 +359,7 @@ int mask_compile_launch(const bma_mask_spec& spec, int B, int H, const bma_block
     const int reps = ((p.CB == l.B) ? 1 : l.B) * ((p.CH == l.H) ? 1 : l.H);
     int gy = std::max(1, std::min(reps, (sm_count * 4 + rows - 1) / rows));
     gy = std::min(gy, 65535);
-    const size_t smem = sizeof(int32_t) * 2 * (size_t)NC;
+    const size_t smem = sizeof(int32_t) * 2 * (size_t)NC + align_up((size_t)NC, 16);
     dim3 grid(rows, gy);
     if (transposed) {
       if (smem > 48 * 1024)
