@@ -548,6 +548,13 @@ def main():
                              "frac": (fwd_tf / sustained) if fwd_tf else None, "traffic": traffic.get("fwd")},
             "clocks": clocks, "gpu_launches": int(launches),
         }
+        pre_ms = per_kernel.get("bwd_preprocess")
+        if pre_ms and w["dtype"] == "bf16" and be == 2:
+            # delta = rowsum(dO * O) and the bf16 copy of the float32 cotangent: reads O and dO (float32), writes dO (bf16) and delta
+            pre_bytes = B * L * H * d * (4 + 4 + 2) + 4 * B * H * L
+            pre_gbs = pre_bytes / (pre_ms * 1e-3) / 1e9
+            line["roofline_preprocess"] = {"bound": "hbm", "kernel": "bwd_preprocess_rows4_kernel", "achieved": pre_gbs, "peak": hbm,
+                                           "unit": "GB/s", "frac": pre_gbs / hbm, "traffic": None}
         dkdv_ms, replay_ms = per_kernel.get("bwd_dkdv"), per_kernel.get("bwd_dq_replay")
         if dkdv_ms and replay_ms:
             # The two backward kernels timed separately (the library records an event between them).  The dK/dV kernel

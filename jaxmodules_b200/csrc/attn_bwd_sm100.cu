@@ -16,8 +16,9 @@
 //
 // Pipelining: the consumers pull St into registers and release its columns at once, so the next
 // tile's K Q^T runs under the element-wise math, and they compute the exponentials of tile n+1
-// while the MMAs of tile n run.  Pt is written over the dPt columns once every consumer has read
-// them; the next V dO^T is issued behind dV += Pt dO (MMAs of one issuing thread execute in order).
+// while the MMAs of tile n run.  Each thread writes its Pt over dPt columns that it has itself just
+// read (so the consumers never wait for one another inside a tile); the next V dO^T is issued
+// behind dV += Pt dO (MMAs of one issuing thread execute in order).
 // Warp 10 stages lse*log2e and delta of the coming q tiles in shared memory.
 //
 // With a scratch buffer (BwdParams::ds_out) the kernel also hands every dSt tile to the dQ kernel:
@@ -274,11 +275,12 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (ok) ok = mbar_wait(&sm.bar[BAR_P], ph);
         if (!ok) break;
         tc_fence_after();
-        // dV += Pt dO      (A from TMEM, 8 columns per 16-query k-step; B = dO rows as K)
+        // dV += Pt dO      (A from TMEM, 8 columns per 16-query k-step — the Pt of queries [64h, 64h+64) sits in the first 32
+        // of the 64 dPt columns its warps read; B = dO rows as K)
 #pragma unroll
         for (int ks = 0; ks < BT / 16; ++ks)
           if (leader)
-            mma_ts(tmem + COL_DV, tmem + COL_PT + ks * 8, ddom0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)), idesc_kn, (n > 0) || (ks > 0));
+            mma_ts(tmem + COL_DV, tmem + COL_PT + (ks >> 2) * 64 + (ks & 3) * 8, ddom0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)), idesc_kn, (n > 0) || (ks > 0));
         // dK += dSt Q      (A = dSt in shared memory, K-major over queries)
 #pragma unroll
         for (int ks = 0; ks < BT / 16; ++ks) {
@@ -463,14 +465,13 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           dsp[16 + j4 * 2 + 1] = pack_bf16(x1[2], x1[3]);
         }
       }
-      // every consumer holds its dPt values: Pt may now overwrite those columns
-      ok = consumer_sync(&sm.bar[BAR_SYNC2], ph);
-      // the dSt buffer is still being read by dK += dSt Q of the previous tile until BAR_D completes
-      if (ok && n > 0) ok = mbar_wait(&sm.bar[BAR_D], (n - 1) & 1);
+      // Pt goes over columns of dPt that this very thread has just read (its half's 64 columns), so the consumers need
+      // no rendezvous here.  The dSt buffer is still being read by dK += dSt Q of the previous tile until BAR_D completes.
+      if (n > 0) ok = mbar_wait(&sm.bar[BAR_D], (n - 1) & 1);
       // ... and, when dSt tiles are handed to the dQ kernel, until the bulk store of the previous one has read it
       if (ok && n > 0 && p.ds_out != nullptr) ok = mbar_wait(&sm.bar[BAR_DSR], (n - 1) & 1);
       if (!ok) break;
-      tmem_st32(tmem + COL_PT + lane_base + half * 32, pk);  // 64 queries = 32 packed columns per half
+      tmem_st32(tmem + COL_PT + lane_base + half * 64, pk);  // 64 queries = 32 packed columns, inside this half's dPt columns
       {
         // dSt row `row`, query columns [64*half, 64*half+64): eight 16-byte chunks of the 128-byte-swizzled
         // [128 keys x 64 queries] box `half`
@@ -534,7 +535,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
       fence_proxy_async();  // the TMA engine reads the staged tiles through the async proxy
-      ok = consumer_sync(&sm.bar[BAR_SYNC2], total & 1);
+      ok = consumer_sync(&sm.bar[BAR_SYNC2], 0);
       if (!ok) {
         report_device_error(p.status, 340 + warp);
       } else if (threadIdx.x == 0) {
