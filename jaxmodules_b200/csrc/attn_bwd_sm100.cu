@@ -357,6 +357,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     int h = 0, qi = 0;
     bool partial = false;
     float pr[64];  // Pt of the current tile (this thread's key row, its 64 query columns)
+    uint32_t pk[32];  // ... and its bf16 pairs, packed while the exponentials keep the MUFU pipe busy
 
     // exponentials of one tile: pull St out of TMEM, release its columns, Pt = exp2(St*c - lse2)
     auto exp_phase = [&](int n, int h_, int qi_, bool partial_) -> bool {
@@ -422,6 +423,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           pr[32 + j] = (bits[1] >> j) & 1u ? pr[32 + j] : 0.f;
         }
       }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        pk[j] = pack_bf16(pr[2 * j], pr[2 * j + 1]);
+        pk[16 + j] = pack_bf16(pr[32 + 2 * j], pr[32 + 2 * j + 1]);
+      }
       return true;
     };
 
@@ -437,12 +443,14 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       ok = mbar_wait(&sm.bar[BAR_S2], ph);
       if (!ok) break;
       tc_fence_after();
-      uint32_t pk[32], dsp[32];
+      uint32_t dsp[32];
       {
         uint32_t d0[32], d1[32];
         tmem_ld32(tmem + COL_DPT + lane_base + (half * 2) * 32, d0);
         tmem_ld32(tmem + COL_DPT + lane_base + (half * 2 + 1) * 32, d1);
         tmem_wait_ld();
+        // this thread holds its dPt values: its Pt may take their place (the store completes under the products below)
+        tmem_st32(tmem + COL_PT + lane_base + half * 64, pk);  // 64 queries = 32 packed columns, inside this half's dPt columns
 #pragma unroll
         for (int j4 = 0; j4 < 8; ++j4) {
           const float4 da = *reinterpret_cast<const float4*>(&sm.delta[st][(half * 2) * 32 + j4 * 4]);
@@ -455,10 +463,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             x0[e] = pr[j] * (__uint_as_float(d0[j]) - dav[e]);
             x1[e] = pr[32 + j] * (__uint_as_float(d1[j]) - dbv[e]);
           }
-          pk[j4 * 2] = pack_bf16(pr[j4 * 4], pr[j4 * 4 + 1]);
-          pk[j4 * 2 + 1] = pack_bf16(pr[j4 * 4 + 2], pr[j4 * 4 + 3]);
-          pk[16 + j4 * 2] = pack_bf16(pr[32 + j4 * 4], pr[32 + j4 * 4 + 1]);
-          pk[16 + j4 * 2 + 1] = pack_bf16(pr[32 + j4 * 4 + 2], pr[32 + j4 * 4 + 3]);
           dsp[j4 * 2] = pack_bf16(x0[0], x0[1]);
           dsp[j4 * 2 + 1] = pack_bf16(x0[2], x0[3]);
           dsp[16 + j4 * 2] = pack_bf16(x1[0], x1[1]);
@@ -471,7 +475,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // ... and, when dSt tiles are handed to the dQ kernel, until the bulk store of the previous one has read it
       if (ok && n > 0 && p.ds_out != nullptr) ok = mbar_wait(&sm.bar[BAR_DSR], (n - 1) & 1);
       if (!ok) break;
-      tmem_st32(tmem + COL_PT + lane_base + half * 64, pk);  // 64 queries = 32 packed columns, inside this half's dPt columns
       {
         // dSt row `row`, query columns [64*half, 64*half+64): eight 16-byte chunks of the 128-byte-swizzled
         // [128 keys x 64 queries] box `half`
