@@ -54,7 +54,7 @@ constexpr uint32_t COL_DV = 0, COL_DK = 128, COL_ST = 256, COL_DPT = 384, COL_PT
 
 enum {
   BAR_KV = 0, BAR_FULLQ0, BAR_FULLQ1, BAR_FULLDO0, BAR_FULLDO1, BAR_STAT0, BAR_STAT1,
-  BAR_S1, BAR_S2, BAR_LS, BAR_P, BAR_D, BAR_SYNC2, BAR_DSR,
+  BAR_S1, BAR_S2, BAR_LS, BAR_P, BAR_QF, BAR_D, BAR_SYNC2, BAR_DSR,
   NUM_BARS
 };
 
@@ -218,11 +218,15 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         int h, qi; bool partial;
         loader.next(h, qi, partial);
         const int st = n & 1;
-        // the stage is free once tile n-2 has been multiplied (BAR_D of n-2 has the parity of n)
-        if (n >= 2) ok = mbar_wait(&sm.bar[BAR_D], n & 1);
+        // The Q stage is free once dK += dSt Q of tile n-2 has completed (BAR_QF of n-2 has the parity of n), the dO
+        // stage once dV += Pt dO has (BAR_D).  dK is issued first: Q is the operand the next tile needs first (K Q^T),
+        // and its load is the one whose latency the two-stage ring barely covers.
+        if (n >= 2) ok = mbar_wait(&sm.bar[BAR_QF], n & 1);
         if (!ok) break;
         mbar_expect_tx(&sm.bar[BAR_FULLQ0 + st], kTileBytes);
         load_tile(&map_q, sm.q[st], &sm.bar[BAR_FULLQ0 + st], h, qi * BT);
+        if (n >= 2) ok = mbar_wait(&sm.bar[BAR_D], n & 1);
+        if (!ok) break;
         mbar_expect_tx(&sm.bar[BAR_FULLDO0 + st], kTileBytes);
         load_tile(&map_do, sm.d_o[st], &sm.bar[BAR_FULLDO0 + st], h, qi * BT);
       }
@@ -275,12 +279,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (ok) ok = mbar_wait(&sm.bar[BAR_P], ph);
         if (!ok) break;
         tc_fence_after();
-        // dV += Pt dO      (A from TMEM, 8 columns per 16-query k-step — the Pt of queries [64h, 64h+64) sits in the first 32
-        // of the 64 dPt columns its warps read; B = dO rows as K)
-#pragma unroll
-        for (int ks = 0; ks < BT / 16; ++ks)
-          if (leader)
-            mma_ts(tmem + COL_DV, tmem + COL_PT + (ks >> 2) * 64 + (ks & 3) * 8, ddom0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)), idesc_kn, (n > 0) || (ks > 0));
         // dK += dSt Q      (A = dSt in shared memory, K-major over queries)
 #pragma unroll
         for (int ks = 0; ks < BT / 16; ++ks) {
@@ -288,6 +286,13 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           if (leader)
             mma_ss(tmem + COL_DK, dds + off, dqm0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)), idesc_kn, (n > 0) || (ks > 0));
         }
+        if (leader) mma_commit(&sm.bar[BAR_QF]);  // the Q stage and the dSt buffer are free
+        // dV += Pt dO      (A from TMEM, 8 columns per 16-query k-step — the Pt of queries [64h, 64h+64) sits in the first 32
+        // of the 64 dPt columns its warps read; B = dO rows as K)
+#pragma unroll
+        for (int ks = 0; ks < BT / 16; ++ks)
+          if (leader)
+            mma_ts(tmem + COL_DV, tmem + COL_PT + (ks >> 2) * 64 + (ks & 3) * 8, ddom0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)), idesc_kn, (n > 0) || (ks > 0));
         if (leader) mma_commit(&sm.bar[BAR_D]);
         // the next dPt overwrites the columns Pt was read from; it is queued behind dV += Pt dO
         if (n + 1 < total) {
@@ -470,8 +475,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
       // Pt goes over columns of dPt that this very thread has just read (its half's 64 columns), so the consumers need
-      // no rendezvous here.  The dSt buffer is still being read by dK += dSt Q of the previous tile until BAR_D completes.
-      if (n > 0) ok = mbar_wait(&sm.bar[BAR_D], (n - 1) & 1);
+      // no rendezvous here.  The dSt buffer is still being read by dK += dSt Q of the previous tile until BAR_QF completes.
+      if (n > 0) ok = mbar_wait(&sm.bar[BAR_QF], (n - 1) & 1);
       // ... and, when dSt tiles are handed to the dQ kernel, until the bulk store of the previous one has read it
       if (ok && n > 0 && p.ds_out != nullptr) ok = mbar_wait(&sm.bar[BAR_DSR], (n - 1) & 1);
       if (!ok) break;
