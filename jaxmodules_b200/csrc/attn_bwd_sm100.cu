@@ -10,21 +10,23 @@
 //     St  = K Q^T            A = K (K-major),  B = Q  (K-major)      -> TMEM [256,384)
 //     dPt = V dO^T           A = V (K-major),  B = dO (K-major)      -> TMEM [384,512)
 //     dV += Pt dO            A = Pt (bf16 in TMEM, over dPt),  B = dO (MN-major) -> TMEM [0,128)
-//     dK += dSt Q            A = dSt (shared, K-major),        B = Q  (MN-major) -> TMEM [128,256)
+//     dK += dSt Q            A = dSt (bf16 in TMEM, over dPt), B = Q  (MN-major) -> TMEM [128,256)
 // with Pt = exp2(St*scale*log2e - lse*log2e) and dSt = Pt * (dPt - delta) computed by eight warps
 // (thread = key row; warps w and w+4 split the 128 query columns).
 //
 // Pipelining: the consumers pull St into registers and release its columns at once, so the next
 // tile's K Q^T runs under the element-wise math, and they compute the exponentials of tile n+1
-// while the MMAs of tile n run.  Each thread writes its Pt over dPt columns that it has itself just
-// read (so the consumers never wait for one another inside a tile); the next V dO^T is issued
-// behind dV += Pt dO (MMAs of one issuing thread execute in order).
+// while the MMAs of tile n run.  Each thread writes its Pt and dSt (bf16) over dPt columns that it
+// has itself just read — the 64 fp32 columns of its half hold 32 packed columns of Pt and 32 of dSt
+// — so the consumers never wait for one another, nor for a buffer, inside a tile; the next V dO^T
+// is issued behind the two accumulations (MMAs of one issuing thread execute in order).
 // Warp 10 stages lse*log2e and delta of the coming q tiles in shared memory.
 //
 // With a scratch buffer (BwdParams::ds_out) the kernel also hands every dSt tile to the dQ kernel:
-// warp 11 copies the 32 KB shared-memory image (already in MMA operand layout) to its slot in
-// global memory with one bulk store per tile, and dQ += dS K then needs no recomputation of S and
-// dP (5 instead of 7 MMAs per block for the whole backward, paid with 32 KB of HBM traffic each way).
+// each consumer thread stages its 64 dSt values as one 128-byte line of a 32 KB tile image laid out
+// like a 128-byte-swizzled MMA operand in shared memory, warp 11 sends the image to its slot with one
+// bulk store, and dQ += dS K then needs no recomputation of S and dP (5 instead of 7 MMAs per block
+// for the whole backward, paid with 32 KB of HBM traffic each way).
 // Every mbarrier wait is bounded; on a timeout the thread records an error code and unwinds.
 #include "common.cuh"
 #include "ptx_sm100.cuh"
@@ -54,7 +56,7 @@ constexpr uint32_t COL_DV = 0, COL_DK = 128, COL_ST = 256, COL_DPT = 384, COL_PT
 
 enum {
   BAR_KV = 0, BAR_FULLQ0, BAR_FULLQ1, BAR_FULLDO0, BAR_FULLDO1, BAR_STAT0, BAR_STAT1,
-  BAR_S1, BAR_S2, BAR_LS, BAR_P, BAR_QF, BAR_D, BAR_SYNC2, BAR_DSR,
+  BAR_S1, BAR_S2, BAR_LS, BAR_P, BAR_QF, BAR_D, BAR_SYNC2, BAR_STG, BAR_DSR,
   NUM_BARS
 };
 
@@ -62,7 +64,7 @@ template <int HD>
 struct __align__(1024) BwdSmem {
   uint8_t k[kTileBytesOf<HD>];
   uint8_t v[kTileBytesOf<HD>];
-  uint8_t ds[kDsBytes];
+  uint8_t ds[kDsBytes];  // staging of the dSt image for the hand-over (not an MMA operand)
   uint8_t q[2][kTileBytesOf<HD>];
   uint8_t d_o[2][kTileBytesOf<HD>];
   float lse2[2][BT];
@@ -169,7 +171,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (threadIdx.x == 0) {
     for (int i = 0; i < NUM_BARS; ++i) {
       uint32_t count = 1;
-      if (i == BAR_LS || i == BAR_P || i == BAR_SYNC2) count = kConsumers;
+      if (i == BAR_LS || i == BAR_P || i == BAR_SYNC2 || i == BAR_STG) count = kConsumers;
       if (i == BAR_STAT0 || i == BAR_STAT1) count = 32;
       mbar_init(&sm.bar[i], count);
     }
@@ -240,7 +242,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       constexpr uint32_t idesc_kn = make_idesc_bf16(BT, HD, 0, 1);  // B MN-major
       // descriptors are built once; per MMA only the 16-byte-unit start address moves
       const uint64_t dk = make_smem_desc(smem_u32(sm.k), 16, 1024), dv = make_smem_desc(smem_u32(sm.v), 16, 1024);
-      const uint64_t dds = make_smem_desc(smem_u32(sm.ds), 16, 1024);
       const uint64_t dq0 = make_smem_desc(smem_u32(sm.q[0]), 16, 1024), ddo0 = make_smem_desc(smem_u32(sm.d_o[0]), 16, 1024);
       const uint64_t dqm0 = make_smem_desc(smem_u32(sm.q[0]), kHalfTile, 1024), ddom0 = make_smem_desc(smem_u32(sm.d_o[0]), kHalfTile, 1024);
       constexpr uint32_t kStageUnits = kTileBytes >> 4;
@@ -279,14 +280,12 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (ok) ok = mbar_wait(&sm.bar[BAR_P], ph);
         if (!ok) break;
         tc_fence_after();
-        // dK += dSt Q      (A = dSt in shared memory, K-major over queries)
+        // dK += dSt Q      (A = dSt from TMEM: 8 columns per 16-query k-step, in the second 32 of the half's 64 dPt columns)
 #pragma unroll
-        for (int ks = 0; ks < BT / 16; ++ks) {
-          const uint32_t off = ((ks >> 2) * kHalfTile + (ks & 3) * 32) >> 4;
+        for (int ks = 0; ks < BT / 16; ++ks)
           if (leader)
-            mma_ss(tmem + COL_DK, dds + off, dqm0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)), idesc_kn, (n > 0) || (ks > 0));
-        }
-        if (leader) mma_commit(&sm.bar[BAR_QF]);  // the Q stage and the dSt buffer are free
+            mma_ts(tmem + COL_DK, tmem + COL_PT + (ks >> 2) * 64 + 32 + (ks & 3) * 8, dqm0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)), idesc_kn, (n > 0) || (ks > 0));
+        if (leader) mma_commit(&sm.bar[BAR_QF]);  // the Q stage is free
         // dV += Pt dO      (A from TMEM, 8 columns per 16-query k-step — the Pt of queries [64h, 64h+64) sits in the first 32
         // of the 64 dPt columns its warps read; B = dO rows as K)
 #pragma unroll
@@ -328,16 +327,16 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       if (!ok && lane == 0) report_device_error(p.status, 315);
     } else if (warp == 11 && p.ds_out != nullptr && total > 0) {
-      // ---------------------------------------------------------------- dSt hand-over to the dQ kernel
-      // BAR_P says that all consumers have written (and fenced) the dSt image of tile n; one bulk store
-      // moves it to its slot, and BAR_DSR tells the consumers that the buffer has been read.
+      // ---------------------------------------------------------------- dSt hand-over to the dQ replay kernel
+      // BAR_STG says that all consumers have staged (and fenced) the dSt image of tile n in shared memory; one
+      // bulk store moves it to its slot, and BAR_DSR tells the consumers that the buffer has been read.
       QTileIter loader(p.l, b, hk, G, kj);
       const uint64_t policy = l2_evict_first();
       bool ok = true;
       for (int n = 0; n < total && ok; ++n) {
         int h, qi; bool partial;
         loader.next(h, qi, partial);
-        ok = mbar_wait(&sm.bar[BAR_P], n & 1);
+        ok = mbar_wait(&sm.bar[BAR_STG], n & 1);
         if (!ok) break;
         if (lane == 0) {
           const int64_t slot = (((int64_t)(b - p.b0) * (p.nhk * G) + (h - p.hk0 * G)) * p.l.NQ + qi) * p.l.NKV + kj;
@@ -474,26 +473,30 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           dsp[16 + j4 * 2 + 1] = pack_bf16(x1[2], x1[3]);
         }
       }
-      // Pt goes over columns of dPt that this very thread has just read (its half's 64 columns), so the consumers need
-      // no rendezvous here.  The dSt buffer is still being read by dK += dSt Q of the previous tile until BAR_QF completes.
-      if (n > 0) ok = mbar_wait(&sm.bar[BAR_QF], (n - 1) & 1);
-      // ... and, when dSt tiles are handed to the dQ kernel, until the bulk store of the previous one has read it
-      if (ok && n > 0 && p.ds_out != nullptr) ok = mbar_wait(&sm.bar[BAR_DSR], (n - 1) & 1);
-      if (!ok) break;
-      {
-        // dSt row `row`, query columns [64*half, 64*half+64): eight 16-byte chunks of the 128-byte-swizzled
-        // [128 keys x 64 queries] box `half`
+      // Pt and dSt go over columns of dPt that this very thread has just read (its half's 64 columns: Pt in the first 32,
+      // dSt in the second 32), so the consumers need no rendezvous and no buffer to wait for.
+      tmem_st32(tmem + COL_PT + lane_base + half * 64 + 32, dsp);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&sm.bar[BAR_P]);
+      if (p.ds_out != nullptr) {
+        // Hand-over to the dQ replay kernel, off the MMAs' critical path: the thread's 64 dSt values are one 128-byte
+        // line of the tile image (key row `row`, box `half`, 16-byte chunks swizzled like an MMA operand); the image is
+        // staged in shared memory and leaves as one bulk store (warp 11).  Global stores issued by the consumer warps
+        // themselves — a line per thread, or 512 contiguous bytes per instruction after a turn through shared memory —
+        // were measured 25 % and 9 % slower for the whole kernel: 32 KB per tile is more than the load/store path of
+        // an SM absorbs without stalling the warps that issue it.
+        if (n > 0) ok = mbar_wait(&sm.bar[BAR_DSR], (n - 1) & 1);  // the previous image has been read
+        if (!ok) break;
         uint8_t* ds_row = sm.ds + half * kHalfTile + row * 128;
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           const int chunk = u ^ (row & 7);
           *reinterpret_cast<uint4*>(ds_row + chunk * 16) = make_uint4(dsp[u * 4], dsp[u * 4 + 1], dsp[u * 4 + 2], dsp[u * 4 + 3]);
         }
+        fence_proxy_async();  // the bulk store reads the image through the async proxy
+        mbar_arrive(&sm.bar[BAR_STG]);
       }
-      tmem_wait_st();
-      fence_proxy_async();  // dSt was written with ordinary stores; the MMA reads it through the async proxy
-      tc_fence_before();
-      mbar_arrive(&sm.bar[BAR_P]);
 
       // ---- exponentials of the next tile while the MMAs of this one run
       if (n + 1 < total) {
