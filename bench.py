@@ -63,10 +63,10 @@ WORKLOADS = {
 # profiles/tensor_core_kernels_c2_small.md (taken on a quarter of c2 and scaled by the units processed)
 NCU_TRAFFIC_BYTES = {
     # bwd = bwd_dkdv_kernel (read + write, the write includes 1.107 GB of dS tiles) + bwd_dq_replay_kernel (read + write)
-    "c2": {"fwd": 4 * (201.4e6 + 103.8e6), "bwd": 4 * (290.0e6 + 1183.5e6 + 1174.5e6 + 40.4e6),
-           "bwd_dkdv": 4 * (290.0e6 + 1183.5e6), "bwd_dq_replay": 4 * (1174.5e6 + 40.4e6)},
-    "c2_small": {"fwd": 201.4e6 + 103.8e6, "bwd": 290.0e6 + 1183.5e6 + 1174.5e6 + 40.4e6,
-                 "bwd_dkdv": 290.0e6 + 1183.5e6, "bwd_dq_replay": 1174.5e6 + 40.4e6},
+    "c2": {"fwd": 4 * (201.4e6 + 103.8e6), "bwd": 4 * (289.6e6 + 1183.5e6 + 1174.6e6 + 41.0e6),
+           "bwd_dkdv": 4 * (289.6e6 + 1183.5e6), "bwd_dq_replay": 4 * (1174.6e6 + 41.0e6)},
+    "c2_small": {"fwd": 201.4e6 + 103.8e6, "bwd": 289.6e6 + 1183.5e6 + 1174.6e6 + 41.0e6,
+                 "bwd_dkdv": 289.6e6 + 1183.5e6, "bwd_dq_replay": 1174.6e6 + 41.0e6},
 }
 
 
