@@ -247,7 +247,7 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
 # grow-only buffer per (device, stream), reused by every call in that stream's order.  A problem whose
 # scratch exceeds the limit runs range by range over (batch, kv head) units; when not even one unit fits
 # (32 KB x Hq/Hkv x N/128 x L/128), the dQ kernel recomputes S and dP instead.
-_scratch_limit = int(float(os.environ.get("BMA_BWD_SCRATCH_GB", "16")) * (1 << 30))   # environment override, in GiB
+_scratch_limit = int(float(os.environ.get("BMA_BWD_SCRATCH_GB", "20")) * (1 << 30))   # environment override, in GiB
 _scratch_buffers = {}
 
 
