@@ -1,4 +1,7 @@
-// Backward dQ for bf16, head dim 128, on the sm_100a tensor core (tcgen05 + TMEM + TMA).
+// Backward dQ for bf16, head dim 128 / 64, on the sm_100a tensor core (tcgen05 + TMEM + TMA): the
+// variant that recomputes S and dP.  It runs when the caller gives bma_attn_bwd no scratch buffer
+// (or one smaller than a single (batch, kv head) unit); otherwise attn_bwd_dq_replay_sm100.cu
+// computes dQ from the dS tiles that the dK/dV kernel stored.
 //
 // Query-major, the mirror image of the forward kernel: one CTA per SM works on a PAIR of 128-query
 // tiles (2p, 2p+1) of one (batch, query head) and walks the union of the kv tiles their block

@@ -1,7 +1,7 @@
 // Backward dK / dV for bf16, head dim 128, on the sm_100a tensor core (tcgen05 + TMEM + TMA).
-// (dQ is produced by the query-major kernel in attn_bwd_dq_sm100.cu; splitting the backward in
-// two keeps every accumulator in tensor memory: no global reductions, no float32 workspace, and a
-// fixed summation order.)
+// (dQ is produced by a query-major kernel — attn_bwd_dq_replay_sm100.cu from the dS tiles this
+// kernel stores, or attn_bwd_dq_sm100.cu by recomputation; splitting the backward in two keeps every
+// accumulator in tensor memory: no global reductions, no float32 workspace, and a fixed summation order.)
 //
 // One CTA per (kv tile of 128 keys, kv head, batch), one CTA per SM (all 512 TMEM columns).  K and
 // V of the tile stay in shared memory; the CTA walks the q tiles named by the q-side block lists of
