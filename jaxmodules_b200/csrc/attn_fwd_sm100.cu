@@ -403,7 +403,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       // columns at a time (two passes).  A tile without any key block must first let the Q load land.
       if (cnt == 0) ok = mbar_wait(&sm.bar[BAR_Q], 0);
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      // A row whose reference maximum never became finite has seen no allowed key: O = 0 and lse = -inf.  (Its l is
+      // not exactly 0: the polynomial exponential clamps its argument and returns 2^-126 for a masked score.)
+      const bool dead = (m_ref == -INFINITY);
+      const float inv = (l > 0.f && !dead) ? 1.f / l : 0.f;
       uint8_t* q_row = sm.q[x] + row * 128;
       uint32_t syncs = 0;
       auto rendezvous = [&]() {  // the 128 threads of this tile
@@ -476,7 +479,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       }
       if (!ok) report_device_error(p.status, 230 + warp);
       if (q < a.N && a.lse)
-        a.lse[((int64_t)b * a.Hq + h) * a.N + q] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+        a.lse[((int64_t)b * a.Hq + h) * a.N + q] = (l > 0.f && !dead) ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
     }
   }
 

@@ -238,6 +238,20 @@ def test_backward_ds_hand_over_matches_recompute(d, G, mask):
         assert (x.float() - z.float()).abs().mean() <= 2e-3
 
 
+def test_rows_without_keys_inside_a_visited_tile_bf16():
+    """More queries than keys under a band mask: the q tile where the band runs out has rows with and rows without an
+    allowed key.  The rows without must give O = 0 and lse = -inf (jaxmodules/attention.py:99-100) on the tensor-core
+    path too, whose polynomial exponential does not return an exact 0 for a masked score."""
+    N, L = 832, 383
+    Q = gen((1, N, 2, 128), 0, torch.bfloat16)
+    K, V = (gen((1, L, 1, 128), i, torch.bfloat16) for i in (1, 2))
+    O, lse = jm.masked_attention_via_map(Q.cuda(), K.cuda(), V.cuda(), mask_fn=M.sliding_window_mask(216, 42), block_size=100,
+                                         return_lse=True)
+    last = L - 1 + 216                     # last query that still sees key L-1
+    assert float(O[:, last + 1:].abs().max()) == 0.0 and bool(torch.isinf(lse[..., last + 1:]).all())
+    assert bool(torch.isfinite(lse[..., :last + 1]).all()) and float(O[:, :last + 1].abs().max()) > 0.1
+
+
 def test_full_size_properties_config2():
     """BASELINE config 2 at full size (B=8, L=4096, H=32, d=128, bf16 causal): properties that do
     not need the oracle — row 0 attends only key 0 so O[:,0] == V[:,0]; the output is a convex
