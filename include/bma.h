@@ -156,7 +156,10 @@ size_t bma_mask_compile_workspace_bytes(const bma_mask_spec* spec, int32_t B, in
  * jaxmodules/block_mask.py:454-498, 227-275, 411-451.  `B`,`H` are the mask's logical batch
  * and query-head counts; lists->B / lists->H are the extents actually written (1 only if
  * the spec does not depend on that index).  NQ = ceil(q_valid / q_block) etc. are taken
- * from `lists`; elements outside the valid box count as masked. */
+ * from `lists`; elements outside the valid box count as masked.  The output arrays double as
+ * scratch during the call (the list of blocks that need an element scan sits in kv_idx until
+ * the lists are written): they must not alias the inputs and hold no meaningful data until the
+ * call's work has completed on `stream`. */
 int bma_mask_compile(const bma_mask_spec* spec, int32_t B, int32_t H,
                      const bma_block_lists* lists, void* workspace, size_t workspace_bytes,
                      bma_stream_t stream);
