@@ -240,9 +240,11 @@ int bma_attn_fwd(const bma_attn_args* args, const bma_mask_spec* spec,
                  const bma_block_lists* lists, bma_stream_t stream);
 
 /* Backward preprocess: delta = rowsum(dO * O); when d_o_bf16 is non-NULL also writes a
- * bf16 copy of dO with the layout/strides of args->o (the cotangent arrives in float32
- * because the reference returns O in float32, jaxmodules/attention.py:173).  Part of what
- * jax.vjp derives at jaxmodules/attention.py:320-321. */
+ * bf16 copy of dO there as a DENSE [B, N, Hq, d] array (the caller allocates B*N*Hq*d bf16
+ * elements and describes it to bma_attn_bwd with strides N*Hq*d, Hq*d, d -- whatever the
+ * strides of args->o and args->d_o are).  The cotangent arrives in float32 because the
+ * reference returns O in float32, jaxmodules/attention.py:173.  Part of what jax.vjp
+ * derives at jaxmodules/attention.py:320-321. */
 int bma_attn_bwd_preprocess(const bma_attn_args* args, void* d_o_bf16, bma_stream_t stream);
 
 /* Scratch bytes bma_attn_bwd needs.  Currently 0 for every backend (all gradients are

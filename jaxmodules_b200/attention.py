@@ -113,9 +113,9 @@ def _stream(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def plan(Q, K, V, backend=nat.BMA_BACKEND_AUTO, backward: bool = False, key_bias=None):
+def plan(Q, K, V, backend=nat.BMA_BACKEND_AUTO, backward: bool = False, key_bias=None, scale=None):
     """(backend, q_tile, kv_tile) the library will use for the forward (or backward) pass."""
-    a = _make_args(Q, K, V, backend, key_bias=key_bias)
+    a = _make_args(Q, K, V, backend, scale, key_bias)
     be, tq, tk = C.c_int32(), C.c_int32(), C.c_int32()
     fn = nat.lib().bma_attn_bwd_plan if backward else nat.lib().bma_attn_plan
     nat.check(fn(C.byref(a), C.byref(be), C.byref(tq), C.byref(tk)), "bma_attn_plan")
@@ -145,6 +145,31 @@ class _Span:
 
 _profile_sink = None
 
+# Every wait inside the tensor-core kernels is bounded; a wait that gives up writes a code to a status word on
+# the device and the kernel unwinds, leaving wrong results behind a BMA_OK launch.  Reading the word costs a
+# stream synchronisation, so the hot path does not do it: call ``device_status`` wherever the stream is
+# synchronised anyway (tests and the benchmark do), or set BMA_CHECK_STATUS=1 to check after every launch group.
+_check_status = os.environ.get("BMA_CHECK_STATUS", "0") not in ("", "0")
+
+
+def device_status(device=None) -> int:
+    """Reads and clears the status word of ``device`` (synchronises its current stream).  0 = no bounded wait
+    or bounds check inside a kernel has given up since the last read; otherwise the code of the first that did."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        code = C.c_int32()
+        rc = nat.lib().bma_device_status(_stream(dev), C.byref(code))
+        if rc not in (nat.BMA_OK, nat.BMA_ERR_DEVICE_CHECK):
+            nat.check(rc, "bma_device_status")
+        return int(code.value)
+
+
+def _maybe_check_status(dev, where):
+    if _check_status:
+        code = device_status(dev)
+        if code:
+            raise RuntimeError(f"{where}: a bounded wait inside a kernel gave up (device status {code}); results are invalid")
+
 
 def set_profile_sink(sink):
     """Install (or remove with None) a dict that collects (start, end) CUDA event pairs per
@@ -168,10 +193,10 @@ def attention_forward(Q, K, V, terms: _masks.MaskTerms, *, out_dtype=torch.float
     L = K.shape[1]
     with torch.cuda.device(dev):
         a = _make_args(Q, K, V, backend, scale, key_bias)
-        be, tq, tk = plan(Q, K, V, backend, key_bias=key_bias)
+        be, tq, tk = plan(Q, K, V, backend, key_bias=key_bias, scale=scale)
         dmask = _masks.to_device_mask(terms, N, L, dev)
         # when the backward pass will walk the same tile size, build its q-side lists in the same launches
-        both_sides = need_q_side and plan(Q, K, V, backend, backward=True, key_bias=key_bias)[1:] == (tq, tk)
+        both_sides = need_q_side and plan(Q, K, V, backend, backward=True, key_bias=key_bias, scale=scale)[1:] == (tq, tk)
         with _Span(_profile_sink, "mask_compile", dev):
             ready = lists_fn(tq, tk, both_sides) if lists_fn is not None else None
             lists, lt = ready if ready is not None else compile_block_lists(dmask, B, Hq, N, L, tq, tk, dev, q_side=both_sides, conservative=True)
@@ -180,6 +205,7 @@ def attention_forward(Q, K, V, terms: _masks.MaskTerms, *, out_dtype=torch.float
         a.o, a.lse = _tensor(O), lse.data_ptr()
         with _Span(_profile_sink, "fwd", dev):
             nat.check(lib.bma_attn_fwd(C.byref(a), C.byref(dmask.spec), C.byref(lists), _stream(dev)), "bma_attn_fwd")
+        _maybe_check_status(dev, "bma_attn_fwd")
     ctx = dict(dmask=dmask, lists=lists, list_tensors=lt, backend=be, scale=scale, lists_fn=lists_fn,
                lists_tile=(tq, tk), lists_have_q_side=both_sides, key_bias=key_bias)
     return O, lse, ctx
@@ -193,7 +219,7 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
     L = K.shape[1]
     with torch.cuda.device(dev):
         a = _make_args(Q, K, V, backend, ctx.get("scale"), ctx.get("key_bias"))
-        be, tq, tk = plan(Q, K, V, backend, backward=True, key_bias=ctx.get("key_bias"))
+        be, tq, tk = plan(Q, K, V, backend, backward=True, key_bias=ctx.get("key_bias"), scale=ctx.get("scale"))
         with _Span(_profile_sink, "mask_compile_bwd", dev):
             if ctx.get("lists_have_q_side") and ctx.get("lists_tile") == (tq, tk):
                 lists, lt = ctx["lists"], ctx["list_tensors"]      # built by the forward pass
@@ -237,6 +263,7 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
         with _Span(_profile_sink, "bwd", dev) as span:
             nat.check(lib.bma_attn_bwd(C.byref(a), C.byref(ctx["dmask"].spec), C.byref(lists), ws.data_ptr(), ws_bytes, st),
                       "bma_attn_bwd")
+        _maybe_check_status(dev, "bma_attn_bwd")
         if mid is not None:
             _profile_sink.setdefault("bwd_dkdv", []).append((span.t0, mid))
             _profile_sink.setdefault("bwd_dq_replay" if scratch > 0 else "bwd_dq_recompute", []).append((mid, span.t1))

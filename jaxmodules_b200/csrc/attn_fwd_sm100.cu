@@ -92,7 +92,10 @@ __device__ __forceinline__ void row_interval(const MaskView& m, int q, int k0, i
   jhi = min(hi - m.k_offset, m.k_valid - 1) - k0;
 }
 
-// KB: the per-head key bias (bma_attn_args.key_bias) is compiled in only where it is used
+// KB: the variant that folds the scale (and the per-head key bias, bma_attn_args.key_bias, when there is one)
+// into the scores BEFORE the running maximum is taken.  Compiled in only where it is needed: a key bias, or a
+// negative scale, for which max(raw score) * scale is the MINIMUM of the scaled scores and the exponentials
+// taken against it would overflow.
 template <int HD, bool KB>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -273,7 +276,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tmem_s = tmem + x * 128 + lane_base, tmem_o = tmem + 256 + x * 128 + lane_base;
     const MaskView mv = make_mask_view(p.spec, b, h);
-    const float kb2 = KB ? __ldg(a.key_bias + h) * kLog2e : 0.f;  // per-head key bias, log2 units
+    const float kb2 = (KB && a.key_bias) ? __ldg(a.key_bias + h) * kLog2e : 0.f;  // per-head key bias, log2 units
     float m_ref = -INFINITY;  // reference max (log2 domain) the exponentials are taken against
     float l = 0.f;
     bool ok = true;
@@ -590,8 +593,9 @@ int sm100_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
     kernel<<<grid, kThreads, smem, st>>>(mq, mk, mv, mo, p);
     return BMA_OK;
   };
-  if (a.d == 128) rc = a.key_bias ? launch(fwd_kernel<128, true>, sizeof(FwdSmem<128>)) : launch(fwd_kernel<128, false>, sizeof(FwdSmem<128>));
-  else rc = a.key_bias ? launch(fwd_kernel<64, true>, sizeof(FwdSmem<64>)) : launch(fwd_kernel<64, false>, sizeof(FwdSmem<64>));
+  const bool kb = a.key_bias != nullptr || a.scale < 0.f;
+  if (a.d == 128) rc = kb ? launch(fwd_kernel<128, true>, sizeof(FwdSmem<128>)) : launch(fwd_kernel<128, false>, sizeof(FwdSmem<128>));
+  else rc = kb ? launch(fwd_kernel<64, true>, sizeof(FwdSmem<64>)) : launch(fwd_kernel<64, false>, sizeof(FwdSmem<64>));
   if (rc) return rc;
   count_launches(1);
   BMA_CUDA_TRY(cudaGetLastError());

@@ -193,8 +193,11 @@ def flex_route(block_mask: Optional[BlockMask], B: int, Hq: int, tiles, device) 
     return "terms" if _lists_match_terms(block_mask, terms, B, Hq, device) else "table"
 
 
-def score_mod_affine(score_mod: Callable, B: int, Hq: int, L: int, S: int):
-    """(a, w) with ``score_mod(score, b, h, q, k) == a * score + w[h] * k + (terms constant along k)``.
+def score_mod_affine(score_mod: Callable, B: int, H: int, L: int, S: int):
+    """(a, w) with ``score_mod(score, b, h, q, k) == a * score + w[h] * k + (terms constant along k)``
+    for ``h`` in ``range(H)``.  The reference calls score_mod with the KV-head index
+    (jaxmodules/attention.py:543-554: ``score_mod(score, b, h, ...)`` inside the loop over kv heads),
+    so ``flex_attention`` probes ``H = Hkv`` heads and repeats ``w`` over each query-head group.
 
     Terms that do not vary with the key index cancel in the softmax, so such a score_mod — ALiBi
     ``score + slope[h] * (k - q)``, the relative-position bias of the reference's
@@ -207,9 +210,9 @@ def score_mod_affine(score_mod: Callable, B: int, Hq: int, L: int, S: int):
         return float(score_mod(np.float64(s), b, h, q, k))
     qs = sorted({0, L // 3, L - 1})
     ks = sorted({0, S // 2, S - 1}) if S > 2 else list(range(S))
-    a_ref, w = None, np.zeros(Hq, dtype=np.float64)
+    a_ref, w = None, np.zeros(H, dtype=np.float64)
     for b in sorted({0, B - 1}):
-        for h in range(Hq):
+        for h in range(H):
             base = f(0.0, b, h, qs[0], ks[0])
             a = f(1.0, b, h, qs[0], ks[0]) - base
             slope = (f(0.0, b, h, qs[0], ks[-1]) - base) / (ks[-1] - ks[0]) if len(ks) > 1 else 0.0
@@ -241,8 +244,10 @@ def flex_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, 
     (``out_dtype=torch.bfloat16`` halves the output traffic).  Differentiable in query, key and
     value.  Shape checks and their messages follow jaxmodules/attention.py:501-531;
     ``return_lse`` raises NotImplementedError as there (:491-492).  ``score_mod``: functions of the form
-    ``a * score + w[h] * k_idx + (terms constant along k_idx)`` (see ``score_mod_affine``) run on the FP32
-    SIMT kernels; others raise NotImplementedError."""
+    ``a * score + w[h] * k_idx + (terms constant along k_idx)`` (see ``score_mod_affine``; ``h`` is the kv-head
+    index, as in the reference) run on the same kernels as a logit scale plus a per-head key bias — a
+    compile-time variant of the tcgen05 kernels for bf16, the SIMT kernels for float32; others raise
+    NotImplementedError."""
     if return_lse:
         raise NotImplementedError("return_lse is not supported yet")
     if query.ndim != 4 or key.ndim != 4 or value.ndim != 4:
@@ -268,7 +273,8 @@ def flex_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, 
     if block_mask is not None:
         if block_mask.B not in (1, B) or block_mask.H not in (1, Hq):
             raise ValueError("block_mask batch / head extents must be 1 or match the query")
-    affine = None if score_mod is None else score_mod_affine(score_mod, B, Hq, L, S)   # raises for other forms
+    # score_mod sees the kv-head index, like the reference (:543-554); raises for other forms
+    affine = None if score_mod is None else score_mod_affine(score_mod, B, Hkv, L, S)
     if not (query.is_cuda and key.is_cuda and value.is_cuda):
         raise RuntimeError("flex_attention needs CUDA tensors; there is no CPU path")
     if query.dtype not in (torch.float32, torch.bfloat16) or key.dtype != query.dtype or value.dtype != query.dtype:
@@ -281,8 +287,8 @@ def flex_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, 
     key_bias = None
     if affine is not None:
         scale = affine[0] * (1.0 / math.sqrt(E) if scale is None else float(scale))
-        if np.any(affine[1] != 0.0):
-            key_bias = torch.from_numpy(affine[1].astype(np.float32)).to(dev)
+        if np.any(affine[1] != 0.0):   # the kernels index the bias with the query head: hq = hkv * G + g
+            key_bias = torch.from_numpy(np.repeat(affine[1], Hq // Hkv).astype(np.float32)).to(dev)
     with torch.cuda.device(dev):
         if block_mask is None:
             terms = _masks.MaskTerms()

@@ -29,3 +29,18 @@ MASKS = {
 @pytest.fixture(scope="session")
 def named_masks():
     return MASKS
+
+
+@pytest.fixture(autouse=True)
+def _device_status_is_clean(request):
+    """After every GPU test: no kernel may have given up a bounded wait (the status word the kernels
+    write instead of hanging).  A test that provokes a time-out on purpose reads the word itself."""
+    yield
+    if request.node.get_closest_marker("gpu") is None:
+        return
+    import torch
+    if not torch.cuda.is_available():
+        return
+    from jaxmodules_b200 import attention as A
+    code = A.device_status()          # the current device: the one the single-process tests run on
+    assert code == 0, f"a kernel reported status {code} during {request.node.name}"

@@ -123,6 +123,21 @@ def test_score_mod_affine():
             close(x, r, dtype)
 
 
+def test_score_mod_sees_the_kv_head_under_gqa():
+    """enable_gqa with a head-dependent score_mod: the reference calls score_mod with the KV-head index
+    (jaxmodules/attention.py:543-554), so ``slopes`` has one entry per kv head and every query head of a
+    group gets its group's slope.  Checked against the flex oracle, which applies score_mod per element."""
+    for dtype, e, l in ((torch.float32, 32, 64), (torch.bfloat16, 128, 256)):
+        hq, hkv = 4, 2
+        q, k, v = qkv(21, hq=hq, hkv=hkv, l=l, e=e, b=2, dtype=dtype)
+        slopes = [0.25, 0.03125]                       # len == Hkv: indexing it with a query head would raise
+        alibi = lambda score, b_, h_, qi, ki: score + slopes[h_] * (ki - qi)
+        bm = jm.create_block_mask(M.causal_mask(), 1, 1, l, l, 64 if l == 64 else 128)
+        got = flex_attention(q, k, v, score_mod=alibi, block_mask=bm, enable_gqa=True)
+        want = flex_attention_oracle(q, k, v, score_mod=alibi, block_mask=bm, enable_gqa=True)
+        close(got, want, dtype)
+
+
 def dense_reference_grads(q, k, v, dense, d_out, scale=None):
     """float64 autograd through the dense softmax with the element mask ``dense`` [B,Hq,L,S]."""
     q, k, v = (t.double().cpu().requires_grad_(True) for t in (q, k, v))

@@ -1,6 +1,6 @@
-"""Seeded random shapes on the tensor-core path against the exact-FP32 SIMT kernels: ragged and
-rectangular lengths, odd numbers of tiles, GQA groups, both head dimensions, every structured mask
-family, with the backward scratch whole, split into ranges, and absent."""
+"""Seeded random shapes on the tensor-core path against the float64 dense oracle and against the
+exact-FP32 SIMT kernels: ragged and rectangular lengths, odd numbers of tiles, GQA groups, both head
+dimensions, every structured mask family, with the backward scratch whole, split into ranges, and absent."""
 import numpy as np
 import pytest
 import torch
@@ -9,6 +9,7 @@ import jaxmodules_b200 as jm
 from jaxmodules_b200 import _native as nat
 from jaxmodules_b200 import attention as A
 from jaxmodules_b200 import masks as M
+from oracle import attention_oracle as ao
 
 pytestmark = pytest.mark.gpu
 
@@ -64,6 +65,12 @@ def test_random_shape_matches_exact_kernels(seed):
     finally:
         A.set_backward_scratch_limit(limit)
     want = _run(Q, K, V, dO, backend=nat.BMA_BACKEND_SIMT, **c["kw"])
+    ref = ao.masked_attention_dense(Q.float().numpy(), K.float().numpy(), V.float().numpy(), dO=dO.numpy(), **c["kw"])
+    for name, x in zip(("O", "dQ", "dK", "dV"), got):      # the oracle: same bounds as below
+        y = torch.from_numpy(ref[name]).float()
+        err = (x - y).abs()
+        assert float((err / y.abs().clamp(min=1.0)).max()) <= 2e-2 and float(err.mean()) <= 2e-3 * (1.0 + float(y.abs().mean())), \
+            f"{c}: {name} against the oracle: max {float(err.max()):.3e} mean {float(err.mean()):.3e}"
     for name, x, y in zip(("O", "dQ", "dK", "dV"), got, want):
         assert torch.isfinite(x).all(), f"{c}: {name} not finite"
         err = (x - y).abs()
