@@ -59,15 +59,20 @@ WORKLOADS = {
 }
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
-# profiles/tensor_core_kernels_c2_small.md (taken on a quarter of c2 and scaled by the units processed)
-NCU_TRAFFIC_BYTES = {
-    # bwd = bwd_dkdv_kernel (read + write, the write includes 1.107 GB of dS tiles) + bwd_dq_replay_kernel (read + write)
-    "c2": {"fwd": 4 * (201.4e6 + 103.8e6), "bwd": 4 * (289.6e6 + 1183.5e6 + 1174.6e6 + 41.0e6),
-           "bwd_dkdv": 4 * (289.6e6 + 1183.5e6), "bwd_dq_replay": 4 * (1174.6e6 + 41.0e6)},
-    "c2_small": {"fwd": 201.4e6 + 103.8e6, "bwd": 289.6e6 + 1183.5e6 + 1174.6e6 + 41.0e6,
-                 "bwd_dkdv": 289.6e6 + 1183.5e6, "bwd_dq_replay": 1174.6e6 + 41.0e6},
-}
+def ncu_traffic(workload):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch and kernel, from an ncu capture of the
+    quarter-size workload (c2_small), kept as JSON beside the capture's summary.  The full-size shape is the
+    captured one times four: every input is read once and every output written once, so traffic grows with the
+    units processed.  Workloads without a capture report null."""
+    try:
+        table = json.loads((ROOT / "profiles" / "ncu_dram_traffic.json").read_text())
+    except (OSError, ValueError):
+        return {}
+    entry = table.get("workloads", {}).get(workload)
+    if entry is None:
+        return {}
+    base = table["captures"][entry["capture"]]
+    return {k: v * entry["scale"] for k, v in base.items()}
 
 
 def synth(shape, seed, dtype, scale=1.0, device="cpu", pin=False):
@@ -214,6 +219,208 @@ def cpu_reference_run(w, steps, warmup, threads=None):
                        f"which visits every block; FLOPs counted on the {blocks} non-empty blocks only)")
 
 
+def device_randn(shape, seed, dtype, scale, dev):
+    """Seeded N(0,1) inputs generated on the device (the side workloads of ``extra``; the headline workload
+    uses the configs' NumPy PCG64 definition through pinned host memory)."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    x = torch.randn(shape, device=dev, generator=g)
+    if scale != 1.0:
+        x.mul_(scale)
+    return x.to(dtype)
+
+
+def dense_fp32_slice(q, k, v, do, allowed, scale, chunk=2048):
+    """float32 attention of one (batch, head) slice on the GPU, written out densely in query chunks (torch
+    float32 matmul, TF32 off): O, dQ, dK, dV from P = exp(s - lse), delta = rowsum(dO*O), dS = P*(dO V^T - delta)."""
+    N, L = q.shape[0], k.shape[0]
+    O, dQ = torch.empty_like(q), torch.empty_like(q)
+    dK, dV = torch.zeros_like(k), torch.zeros_like(v)
+    ki = torch.arange(L, device=q.device)[None, :]
+    for q0 in range(0, N, chunk):
+        sl = slice(q0, min(N, q0 + chunk))
+        qi = torch.arange(sl.start, sl.stop, device=q.device)[:, None]
+        s = (q[sl] @ k.T) * scale
+        s.masked_fill_(~allowed(qi, ki), float("-inf"))
+        lse = torch.logsumexp(s, dim=-1)
+        p = torch.exp(s - torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)[:, None])
+        o = p @ v
+        ds = p * (do[sl] @ v.T - (do[sl] * o).sum(dim=-1, keepdim=True))
+        O[sl], dQ[sl] = o, (ds @ k) * scale
+        dK += (ds.T @ q[sl]) * scale
+        dV += p.T @ do[sl]
+        del s, p, ds
+    return dict(O=O, dQ=dQ, dK=dK, dV=dV)
+
+
+def dense_predicate(w, seg):
+    if w["mask"] == "causal":
+        return lambda b: (lambda qi, ki: ki <= qi)
+    if w["mask"] == "sliding256":
+        return lambda b: (lambda qi, ki: (ki >= qi - 256) & (ki <= qi + 256))
+    return lambda b: (lambda qi, ki: (seg[b][qi] == seg[b][ki]) & (ki <= qi))
+
+
+def parity_of_slices(w, Q, K, V, dO, O, grads, seg=None, flex=False):
+    """Observed max / mean absolute error of O, dQ, dK, dV on two (batch, head) slices of the benchmarked
+    workload against the dense float32 attention of the same slice (slices are independent)."""
+    B, H, d = w["B"], w["H"], w["d"]
+    pick = (lambda t, b, h: t[b, h]) if flex else (lambda t, b, h: t[b, :, h])
+    pred = dense_predicate(w, None if seg is None else torch.from_numpy(seg).to(Q.device))
+    out = {}
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        for b, h in ((0, 0), (B - 1, H - 1)):
+            ref = dense_fp32_slice(pick(Q, b, h).detach().float(), pick(K, b, h).detach().float(), pick(V, b, h).detach().float(),
+                                   pick(dO, b, h).float(), pred(b), 1 / math.sqrt(d))
+            for name, got in zip(("O", "dQ", "dK", "dV"), (O,) + tuple(grads)):
+                err = (pick(got, b, h).detach().float() - ref[name]).abs()
+                e = out.setdefault(name, {"max_abs": 0.0, "mean_abs": 0.0, "ref_max_abs": 0.0})
+                e["max_abs"] = max(e["max_abs"], float(err.max()))
+                e["mean_abs"] = max(e["mean_abs"], float(err.mean()))
+                e["ref_max_abs"] = max(e["ref_max_abs"], float(ref[name].abs().max()))
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    out["against"] = "dense float32 torch attention of the slices (b,h) = (0,0) and (B-1,H-1); worst of the two"
+    out["bound"] = "max-abs 2e-2, mean-abs 2e-3 (bf16 I/O)" if w["dtype"] == "bf16" else "max-abs 1e-4 (fp32 I/O)"
+    return out
+
+
+def measure_config(name, dev, steps=5, warmup=3, seed=100):
+    """One side workload, device-timed: forward + backward through masked_attention_via_map on inputs generated
+    on the device; the launch groups are timed separately with CUDA events on the launching stream."""
+    import jaxmodules_b200 as jm
+    from jaxmodules_b200 import _native as nat, attention as A, masks as M
+    from jaxmodules_b200.block_mask import compile_block_lists
+    w = WORKLOADS[name]
+    B, L, H, d = w["B"], w["L"], w["H"], w["d"]
+    dt = torch_dtype(w["dtype"])
+    scale = 1 / math.sqrt(d) if w["qkv_scale"] == "rsqrt_d" else 1.0
+    Q, K, V = (device_randn((B, L, H, d), seed + i, dt, scale, dev).requires_grad_(True) for i in range(3))
+    dO = device_randn((B, L, H, d), seed + 3, torch.float32, 1.0, dev)
+    kw = mask_kwargs(w, M)
+    be, tq, tk = A.plan(Q, K, V)
+    terms = M.MaskTerms(causal=True) if kw.get("is_causal") else M.terms_from_mask_fn(kw["mask_fn"], B, H, L, L)
+    if kw.get("window_size") is not None:
+        bs = w["bs"]
+        terms = terms.merged(M.MaskTerms(window=(bs, (kw["window_size"][0] + bs - 1) // bs, 1 + (kw["window_size"][1] + bs - 1) // bs, L // bs)))
+    _, lt = compile_block_lists(M.to_device_mask(terms, L, L, dev), B, H, L, L, tq, tk, dev, q_side=False)
+    fwd_flops, step_flops, blocks = flops_of(lt, tq, d, B, H)
+
+    def step():
+        O = jm.masked_attention_via_map(Q, K, V, **kw)
+        Q.grad = K.grad = V.grad = None
+        O.backward(dO)
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize(dev)
+    sink = {}
+    A.set_profile_sink(sink)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        step()
+    t1.record()
+    torch.cuda.synchronize(dev)
+    A.set_profile_sink(None)
+    ms = t0.elapsed_time(t1) / steps
+    per = {k: float(np.mean([a.elapsed_time(b) for a, b in v])) for k, v in sink.items()}
+    _, burst, _, _ = peaks()
+    tf = lambda fl, t: fl / (t * 1e-3) / 1e12 if t else None
+    out = {"workload": w["desc"], "backend": {1: "simt", 2: "tcgen05"}.get(be, str(be)), "steps": steps, "warmup": warmup,
+           "nonempty_blocks": blocks, "ms_per_step": ms, "value": tf(step_flops, ms), "fwd_tflops": tf(fwd_flops, per.get("fwd")),
+           "bwd_tflops": tf(step_flops - fwd_flops, per.get("bwd")), "kernel_ms": per, "status": A.device_status(dev)}
+    if be == 2:
+        out["frac_of_burst"] = {"value": out["value"] / burst, "fwd": out["fwd_tflops"] / burst, "bwd": out["bwd_tflops"] / burst}
+    else:
+        out["us_per_step"] = ms * 1e3      # latency-bound shapes
+    del Q, K, V, dO
+    torch.cuda.empty_cache()
+    return out
+
+
+def block_mask_build_entry(w, dev, steps, warmup):
+    """create_block_mask alone (full [B, H] extents, both list sides): HBM-write bound."""
+    import jaxmodules_b200 as jm
+    from jaxmodules_b200 import masks as M
+    B, L, H, bs = w["B"], w["L"], w["H"], w["bs"]
+    if w["mask"] == "causal":
+        mask_mod = M.causal_mask()
+    elif w["mask"] == "sliding256":
+        mask_mod = M.sliding_window_mask(256, 256)
+    else:
+        mask_mod = M.document_mask(document_segments(B, L), causal=True)
+    build = lambda: jm.create_block_mask(mask_mod, B, H, L, L, bs, device=dev)
+    for _ in range(warmup):
+        build()
+    torch.cuda.synchronize(dev)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        build()
+    t1.record()
+    torch.cuda.synchronize(dev)
+    ms = t0.elapsed_time(t1) / steps
+    NQ = NKV = L // bs
+    out_bytes = 2 * 4 * (2 * B * H * NQ + 2 * B * H * NQ * NKV)
+    _, _, hbm, peak_kind = peaks()
+    gbs = out_bytes / (ms * 1e-3) / 1e9
+    torch.cuda.empty_cache()
+    return {"workload": "create_block_mask, " + w["desc"], "ms": ms, "list_bytes_per_build": out_bytes, "GB/s": gbs,
+            "frac_of_hbm": gbs / hbm, "peak": hbm, "peak_kind": peak_kind,
+            "kernels": "classify_kernel + compact_kernel<0> + compact_kernel<1>"}
+
+
+def c5_head_shards(rank, world, dev, dist, steps=3, warmup=2):
+    """BASELINE config 5 split by head: each rank takes H/N heads of the ONE B=1 sequence (strong scaling, no
+    collective on the data path); value = the whole sequence's FLOPs / max-over-ranks step time."""
+    import jaxmodules_b200 as jm
+    from jaxmodules_b200 import sharding as S
+    w = WORKLOADS["c5"]
+    B, L, H, d = w["B"], w["L"], w["H"], w["d"]
+    units = S.shard_units(B, H, rank, world)
+    shards = []
+    for b, h0, h1 in units:      # this rank's heads only are ever materialised
+        q, k, v = (device_randn((1, L, h1 - h0, d), 1000 * (b * H + h0) + i, torch.bfloat16, 1.0, dev).requires_grad_(True) for i in range(3))
+        shards.append((q, k, v, device_randn((1, L, h1 - h0, d), 1000 * (b * H + h0) + 3, torch.float32, 1.0, dev)))
+
+    def step():
+        for q, k, v, do in shards:
+            o = jm.masked_attention_via_map(q, k, v, is_causal=True, block_size=w["bs"])
+            q.grad = k.grad = v.grad = None
+            o.backward(do)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(warmup):
+        step()
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        step()
+    t1.record()
+    barrier()
+    ms = t0.elapsed_time(t1) / steps
+    if dist is not None:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    nblk = L // 128
+    flops = 3.5 * 4.0 * 128 * 128 * d * (B * H * nblk * (nblk + 1) // 2)
+    del shards
+    torch.cuda.empty_cache()
+    _, burst, _, _ = peaks()
+    tfl = flops / (ms * 1e-3) / 1e12
+    return {"workload": w["desc"], "parallelism": f"{H} heads of one sequence dealt to {world} GPU(s) (sharding.shard_units), no collective",
+            "scaling": "strong", "heads_per_gpu": [h1 - h0 for _, h0, h1 in units], "steps": steps, "warmup": warmup, "ms_per_step": ms, "value": tfl,
+            "per_gpu": tfl / world, "frac_of_burst_per_gpu": tfl / world / burst}
+
+
 def run_reference(args, w, rank):
     if rank != 0:
         return
@@ -231,56 +438,36 @@ def run_reference(args, w, rank):
 
 
 def run_block_mask_build(args, w, rank, world, dev, warmup):
-    """The BlockMask builder alone: create_block_mask with full [B, H] extents, as the reference's
-    create_block_mask returns them.  HBM-write bound: both list sides are 4*(2*B*H*NQ + 2*B*H*NQ*NKV) bytes each."""
-    import jaxmodules_b200 as jm
-    from jaxmodules_b200 import _native as nat, masks as M
-    B, L, H, bs = w["B"], w["L"], w["H"], w["bs"]
-    if w["mask"] == "causal":
-        mask_mod = M.causal_mask()
-    elif w["mask"] == "sliding256":
-        mask_mod = M.sliding_window_mask(256, 256)
-    else:
-        mask_mod = M.document_mask(document_segments(B, L), causal=True)
-    build = lambda: jm.create_block_mask(mask_mod, B, H, L, L, bs, device=dev)
-    for _ in range(warmup):
-        bm = build()
-    torch.cuda.synchronize(dev)
+    """``--block-mask``: the BlockMask builder alone, as its own JSON line."""
+    from jaxmodules_b200 import _native as nat
     launches0 = nat.lib().bma_launch_count()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(args.steps):
-        bm = build()
-    t1.record()
-    torch.cuda.synchronize(dev)
-    ms = t0.elapsed_time(t1) / args.steps
-    NQ = NKV = L // bs
-    out_bytes = 2 * 4 * (2 * B * H * NQ + 2 * B * H * NQ * NKV)
-    _, _, hbm, peak_kind = peaks()
-    gbs = out_bytes / (ms * 1e-3) / 1e9
+    e = block_mask_build_entry(w, dev, args.steps, warmup)
     if rank == 0:
         print(json.dumps({
-            "metric": "block_mask_build_bandwidth", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
-            "ms_per_step": ms, "higher_is_better": True, "dtype": "int32", "data": "synthetic",
-            "config": {"workload": "create_block_mask, " + w["desc"], "list_bytes_per_build": out_bytes,
-                       "l2": "each build writes fresh output arrays" + (" larger than the 126 MB L2" if out_bytes > 126e6 else " (they fit in L2: latency-bound)")},
-            "roofline": {"bound": "hbm", "kernel": "classify_kernel + compact_kernel<0> + compact_kernel<1>", "achieved": gbs, "peak": hbm,
-                         "unit": "GB/s", "frac": gbs / hbm, "traffic": None, "peak_kind": peak_kind},
+            "metric": "block_mask_build_bandwidth", "value": e["GB/s"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": e["ms"], "higher_is_better": True, "dtype": "int32", "data": "synthetic",
+            "config": {"workload": e["workload"], "list_bytes_per_build": e["list_bytes_per_build"],
+                       "l2": "each build writes fresh output arrays" + (" larger than the 126 MB L2" if e["list_bytes_per_build"] > 126e6 else " (they fit in L2: latency-bound)")},
+            "roofline": {"bound": "hbm", "kernel": e["kernels"], "achieved": e["GB/s"], "peak": e["peak"],
+                         "unit": "GB/s", "frac": e["frac_of_hbm"], "traffic": None, "peak_kind": e["peak_kind"]},
             "gpu_launches": int(nat.lib().bma_launch_count() - launches0)}), flush=True)
 
 
-def run_ring(args, w, rank, world, local_rank, dev, dist, warmup):
-    """Sequence-partition mode: forward and backward of one causal sequence set split over the ranks."""
+def ring_entry(w, rank, world, local_rank, dev, dist, steps, warmup, ring="zigzag", sample_clocks=True):
+    """Sequence-partition mode: forward and backward of ONE causal sequence set split over the ranks
+    (strong scaling); K/V and the dK/dV accumulators travel round the ring over NCCL P2P.  Returns the
+    result line (meaningful on rank 0)."""
     from jaxmodules_b200 import _native as nat, masks as M, sharding as S
     B, L, H, d = w["B"], w["L"], w["H"], w["d"]
     assert w["mask"] == "causal" and L % (2 * world * 128) == 0
     dt = torch_dtype(w["dtype"])
     n = L // world
     scale = 1 / math.sqrt(d) if w["qkv_scale"] == "rsqrt_d" else 1.0
-    Q, K, V = (synth((B, n, H, d), 10 * rank + s, dt, scale).to(dev) for s in (0, 1, 2))
-    dO = synth((B, n, H, d), 10 * rank + 3, torch.float32).to(dev)
-    layout = (S.zigzag_layout if args.ring == "zigzag" else S.contiguous_layout)(n)
+    Q, K, V = (device_randn((B, n, H, d), 10 * rank + s, dt, scale, dev) for s in (0, 1, 2))
+    dO = device_randn((B, n, H, d), 10 * rank + 3, torch.float32, 1.0, dev)
+    layout = (S.zigzag_layout if ring == "zigzag" else S.contiguous_layout)(n)
     terms = M.MaskTerms(causal=True)
+    timing = {}
 
     def step():
         O, lse = S.ring_attention_forward(Q, K, V, rank=rank, world=world, terms=terms, layout=layout)
@@ -298,38 +485,46 @@ def run_ring(args, w, rank, world, local_rank, dev, dist, warmup):
         step()
     barrier()
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    if rank == 0 and sample_clocks:
         sampler.start()
     launches0 = nat.lib().bma_launch_count()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step()
     t1.record()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop() if (rank == 0 and sample_clocks) else None
     launches = nat.lib().bma_launch_count() - launches0
-    ms_step = t0.elapsed_time(t1) / args.steps
+    ms_step = t0.elapsed_time(t1) / steps
     if dist is not None:
         t = torch.tensor([ms_step], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_step = float(t[0])
+    sustained, burst, hbm, peak_kind = peaks()
+    tf = step_flops / (ms_step * 1e-3) / 1e12
+    del Q, K, V, dO
+    torch.cuda.empty_cache()
+    return {
+        "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": w["dtype"],
+        "data": "synthetic",
+        "config": {"workload": w["desc"], "api": "sharding.ring_attention_forward + ring_attention_backward",
+                   "parallelism": f"sequence split over {world} GPU(s), {ring} token layout, K/V and dK/dV ring over NCCL P2P",
+                   "tokens_per_gpu": n, "nonempty_blocks_total": blocks, "flop_model": "fwd 4*bq*bk*d per non-empty block, bwd 2.5x fwd",
+                   "l2": "inputs exceed the 126 MB L2; no flush needed"},
+        "roofline": {"bound": "tensor", "kernel": "forward + backward kernels of all ring steps", "achieved": tf / world,
+                     "peak": sustained, "unit": "TFLOP/s per GPU", "frac": tf / world / sustained, "traffic": None,
+                     "peak_kind": f"{peak_kind} sustained dense bf16"},
+        "per_gpu": tf / world, "frac_of_burst_per_gpu": tf / world / burst,
+        "clocks": clocks, "gpu_launches": int(launches)}
+
+
+def run_ring(args, w, rank, world, local_rank, dev, dist, warmup):
+    line = ring_entry(w, rank, world, local_rank, dev, dist, args.steps, warmup, args.ring)
     if rank == 0:
-        sustained, burst, hbm, peak_kind = peaks()
-        tf = step_flops / (ms_step * 1e-3) / 1e12
-        print(json.dumps({
-            "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": w["dtype"],
-            "data": "synthetic",
-            "config": {"workload": w["desc"], "api": "sharding.ring_attention_forward + ring_attention_backward",
-                       "parallelism": f"sequence split over {world} GPU(s), {args.ring} token layout, K/V and dK/dV ring over NCCL P2P",
-                       "tokens_per_gpu": n, "nonempty_blocks_total": blocks, "flop_model": "fwd 4*bq*bk*d per non-empty block, bwd 2.5x fwd",
-                       "l2": "inputs exceed the 126 MB L2; no flush needed"},
-            "roofline": {"bound": "tensor", "kernel": "forward + backward kernels of all ring steps", "achieved": tf / world,
-                         "peak": sustained, "unit": "TFLOP/s per GPU", "frac": tf / world / sustained, "traffic": None,
-                         "peak_kind": f"{peak_kind} sustained dense bf16"},
-            "clocks": clocks, "gpu_launches": int(launches)}), flush=True)
+        print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
 
@@ -351,6 +546,9 @@ def main():
                     help="time create_block_mask (the BlockMask builder) at the workload's geometry instead of attention")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the `extra` entries: parity of the benchmarked workload, the other configurations, the "
+                         "BlockMask builder at config 5 and (N > 1) config 5 split by head and as a ring")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
 
@@ -404,6 +602,8 @@ def main():
         O.backward(dO)
         return O
 
+    seg_np = document_segments(B, L) if w["mask"] == "documents" else None
+
     def barrier():
         if dist is not None:
             dist.barrier()
@@ -442,6 +642,14 @@ def main():
     launches = nat.lib().bma_launch_count() - launches0
     A.set_profile_sink(None)
     ms_total = t0.elapsed_time(t1)
+    status = A.device_status(dev)      # non-zero: a bounded wait inside a kernel gave up and the results are invalid
+    assert status == 0, f"device status {status} after the timed region"
+    parity = None
+    if rank == 0 and not args.no_extra:
+        O_last = step()
+        torch.cuda.synchronize(dev)
+        parity = parity_of_slices(w, Q, K, V, dO, O_last, (Q.grad, K.grad, V.grad), seg=seg_np, flex=flex)
+        del O_last
     per_kernel = {k: float(np.mean([a.elapsed_time(b) for a, b in v])) for k, v in sink.items()}
 
     # end to end through the public API with host buffers (H2D of inputs, D2H of results inside the timed region)
@@ -473,7 +681,9 @@ def main():
                 for x in dev_in[slot]:
                     x.record_stream(main)
 
-        def e2e_run(n):
+        kept = []
+
+        def e2e_run(n, compute=True):
             for ev in computed + copied_out:
                 ev.record(main)
             upload(0)
@@ -482,13 +692,21 @@ def main():
                 if i + 1 < n:
                     upload(slot ^ 1)
                 main.wait_event(in_ready[slot])
-                q, k, v = (x.requires_grad_(True) for x in dev_in[slot][:3])
-                o = attend(q, k, v)
-                fwd_done[slot].record(main)
-                main.wait_event(do_ready[slot])
-                o.backward(dev_in[slot][3])
-                computed[slot].record(main)
-                results = (o.detach(), q.grad, k.grad, v.grad)
+                if compute:
+                    q, k, v = (x.requires_grad_(True) for x in dev_in[slot][:3])
+                    o = attend(q, k, v)
+                    fwd_done[slot].record(main)
+                    main.wait_event(do_ready[slot])
+                    o.backward(dev_in[slot][3])
+                    computed[slot].record(main)
+                    results = (o.detach(), q.grad, k.grad, v.grad)
+                    kept[:] = [results]
+                else:
+                    # the copies alone: same buffers, streams and ordering, no kernels (results of an earlier step go out)
+                    fwd_done[slot].record(main)
+                    main.wait_event(do_ready[slot])
+                    computed[slot].record(main)
+                    results = kept[0]
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(fwd_done[slot])         # O leaves while the backward runs
                     host_out[slot][0].copy_(results[0], non_blocking=True)
@@ -509,17 +727,43 @@ def main():
         e1.record()
         barrier()
         e2e_ms = e0.elapsed_time(e1) / e2e_steps
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        c0.record()
+        e2e_run(e2e_steps, compute=False)
+        c1.record()
+        barrier()
+        copy_ms = c0.elapsed_time(c1) / e2e_steps
         h2d = sum(x.numel() * x.element_size() for x in (hQ, hK, hV, hdO))
         d2h = sum(x.numel() * x.element_size() for x in outs)
-        e2e = (e2e_ms, h2d, d2h)
+        e2e = (e2e_ms, h2d, d2h, copy_ms)
+        del kept[:], dev_in[:], host_out
 
     ms_step = ms_total / args.steps
     if dist is not None:
-        t = torch.tensor([ms_step, e2e[0] if e2e else 0.0], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms_step, e2e[0] if e2e else 0.0, e2e[3] if e2e else 0.0], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_step, e2e_ms_max = float(t[0]), float(t[1])
+        ms_step = float(t[0])
         if e2e:
-            e2e = (e2e_ms_max, e2e[1], e2e[2])
+            e2e = (float(t[1]), e2e[1], e2e[2], float(t[2]))
+
+    # ---- `extra`: everything beside the headline workload that a reader of this one line should see ----------
+    extra = {}
+    if not args.no_extra:
+        del Q, K, V, dO, hQ, hK, hV, hdO
+        torch.cuda.empty_cache()
+        if parity is not None:
+            extra["parity"] = parity
+        if world == 1:
+            extra["per_config"] = {name: measure_config(name, dev) for name in ("t0", "c3", "c4", "c5", "d64", "c1") if name != args.workload}
+            extra["block_mask_c5"] = block_mask_build_entry(WORKLOADS["c5"], dev, steps=5, warmup=3)
+        else:
+            extra["c5_head_shards"] = c5_head_shards(rank, world, dev, dist)
+            if WORKLOADS["c5"]["L"] % (2 * world * 128) == 0:
+                r = ring_entry(WORKLOADS["c5"], rank, world, local_rank, dev, dist, steps=3, warmup=2, ring="zigzag", sample_clocks=False)
+                extra["ring_c5"] = {k: r[k] for k in ("value", "ms_per_step", "steps", "warmup", "scaling", "per_gpu", "frac_of_burst_per_gpu", "gpu_launches")}
+                extra["ring_c5"]["parallelism"] = r["config"]["parallelism"]
+                extra["ring_c5"]["workload"] = r["config"]["workload"]
 
     if rank == 0:
         sustained, burst, hbm, peak_kind = peaks()
@@ -528,7 +772,7 @@ def main():
         fwd_ms = per_kernel.get("fwd")
         bwd_tf = (step_flops - fwd_flops) / (bwd_ms * 1e-3) / 1e12 if bwd_ms else None
         fwd_tf = fwd_flops / (fwd_ms * 1e-3) / 1e12 if fwd_ms else None
-        traffic = NCU_TRAFFIC_BYTES.get(args.workload, {})
+        traffic = ncu_traffic(args.workload)
         line = {
             "metric": METRIC, "value": total_flops / (ms_step * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -574,9 +818,13 @@ def main():
                                     "traffic": traffic.get("bwd")}
         if e2e:
             line["e2e"] = {"value": total_flops / (e2e[0] * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e[0],
-                           "h2d_bytes_per_step": e2e[1], "d2h_bytes_per_step": e2e[2]}
+                           "h2d_bytes_per_step": e2e[1], "d2h_bytes_per_step": e2e[2],
+                           # the same copies on the same streams with no kernel in between: the box's own ceiling
+                           "copy_only_ms_per_step": e2e[3], "copy_only_GBps_each_way": e2e[1] / (e2e[3] * 1e-3) / 1e9}
+        if extra:
+            line["extra"] = extra
         if world == 1 and not args.no_cpu_baseline:
-            r = cpu_reference_run(w, steps=1, warmup=0)
+            r = cpu_reference_run(w, steps=1, warmup=1)
             line["cpu_baseline"] = {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port",
                                     "sample": r["sample"], "seconds": r["seconds_per_step"]}
         print(json.dumps(line), flush=True)

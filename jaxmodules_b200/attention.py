@@ -123,13 +123,15 @@ def plan(Q, K, V, backend=nat.BMA_BACKEND_AUTO, backward: bool = False, key_bias
 
 
 class _Span:
-    """Optional CUDA-event bracket around one launch (used by the benchmark to time a single
-    kernel on the launching stream); a no-op when ``sink`` is None."""
+    """One launch group: an NVTX range named after it (visible in a timeline profiler, free otherwise) and,
+    when ``sink`` is a dict, a CUDA-event bracket on the launching stream (the benchmark times single
+    kernels with it)."""
 
     def __init__(self, sink, key, device):
         self.sink, self.key, self.device = sink, key, device
 
     def __enter__(self):
+        torch.cuda.nvtx.range_push("bma." + self.key)
         if self.sink is not None:
             self.t0 = torch.cuda.Event(enable_timing=True)
             self.t1 = torch.cuda.Event(enable_timing=True)
@@ -140,6 +142,7 @@ class _Span:
         if self.sink is not None:
             self.t1.record(torch.cuda.current_stream(self.device))
             self.sink.setdefault(self.key, []).append((self.t0, self.t1))
+        torch.cuda.nvtx.range_pop()
         return False
 
 
