@@ -251,32 +251,47 @@ int bma_attn_bwd_preprocess(const bma_attn_args* args, void* d_o_bf16, bma_strea
  * accumulated on chip); the query stays so that a backend with scratch can be added. */
 size_t bma_attn_bwd_workspace_bytes(const bma_attn_args* args);
 
-/* Optional scratch of bma_attn_bwd (0 when the backend has no use for it).  Given a workspace of
- * at least this size, the tensor-core backward hands every bf16 dS tile (32 KB per visited
- * 128x128 block, slots addressed densely over [B, Hq, N/128, L/128]) from the dK/dV kernel to the
- * dQ kernel through that buffer instead of recomputing S and dP there: 5 instead of 7 MMAs per
- * block, for 32 KB of HBM traffic each way.  Only valid when the q-side and kv-side arrays of
- * `lists` name the same blocks (they do when both come from one bma_mask_compile call): a slot is
- * read only if it was written during the same call.  A workspace that holds at least one
- * (batch, kv head) unit — bma_attn_bwd_scratch_bytes() / (B * Hkv) — still takes this path: the
- * backward then runs as consecutive launches over ranges of units that reuse the buffer.  With
- * a smaller or NULL workspace the dQ kernel recomputes S and dP; results agree to the bf16
- * rounding of dS either way. */
-size_t bma_attn_bwd_scratch_bytes(const bma_attn_args* args);
+/* Number of visited (full + partial) blocks per list head: visited[b' * lists->H + h'] = sum over the rows of
+ * (kv_num + full_kv_num), int64 on the device, [lists->B * lists->H].  One small kernel; the caller copies the result
+ * to the host once per mask and hands it to bma_attn_bwd_scratch_bytes / bma_attn_bwd, which size the backward
+ * scratch by it.  No counterpart in the reference (its backward recomputes everything, jaxmodules/attention.py:266-342). */
+int bma_block_lists_visited(const bma_block_lists* lists, int64_t* visited, bma_stream_t stream);
 
-/* Profiling aid: the next bma_attn_bwd call of the calling thread records `cuda_event` (a
- * cudaEvent_t created with timing enabled) on its stream between the dK/dV pass and the dQ
- * pass, so that the two kernels can be timed separately with CUDA events.  Used once, then
- * forgotten; ignored by the SIMT backend and when the backward runs in several ranges. */
-void bma_attn_bwd_mark(void* cuda_event);
+/* Optional scratch of bma_attn_bwd (0 when the backend has no use for it).  Given a workspace of
+ * at least this size, the tensor-core backward hands every bf16 dS tile (32 KB per VISITED
+ * 128x128 block; the slots are addressed compactly -- a prefix over the block lists, built into
+ * the front of the workspace by three small launches per call) from the dK/dV kernel to the dQ
+ * kernel through that buffer instead of recomputing S and dP there: 5 instead of 7 MMAs per
+ * block, for 32 KB of HBM traffic each way.
+ *   visited_host: HOST array [lists->B * lists->H] of visited-block counts per list head (from
+ *     bma_block_lists_visited), or NULL; without it every size is the dense bound N/128 * L/128
+ *     blocks per query head.
+ * Only valid when the q-side and kv-side arrays of `lists` name the same blocks (they do when both
+ * come from one bma_mask_compile call): a slot is read only if it was written during the same call,
+ * and a block that only one side names is reported through the status word, never written.
+ * A workspace that holds the tables plus at least the largest (batch, kv head) unit still takes this
+ * path: the backward then runs as consecutive launches over ranges of units that reuse the slots.
+ * With a smaller or NULL workspace the dQ kernel recomputes S and dP; results agree to the bf16
+ * rounding of dS either way.  The workspace must be 256-byte aligned. */
+size_t bma_attn_bwd_scratch_bytes(const bma_attn_args* args, const bma_block_lists* lists,
+                                  const int64_t* visited_host);
 
 /* Backward: dQ, dK, dV from (Q, K, V, O, dO, lse, delta).  Replaces
  * _masked_attention_via_map_bwd, jaxmodules/attention.py:266-342.  `lists` must carry the
  * q-side arrays.  `workspace` must hold bma_attn_bwd_workspace_bytes(); one of
- * bma_attn_bwd_scratch_bytes() selects the hand-over variant described above. */
+ * bma_attn_bwd_scratch_bytes() selects the hand-over variant described above (pass the same
+ * visited_host).  mid_event: NULL, or a cudaEvent_t (created with timing enabled) that is recorded
+ * on `stream` between the dK/dV pass and the dQ pass when the backward runs as one range, so that
+ * the two kernels can be timed separately; ignored by the SIMT backend. */
 int bma_attn_bwd(const bma_attn_args* args, const bma_mask_spec* spec,
                  const bma_block_lists* lists, void* workspace, size_t workspace_bytes,
-                 bma_stream_t stream);
+                 const int64_t* visited_host, void* mid_event, bma_stream_t stream);
+
+/* Self-test of the bounded waits (no counterpart in the reference): launches one CTA that waits on a
+ * barrier nobody arrives at, gives up after limit_ns (at most 1e9) exactly like the waits inside the
+ * attention kernels, records `code` (> 0) in the device status word and returns.  The context stays
+ * usable; bma_device_status then returns BMA_ERR_DEVICE_CHECK with *detail == code. */
+int bma_debug_expire_wait(uint64_t limit_ns, int32_t code, bma_stream_t stream);
 
 /* Merge of two partial attention results over disjoint key sets (sequence-sharded
  * execution; no counterpart in the reference, which is single-device):

@@ -246,48 +246,63 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
         if do_bf16 is not None:
             a.d_o = _tensor(do_bf16)
         ws_bytes = lib.bma_attn_bwd_workspace_bytes(C.byref(a))
-        # dS hand-over between the two backward kernels: only for lists whose two sides name the same blocks
+        # dS hand-over between the two backward kernels: only for lists whose two sides name the same blocks.
+        # The scratch is sized by the blocks the mask visits (fetched once per mask, see masks.visited_counts).
         lists_fn = ctx.get("lists_fn")
-        scratch = lib.bma_attn_bwd_scratch_bytes(C.byref(a)) if (lists_fn is None or getattr(lists_fn, "consistent", False)) else 0
-        ranges = scratch > _scratch_limit
-        if ranges:                         # below the whole problem: whole (batch, kv head) units, processed range by range
-            unit = scratch // (B * K.shape[-2])
-            scratch = (_scratch_limit // unit) * unit
-        if scratch > 0:
-            ws, ws_bytes = _backward_scratch(dev, max(scratch, ws_bytes)), max(scratch, ws_bytes)
+        visited = scratch = 0
+        if be == nat.BMA_BACKEND_TCGEN05 and _scratch_limit > 0 and (lists_fn is None or getattr(lists_fn, "consistent", False)):
+            if lists_fn is None:
+                counts = _masks.visited_counts(ctx["dmask"], lists, dev)
+            else:
+                counts = lists_fn.visited_counts(lists, dev)
+            visited = (C.c_int64 * len(counts))(*[int(c) for c in counts])
+            scratch = lib.bma_attn_bwd_scratch_bytes(C.byref(a), C.byref(lists), visited)
+        given = min(scratch, _scratch_limit, int(scratch * _scratch_fraction) if _scratch_fraction < 1.0 else scratch)
+        if given > 0:
+            ws, ws_bytes = _backward_scratch(dev, max(given, ws_bytes)), max(given, ws_bytes)
         else:
             ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=dev)
+        last_backward_info.update(scratch_bytes=int(scratch), workspace_bytes=int(ws_bytes), whole=bool(scratch and given >= scratch))
         mid = None
-        if _profile_sink is not None and be == nat.BMA_BACKEND_TCGEN05 and not (ranges and scratch > 0):
-            # the library re-records this event between its dK/dV pass and its dQ pass
+        if _profile_sink is not None and be == nat.BMA_BACKEND_TCGEN05 and (scratch == 0 or given >= scratch):
+            # the library records this event between its dK/dV pass and its dQ pass (only when it runs as one range)
             mid = torch.cuda.Event(enable_timing=True)
             mid.record(torch.cuda.current_stream(dev))
-            lib.bma_attn_bwd_mark(mid.cuda_event)
         with _Span(_profile_sink, "bwd", dev) as span:
-            nat.check(lib.bma_attn_bwd(C.byref(a), C.byref(ctx["dmask"].spec), C.byref(lists), ws.data_ptr(), ws_bytes, st),
+            nat.check(lib.bma_attn_bwd(C.byref(a), C.byref(ctx["dmask"].spec), C.byref(lists), ws.data_ptr(), ws_bytes,
+                                       visited if visited else None, mid.cuda_event if mid is not None else None, st),
                       "bma_attn_bwd")
         _maybe_check_status(dev, "bma_attn_bwd")
         if mid is not None:
             _profile_sink.setdefault("bwd_dkdv", []).append((span.t0, mid))
-            _profile_sink.setdefault("bwd_dq_replay" if scratch > 0 else "bwd_dq_recompute", []).append((mid, span.t1))
+            _profile_sink.setdefault("bwd_dq_replay" if given >= scratch > 0 else "bwd_dq_recompute", []).append((mid, span.t1))
     return dQ, dK, dV
 
 
-# Scratch of the tensor-core backward (the dS tiles handed from the dK/dV kernel to the dQ kernel): one
-# grow-only buffer per (device, stream), reused by every call in that stream's order.  A problem whose
-# scratch exceeds the limit runs range by range over (batch, kv head) units; when not even one unit fits
-# (32 KB x Hq/Hkv x N/128 x L/128), the dQ kernel recomputes S and dP instead.
-_scratch_limit = int(float(os.environ.get("BMA_BWD_SCRATCH_GB", "20")) * (1 << 30))   # environment override, in GiB
+# Scratch of the tensor-core backward (the dS tiles handed from the dK/dV kernel to the dQ kernel): 32 KB per block the
+# mask VISITS (a causal mask: half of the dense grid; a sliding window or packed documents: a small fraction) plus a
+# few MB of slot tables, in one buffer per (device, stream) that grows to the largest call seen and is reused by
+# every call in that stream's order.  A problem whose scratch exceeds the limit runs range by range over (batch,
+# kv head) units through the same buffer; when not even the largest unit fits, the dQ kernel recomputes S and dP.
+_scratch_limit = int(float(os.environ.get("BMA_BWD_SCRATCH_GB", "10")) * (1 << 30))   # environment override, in GiB
+_scratch_fraction = 1.0
 _scratch_buffers = {}
+last_backward_info = {}    # sizes of the most recent backward call (diagnostics, tests)
 
 
-def set_backward_scratch_limit(nbytes: int) -> None:
-    """Upper bound in bytes of the backward scratch buffer (32 KB per 128x128 block of the dense
-    [B, Hq, N/128, L/128] grid); 0 switches the dS hand-over off.  Frees buffers above the new limit."""
-    global _scratch_limit
-    _scratch_limit = int(nbytes)
+def set_backward_scratch_limit(nbytes: int, fraction: float = 1.0) -> None:
+    """Upper bound in bytes of the backward scratch buffer; 0 switches the dS hand-over off.  Buffers above the new
+    limit are freed at once.  ``fraction`` < 1 additionally caps every call at that share of what it would need,
+    which forces the backward to run in ranges (a knob for tests and for measuring what ranges cost)."""
+    global _scratch_limit, _scratch_fraction
+    _scratch_limit, _scratch_fraction = int(nbytes), float(fraction)
     for key in [k for k, t in _scratch_buffers.items() if t.numel() > _scratch_limit]:
         del _scratch_buffers[key]
+
+
+def release_backward_scratch() -> None:
+    """Frees every scratch buffer (they come back at the next backward call that wants one)."""
+    _scratch_buffers.clear()
 
 
 def _backward_scratch(dev: torch.device, nbytes: int) -> torch.Tensor:

@@ -19,7 +19,7 @@ CSRC = PKG / "csrc"
 OBJ = CSRC / "build"
 LIB = PKG / "libbma.so"
 
-SOURCES = ["bma_api.cu", "mask_compile.cu", "mask_program.cu", "attn_simt.cu", "attn_fwd_sm100.cu", "attn_bwd_sm100.cu", "attn_bwd_dq_sm100.cu", "attn_bwd_dq_replay_sm100.cu"]
+SOURCES = ["bma_api.cu", "mask_compile.cu", "mask_program.cu", "attn_simt.cu", "attn_fwd_sm100.cu", "attn_bwd_sm100.cu", "attn_bwd_dq_sm100.cu", "attn_bwd_dq_replay_sm100.cu", "bwd_slots.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -55,7 +55,11 @@ struct __align__(1024) ReplaySmem {
 struct ReplayParams {
   bma_attn_args a;
   bma_block_lists l;
-  const uint8_t* ds;  // [nb, nh, NQ, NKV] slots of kDsBytes for the (batch, head) range of this launch
+  const uint8_t* ds;  // slots of kDsBytes, addressed compactly: head_base[b, h] - head_base[first head of the launch]
+                      // + row_base[q tile] + (number of the row's visited kv tiles before this one)
+  const int64_t* head_base;
+  const int32_t* row_base;
+  int64_t capacity;
   int b0, h0, nh;
   int* status;
 };
@@ -127,7 +131,15 @@ bwd_dq_replay_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       // ---------------------------------------------------------------- producer
       prefetch_tensormap(&map_k);
       const uint64_t policy = l2_evict_first();  // every dS tile is read exactly once
-      const uint8_t* ds_bh = p.ds + ((int64_t)(b - p.b0) * p.nh + (h - p.h0)) * NQ * (int64_t)NKV * kDsBytes;
+      // first slot of each of the two query rows; the walk below visits a row's kv tiles in ascending order, which is
+      // the order the slots were numbered in
+      const int64_t head0 = __ldg(p.head_base + (int64_t)b * a.Hq + h) - __ldg(p.head_base + (int64_t)p.b0 * a.Hq + p.h0);
+      int64_t next_slot[2];
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        const int qi = min(pair * 2 + x, NQ - 1);
+        next_slot[x] = head0 + __ldg(p.row_base + ((int64_t)lb * p.l.H + lh) * NQ + qi);
+      }
       bool ok = true;
       int s = 0;  // dS tiles requested so far
       for (int n = 0; n < T && ok; ++n) {
@@ -141,8 +153,11 @@ bwd_dq_replay_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
           const int slot = s % kDsStages;
           if (s >= kDsStages) ok = mbar_wait(&sm.bar[BAR_DS_FREE0 + slot], ((s / kDsStages) - 1) & 1);
           if (!ok) break;
+          // (an index outside the buffer cannot come from consistent lists; it is clamped and reported, never read)
+          int64_t gslot = next_slot[x]++;
+          if (gslot < 0 || gslot >= p.capacity) { gslot = 0; report_device_error(p.status, 511); }
           mbar_expect_tx(&sm.bar[BAR_DS_FULL0 + slot], kDsBytes);
-          bulk_load_1d(sm.ds[slot], ds_bh + ((int64_t)(pair * 2 + x) * NKV + kj) * kDsBytes, kDsBytes, &sm.bar[BAR_DS_FULL0 + slot], policy);
+          bulk_load_1d(sm.ds[slot], p.ds + gslot * (int64_t)kDsBytes, kDsBytes, &sm.bar[BAR_DS_FULL0 + slot], policy);
           ++s;
         }
         if (!ok) break;
@@ -250,8 +265,8 @@ bwd_dq_replay_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
 
 }  // namespace
 
-int sm100_bwd_dq_from_ds(const bma_attn_args& a, const bma_block_lists& lists, const void* ds, int b0, int nb, int hk0, int nhk,
-                         cudaStream_t st) {
+int sm100_bwd_dq_from_ds(const bma_attn_args& a, const bma_block_lists& lists, const void* ds, const SlotTables& tables,
+                         int64_t capacity, int b0, int nb, int hk0, int nhk, cudaStream_t st) {
   BMA_REQUIRE(lists.NKV <= kMaxKvTiles, BMA_ERR_LIMIT);
   BMA_REQUIRE(ds != nullptr, BMA_ERR_ARG);
   CUtensorMap mk, mdq;
@@ -261,6 +276,7 @@ int sm100_bwd_dq_from_ds(const bma_attn_args& a, const bma_block_lists& lists, c
   ReplayParams p;
   p.a = a; p.l = lists;
   p.ds = static_cast<const uint8_t*>(ds);
+  p.head_base = tables.head_base; p.row_base = tables.row_base; p.capacity = capacity;
   const int G = a.Hq / a.Hkv;
   p.b0 = b0; p.h0 = hk0 * G; p.nh = nhk * G;
   p.status = device_status_ptr();

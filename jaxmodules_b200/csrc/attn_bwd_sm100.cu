@@ -28,6 +28,8 @@
 // bulk store, and dQ += dS K then needs no recomputation of S and dP (5 instead of 7 MMAs per block
 // for the whole backward, paid with 32 KB of HBM traffic each way).
 // Every mbarrier wait is bounded; on a timeout the thread records an error code and unwinds.
+#include <algorithm>
+
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -38,7 +40,8 @@
 namespace bma {
 
 int sm100_bwd_dq(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, cudaStream_t st);
-int sm100_bwd_dq_from_ds(const bma_attn_args& a, const bma_block_lists& lists, const void* ds, int b0, int nb, int hk0, int nhk,
+int sm100_bwd_dq_from_ds(const bma_attn_args& a, const bma_block_lists& lists, const void* ds, const SlotTables& tables,
+                         int64_t capacity, int b0, int nb, int hk0, int nhk,
                          cudaStream_t st);
 
 namespace {
@@ -80,7 +83,12 @@ struct BwdParams {
   float scale_log2;
   int interval_mask;
   int* status;
-  uint8_t* ds_out;  // null, or [nb, nhk * G, NQ, NKV] slots of kDsBytes: the dSt image of every visited block
+  uint8_t* ds_out;  // null, or the slots of kDsBytes: the dSt image of every visited block, addressed compactly:
+                    // slot = head_base[b, h] - head_base[first head of the launch] + row_base[qi] + rank[qi][kj]
+  const int64_t* head_base;
+  const int32_t* row_base;
+  const int32_t* rank;
+  int64_t capacity; // slots the buffer holds (a slot index beyond it is reported, never written)
   int b0, hk0;      // first batch / kv head of this launch (the grid covers a range when the scratch is smaller
   int nhk;          // than the whole problem), and the number of kv heads in the range
 };
@@ -332,6 +340,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // bulk store moves it to its slot, and BAR_DSR tells the consumers that the buffer has been read.
       QTileIter loader(p.l, b, hk, G, kj);
       const uint64_t policy = l2_evict_first();
+      const int64_t first_head_base = __ldg(p.head_base + (int64_t)p.b0 * a.Hq + (int64_t)p.hk0 * G);
       bool ok = true;
       for (int n = 0; n < total && ok; ++n) {
         int h, qi; bool partial;
@@ -339,10 +348,16 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         ok = mbar_wait(&sm.bar[BAR_STG], n & 1);
         if (!ok) break;
         if (lane == 0) {
-          const int64_t slot = (((int64_t)(b - p.b0) * (p.nhk * G) + (h - p.hk0 * G)) * p.l.NQ + qi) * p.l.NKV + kj;
-          bulk_store_1d(p.ds_out + slot * (int64_t)kDsBytes, sm.ds, kDsBytes, policy);
-          bulk_commit();
-          bulk_wait_read0();
+          const int64_t lrow = ((int64_t)(p.l.B == 1 ? 0 : b) * p.l.H + (p.l.H == 1 ? 0 : h)) * p.l.NQ + qi;
+          const int r = __ldg(p.rank + lrow * p.l.NKV + kj);
+          const int64_t slot = __ldg(p.head_base + (int64_t)b * a.Hq + h) - first_head_base + __ldg(p.row_base + lrow) + r;
+          if (r >= 0 && slot >= 0 && slot < p.capacity) {
+            bulk_store_1d(p.ds_out + slot * (int64_t)kDsBytes, sm.ds, kDsBytes, policy);
+            bulk_commit();
+            bulk_wait_read0();
+          } else {
+            report_device_error(p.status, 319);   // the two list sides disagree, or the buffer is too small: nothing is written
+          }
           mbar_arrive(&sm.bar[BAR_DSR]);
         }
         __syncwarp();
@@ -577,14 +592,47 @@ bool sm100_bwd_supported(const bma_attn_args& a) { return sm100_supported(a) && 
 
 size_t sm100_bwd_workspace_bytes(const bma_attn_args&) { return 0; }
 
-// one dSt image per (query head of the group, q tile, kv tile) of a (batch, kv head) unit, addressed densely
-static size_t scratch_unit_bytes(const bma_attn_args& a) {
-  return (size_t)(a.Hq / a.Hkv) * ceil_div(a.N, BT) * ceil_div(a.L, BT) * kDsBytes;
+template <typename P>
+static int launch_dkdv(const bma_attn_args& a, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
+                       const CUtensorMap& mdk, const CUtensorMap& mdv, P& p, int b0, int nb, int hk0, int nhk, cudaStream_t st) {
+  p.b0 = b0; p.hk0 = hk0; p.nhk = nhk;
+  dim3 grid(ceil_div(a.L, BT), nhk, nb);
+  int rc;
+  auto launch = [&](auto kernel, size_t smem) -> int {
+    BMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
+    return BMA_OK;
+  };
+  if (a.d == 128) rc = a.key_bias ? launch(bwd_dkdv_kernel<128, true>, sizeof(BwdSmem<128>)) : launch(bwd_dkdv_kernel<128, false>, sizeof(BwdSmem<128>));
+  else rc = a.key_bias ? launch(bwd_dkdv_kernel<64, true>, sizeof(BwdSmem<64>)) : launch(bwd_dkdv_kernel<64, false>, sizeof(BwdSmem<64>));
+  if (rc) return rc;
+  count_launches(1);
+  BMA_CUDA_TRY(cudaGetLastError());
+  return BMA_OK;
 }
-size_t sm100_bwd_scratch_bytes(const bma_attn_args& a) { return (size_t)a.B * a.Hkv * scratch_unit_bytes(a); }
+
+// Visited blocks of one query head: from the caller's per-list-head counts, or the dense bound without them.
+static int64_t head_blocks(const bma_attn_args& a, const bma_block_lists& l, const int64_t* visited, int b, int h) {
+  if (!visited) return (int64_t)ceil_div(a.N, BT) * ceil_div(a.L, BT);
+  return visited[(int64_t)(l.B == 1 ? 0 : b) * l.H + (l.H == 1 ? 0 : h)];
+}
+static int64_t unit_blocks(const bma_attn_args& a, const bma_block_lists& l, const int64_t* visited, int b, int hk) {
+  const int G = a.Hq / a.Hkv;
+  int64_t n = 0;
+  for (int g = 0; g < G; ++g) n += head_blocks(a, l, visited, b, hk * G + g);
+  return n;
+}
+// tables + one dSt image (32 KB) per visited block of the whole problem
+size_t sm100_bwd_scratch_bytes(const bma_attn_args& a, const bma_block_lists& lists, const int64_t* visited_host) {
+  if (lists.NKV > 1024 || lists.NQ <= 0 || lists.B <= 0 || lists.H <= 0) return 0;
+  int64_t blocks = 0;
+  for (int b = 0; b < a.B; ++b)
+    for (int hk = 0; hk < a.Hkv; ++hk) blocks += unit_blocks(a, lists, visited_host, b, hk);
+  return slot_tables_layout(a, lists, nullptr).bytes + (size_t)blocks * kDsBytes;
+}
 
 int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, void* ws, size_t ws_bytes,
-              cudaEvent_t mark, cudaStream_t st) {
+              const int64_t* visited_host, cudaEvent_t mark, cudaStream_t st) {
   BMA_REQUIRE(lists.q_block == BT && lists.kv_block == BT && lists.q_num, BMA_ERR_ARG);
   BMA_REQUIRE(a.d_o.dtype == BMA_DTYPE_BF16, BMA_ERR_UNSUPPORTED);  // bma_attn_bwd_preprocess provides the bf16 copy
   BMA_REQUIRE(aligned16(a.d_o) && aligned16(a.dq) && aligned16(a.dk) && aligned16(a.dv), BMA_ERR_UNSUPPORTED);
@@ -608,39 +656,65 @@ int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   p.interval_mask = interval;
   p.status = device_status_ptr();
   BMA_REQUIRE(p.status != nullptr, BMA_ERR_CUDA);
-  // A scratch buffer switches the dQ pass from recomputation to replaying the dSt tiles.  It must hold at least
-  // one (batch, kv head) unit; when it is smaller than the whole problem the backward runs as consecutive
-  // launches over ranges of batches (or, below one batch, of kv heads) that reuse the buffer.
-  const size_t unit = scratch_unit_bytes(a);
-  const size_t units = (ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 15) == 0) ? ws_bytes / unit : 0;
-  const bool hand_over = units >= 1 && lists.NQ == ceil_div(a.N, BT) && lists.NKV == ceil_div(a.L, BT);
-  p.ds_out = hand_over ? static_cast<uint8_t*>(ws) : nullptr;
-  int step_b = a.B, step_hk = a.Hkv;
-  if (hand_over && units < (size_t)a.B * a.Hkv) {
-    if (units >= (size_t)a.Hkv) step_b = (int)(units / a.Hkv);
-    else { step_b = 1; step_hk = (int)units; }
+  p.ds_out = nullptr; p.head_base = nullptr; p.row_base = nullptr; p.rank = nullptr; p.capacity = 0;
+  // A scratch buffer switches the dQ pass from recomputation to replaying the dSt tiles.  Behind the slot tables it
+  // must hold at least the largest (batch, kv head) unit; when it is smaller than the whole problem the backward runs
+  // as consecutive launches over ranges of whole batches (or, inside a batch that does not fit, of kv heads) that reuse
+  // the slots.  Unit sizes come from the caller's visited-block counts (the dense bound without them); the kernels
+  // address compactly either way, so a range never needs more than the host planned for it.
+  const bool lists_fit = lists.NQ == ceil_div(a.N, BT) && lists.NKV == ceil_div(a.L, BT) && lists.NKV <= 1024;
+  SlotTables tables = slot_tables_layout(a, lists, ws);
+  int64_t capacity = 0;
+  if (ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255) == 0 && ws_bytes > tables.bytes && lists_fit)
+    capacity = (int64_t)((ws_bytes - tables.bytes) / kDsBytes);
+  int64_t largest = 0;
+  for (int b = 0; b < a.B; ++b)
+    for (int hk = 0; hk < a.Hkv; ++hk) largest = std::max(largest, unit_blocks(a, lists, visited_host, b, hk));
+  const bool hand_over = capacity >= 1 && largest <= capacity;
+  if (!hand_over) {
+    rc = launch_dkdv(a, mq, mk, mv, mdo, mdk, mdv, p, 0, a.B, 0, a.Hkv, st);
+    if (rc) return rc;
+    if (mark) BMA_CUDA_TRY(cudaEventRecord(mark, st));
+    return sm100_bwd_dq(a, spec, lists, st);
   }
-  if (step_b < a.B || step_hk < a.Hkv) mark = nullptr;  // several ranges: no single boundary between the passes
-  for (int b0 = 0; b0 < a.B; b0 += step_b) {
-    for (int hk0 = 0; hk0 < a.Hkv; hk0 += step_hk) {
-      const int nb = a.B - b0 < step_b ? a.B - b0 : step_b, nhk = a.Hkv - hk0 < step_hk ? a.Hkv - hk0 : step_hk;
-      p.b0 = b0; p.hk0 = hk0; p.nhk = nhk;
-      dim3 grid(ceil_div(a.L, BT), nhk, nb);
-      auto launch = [&](auto kernel, size_t smem) -> int {
-        BMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kernel<<<grid, kThreads, smem, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
-        return BMA_OK;
-      };
-      if (a.d == 128) rc = a.key_bias ? launch(bwd_dkdv_kernel<128, true>, sizeof(BwdSmem<128>)) : launch(bwd_dkdv_kernel<128, false>, sizeof(BwdSmem<128>));
-      else rc = a.key_bias ? launch(bwd_dkdv_kernel<64, true>, sizeof(BwdSmem<64>)) : launch(bwd_dkdv_kernel<64, false>, sizeof(BwdSmem<64>));
-      if (rc) return rc;
-      count_launches(1);
-      BMA_CUDA_TRY(cudaGetLastError());
-      if (mark) BMA_CUDA_TRY(cudaEventRecord(mark, st));
-      if (hand_over && (rc = sm100_bwd_dq_from_ds(a, lists, ws, b0, nb, hk0, nhk, st))) return rc;
+  if ((rc = slot_tables_build(a, lists, tables, st))) return rc;
+  p.ds_out = static_cast<uint8_t*>(ws) + tables.bytes;
+  p.head_base = tables.head_base; p.row_base = tables.row_base; p.rank = tables.rank;
+  p.capacity = capacity;
+  bool first = true;
+  auto run_range = [&](int b0, int nb, int hk0, int nhk, bool whole) -> int {
+    int r = launch_dkdv(a, mq, mk, mv, mdo, mdk, mdv, p, b0, nb, hk0, nhk, st);
+    if (r) return r;
+    if (mark && first && whole) BMA_CUDA_TRY(cudaEventRecord(mark, st));   // one boundary only when one range covers everything
+    first = false;
+    return sm100_bwd_dq_from_ds(a, lists, p.ds_out, tables, capacity, b0, nb, hk0, nhk, st);
+  };
+  auto batch_blocks = [&](int b) {
+    int64_t n = 0;
+    for (int hk = 0; hk < a.Hkv; ++hk) n += unit_blocks(a, lists, visited_host, b, hk);
+    return n;
+  };
+  for (int b0 = 0; b0 < a.B;) {
+    int nb = 0;
+    int64_t used = 0;
+    while (b0 + nb < a.B && used + batch_blocks(b0 + nb) <= capacity) used += batch_blocks(b0 + nb++);
+    if (nb >= 1) {
+      if ((rc = run_range(b0, nb, 0, a.Hkv, nb == a.B))) return rc;
+      b0 += nb;
+      continue;
     }
+    for (int hk0 = 0; hk0 < a.Hkv;) {   // this batch alone does not fit: ranges of its kv heads
+      int nhk = 0;
+      used = 0;
+      while (hk0 + nhk < a.Hkv && used + unit_blocks(a, lists, visited_host, b0, hk0 + nhk) <= capacity)
+        used += unit_blocks(a, lists, visited_host, b0, hk0 + nhk++);
+      if ((rc = run_range(b0, 1, hk0, nhk, false))) return rc;   // nhk >= 1: the largest unit fits
+      hk0 += nhk;
+    }
+    b0 += 1;
   }
-  return hand_over ? BMA_OK : sm100_bwd_dq(a, spec, lists, st);
+  return BMA_OK;
+
 }
 
 }  // namespace bma

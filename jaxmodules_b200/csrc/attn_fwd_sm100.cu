@@ -19,6 +19,10 @@
 // MMAs issued by one thread execute in issue order, so P_x V (reads P_x) followed by the next
 // S_x (overwrites it) needs no extra barrier.  Every mbarrier wait is bounded; on a timeout the
 // thread records an error code and unwinds to the common exit where TMEM is released.
+#include <algorithm>
+#include <cstdlib>
+#include <mutex>
+
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -494,6 +498,533 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   if (warp == 8) tmem_dealloc(tmem, kTmemCols);
 }
 
+
+// =================================================================================================
+// Persistent variant: one CTA per SM for the whole launch.  Work items — a PAIR of q tiles of one
+// (batch, query head) — are handed out by an atomic counter, heaviest pairs of a group of heads first
+// (causal: the last pair walks the most kv tiles), so that set-up, pipeline fill and epilogue of one
+// item overlap the main loop of the next:
+//   * barriers and tensor memory are set up once per CTA;
+//   * warp 10 takes the next item from the counter and merges its kv lists into the other of two list
+//     slots while the current item computes;
+//   * the TMA producer's K/V ring simply continues into the next item (its first two tiles are in
+//     flight before the current item has finished), and the next Q tile is fetched as soon as the
+//     epilogue has let go of the Q buffer (it doubles as the staging buffer of the O store);
+//   * the two q tiles of a pair still move through the kv list together (one MMA-issuing warp alternating
+//     between them): letting each tile run at its own pace was measured slower — the tile that gets ahead
+//     holds the two-stage K/V ring, so the loads of the next tile can no longer be issued a whole tile early.
+// =================================================================================================
+enum {
+  PB_LIST_FULL0 = 0, PB_LIST_FULL1, PB_LIST_FREE0, PB_LIST_FREE1,
+  PB_Q_FULL0, PB_Q_FULL1, PB_Q_FREE0, PB_Q_FREE1,
+  PB_K_FULL0, PB_K_FULL1, PB_K_FREE0, PB_K_FREE1,
+  PB_V_FULL0, PB_V_FULL1, PB_V_FREE0, PB_V_FREE1,
+  PB_S0, PB_S1, PB_PH0, PB_PH1, PB_P0, PB_P1, PB_O0, PB_O1, PB_EPI0, PB_EPI1,
+  PB_NUM
+};
+constexpr int kListConsumers = 2 + 256;  // producer, MMA warp (one lane each), every softmax thread
+
+template <int HD>
+struct __align__(1024) FwdPersistentSmem {
+  uint8_t q[2][kTileBytesOf<HD>];
+  uint8_t k[2][kTileBytesOf<HD>];
+  uint8_t v[2][kTileBytesOf<HD>];
+  uint16_t merged[2][kMaxKvTiles];  // kv tile | class for tile A << 12 | class for tile B << 14  (1 partial, 2 full)
+  uint8_t cls[kMaxKvTiles];         // scratch of the list builder: class A | class B << 2
+  uint64_t bar[PB_NUM];
+  int4 item[2];                     // (pair, h, b, number of merged kv tiles; -1 = no more work)
+  uint32_t tmem_base;
+};
+
+struct FwdPersistentParams {
+  FwdParams f;
+  int* counter;      // zeroed before the launch
+  int n_pairs;       // ceil(NQ / 2)
+  int group_heads;   // heads (b * Hq + h, flattened) per scheduling group
+};
+
+// item index -> (pair, h, b): groups of `group_heads` consecutive heads, inside a group the heaviest
+// (last) pair of every head first.  Heads of a group share their K/V in L2 while they run side by side.
+__device__ __forceinline__ void decode_item(const FwdPersistentParams& p, int w, int& pair, int& h, int& b) {
+  const int BH = p.f.a.B * p.f.a.Hq, NP = p.n_pairs;
+  const int per_group = p.group_heads * NP;
+  const int full_groups = BH / p.group_heads;
+  int g = w / per_group;
+  int gh = p.group_heads;
+  if (g >= full_groups) { g = full_groups; gh = BH - full_groups * p.group_heads; }
+  const int r = w - g * per_group;
+  pair = NP - 1 - r / gh;
+  const int bh = g * p.group_heads + r % gh;
+  h = bh % p.f.a.Hq;
+  b = bh / p.f.a.Hq;
+}
+
+template <int HD, bool KB>
+__global__ void __launch_bounds__(kThreads, 1)
+fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                      const FwdPersistentParams pp) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  constexpr uint32_t kTileBytes = kTileBytesOf<HD>;
+  FwdPersistentSmem<HD>& sm = *reinterpret_cast<FwdPersistentSmem<HD>*>(smem_raw);
+  const FwdParams& p = pp.f;
+  const bma_attn_args& a = p.a;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
+  const int wg = warp >> 2;
+  const int NQ = p.l.NQ, NKV = p.l.NKV;
+  const int n_items = pp.n_pairs * a.Hq * a.B;
+  const int G = a.Hq / a.Hkv;
+
+  if ((smem_u32(smem_raw) & 1023u) != 0u) {
+    if (threadIdx.x == 0) report_device_error(p.status, 101);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < PB_NUM; ++i) {
+      uint32_t count = 1;
+      if (i == PB_LIST_FREE0 || i == PB_LIST_FREE1) count = kListConsumers;
+      else if (i >= PB_PH0 && i <= PB_P1) count = 128;
+      else if (i == PB_EPI0 || i == PB_EPI1) count = 128;
+      mbar_init(&sm.bar[i], count);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(&sm.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  if (wg == 2) {
+    setmaxnreg_dec_80();
+    if (warp == 10) {
+      // ------------------------------------------------------------ scheduler + kv list merge (whole warp)
+      bool ok = true;
+      for (int it = 0; ok; ++it) {
+        const int slot = it & 1;
+        if (it >= 2) ok = mbar_wait_relaxed(&sm.bar[PB_LIST_FREE0 + slot], ((it >> 1) - 1) & 1);
+        if (!ok) break;
+        int w = 0;
+        if (lane == 0) w = atomicAdd(pp.counter, 1);
+        w = __shfl_sync(0xffffffffu, w, 0);
+        if (w >= n_items) {
+          if (lane == 0) {
+            sm.item[slot] = make_int4(0, 0, 0, -1);
+            mbar_arrive(&sm.bar[PB_LIST_FULL0 + slot]);
+          }
+          break;
+        }
+        int pair, h, b;
+        decode_item(pp, w, pair, h, b);
+        const int lb = p.l.B == 1 ? 0 : b, lh = p.l.H == 1 ? 0 : h;
+        for (int i = lane * 16; i < NKV; i += 32 * 16) *reinterpret_cast<uint4*>(&sm.cls[i]) = make_uint4(0, 0, 0, 0);
+        __syncwarp();
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const int qi = pair * 2 + x;
+          if (qi < NQ) {
+            const int64_t lrow = ((int64_t)lb * p.l.H + lh) * NQ + qi;
+            const int nfull = p.l.full_kv_num[lrow], npart = p.l.kv_num[lrow];
+            const int32_t* full_idx = p.l.full_kv_idx + lrow * NKV;
+            const int32_t* part_idx = p.l.kv_idx + lrow * NKV;
+            for (int i = lane; i < nfull; i += 32) sm.cls[full_idx[i]] |= (uint8_t)(2u << (2 * x));
+            for (int i = lane; i < npart; i += 32) sm.cls[part_idx[i]] |= (uint8_t)(1u << (2 * x));
+          }
+          __syncwarp();
+        }
+        int count = 0;
+        for (int base = 0; base < NKV; base += 32) {
+          const int j = base + lane;
+          const uint32_t c = j < NKV ? sm.cls[j] : 0u;
+          const unsigned m = __ballot_sync(0xffffffffu, c != 0u);
+          if (c) sm.merged[slot][count + __popc(m & ((1u << lane) - 1))] = (uint16_t)((uint32_t)j | (c << 12));
+          count += __popc(m);
+        }
+        __syncwarp();
+        if (lane == 0) {
+          sm.item[slot] = make_int4(pair, h, b, count);
+          mbar_arrive(&sm.bar[PB_LIST_FULL0 + slot]);   // release: the list and the header are visible to whoever acquires
+        }
+      }
+      if (!ok && lane == 0) report_device_error(p.status, 140);
+    } else if (warp == 8 && lane == 0) {
+      // ------------------------------------------------------------ TMA producer
+      prefetch_tensormap(&map_q);
+      prefetch_tensormap(&map_k);
+      prefetch_tensormap(&map_v);
+      bool ok = true;
+      uint32_t g = 0;   // K/V tiles fetched so far: the ring runs on across items
+      for (int it = 0; ok; ++it) {
+        const int slot = it & 1;
+        ok = mbar_wait(&sm.bar[PB_LIST_FULL0 + slot], (it >> 1) & 1);
+        if (!ok) break;
+        const int4 item = sm.item[slot];
+        const int T = item.w;
+        if (T < 0) break;
+        const int pair = item.x, h = item.y, b = item.z, hk = h / G;
+        auto load_q = [&]() {
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            if (it >= 1) ok = ok && mbar_wait(&sm.bar[PB_Q_FREE0 + x], (it - 1) & 1);   // the previous item's O store has read the buffer
+            if (!ok) return;
+            mbar_expect_tx(&sm.bar[PB_Q_FULL0 + x], kTileBytes);
+#pragma unroll
+            for (int box = 0; box < HD / 64; ++box)
+              tma_load_4d(sm.q[x] + box * kHalfTile, &map_q, &sm.bar[PB_Q_FULL0 + x], box * 64, h, (pair * 2 + x) * BM, b);
+          }
+        };
+        bool q_loaded = false;
+        for (int n = 0; n < T && ok; ++n, ++g) {
+          if (n == 2) { load_q(); q_loaded = true; if (!ok) break; }   // after the first two K/V tiles: those can fly while the previous item still stores
+          const int st = g & 1;
+          const int row0 = (int)(sm.merged[slot][n] & 0xfffu) * BN;
+          if (g >= 2) ok = mbar_wait(&sm.bar[PB_K_FREE0 + st], ((g >> 1) - 1) & 1);
+          if (!ok) break;
+          mbar_expect_tx(&sm.bar[PB_K_FULL0 + st], kTileBytes);
+#pragma unroll
+          for (int box = 0; box < HD / 64; ++box) tma_load_4d(sm.k[st] + box * kHalfTile, &map_k, &sm.bar[PB_K_FULL0 + st], box * 64, hk, row0, b);
+          if (g >= 2) ok = mbar_wait(&sm.bar[PB_V_FREE0 + st], ((g >> 1) - 1) & 1);
+          if (!ok) break;
+          mbar_expect_tx(&sm.bar[PB_V_FULL0 + st], kTileBytes);
+#pragma unroll
+          for (int box = 0; box < HD / 64; ++box) tma_load_4d(sm.v[st] + box * kHalfTile, &map_v, &sm.bar[PB_V_FULL0 + st], box * 64, hk, row0, b);
+        }
+        if (ok && !q_loaded) load_q();
+        if (!ok) break;
+        mbar_arrive(&sm.bar[PB_LIST_FREE0 + slot]);
+      }
+      if (!ok) report_device_error(p.status, 110);
+    } else if (warp == 9) {
+      // ------------------------------------------------------------ MMA issuer (whole warp, one elected lane issues)
+      const bool leader = elect_one();
+      constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc_bf16(BM, HD, 0, 1);
+      const uint64_t dq0 = make_smem_desc(smem_u32(sm.q[0]), 16, 1024), dq1 = make_smem_desc(smem_u32(sm.q[1]), 16, 1024);
+      const uint64_t dk0 = make_smem_desc(smem_u32(sm.k[0]), 16, 1024);
+      const uint64_t dv0 = make_smem_desc(smem_u32(sm.v[0]), kHalfTile, 1024);
+      constexpr uint32_t kStageUnits = kTileBytes >> 4;
+      auto issue_s = [&](int x, int st) {
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off = ((ks >> 2) * kHalfTile + (ks & 3) * 32) >> 4;
+          if (leader) mma_ss(tmem + x * 128, (x == 0 ? dq0 : dq1) + off, dk0 + (uint32_t)(st * kStageUnits + off), idesc_s, ks > 0);
+        }
+        if (leader) mma_commit(&sm.bar[PB_S0 + x]);
+      };
+      bool ok = true;
+      uint32_t g0 = 0;                 // ring index of the item's first K/V tile
+      uint32_t done0 = 0, done1 = 0;   // tiles multiplied so far per q tile, over all items (phase counters of PH / P)
+      for (int it = 0; ok; ++it) {
+        const int slot = it & 1;
+        ok = mbar_wait(&sm.bar[PB_LIST_FULL0 + slot], (it >> 1) & 1);
+        if (!ok) break;
+        const int T = sm.item[slot].w;
+        if (T < 0) break;
+        bool have_q0 = false, have_q1 = false;
+        auto need_q = [&](int x) {   // the item's Q tile has landed (asked once, before the first S of that tile)
+          bool& have = x == 0 ? have_q0 : have_q1;
+          if (!have) { ok = ok && mbar_wait(&sm.bar[PB_Q_FULL0 + x], it & 1); have = true; }
+        };
+        int cnt0 = 0, cnt1 = 0;        // tiles accumulated into O_x within this item
+        if (T > 0) {
+          const int st = g0 & 1;
+          ok = mbar_wait(&sm.bar[PB_K_FULL0 + st], (g0 >> 1) & 1);
+          const uint32_t e = sm.merged[slot][0];
+          if (ok && ((e >> 12) & 3u)) { need_q(0); if (ok) { tc_fence_after(); issue_s(0, st); } }
+          if (ok && ((e >> 14) & 3u)) { need_q(1); if (ok) { tc_fence_after(); issue_s(1, st); } }
+          if (ok && leader) mma_commit(&sm.bar[PB_K_FREE0 + st]);
+        }
+        for (int n = 0; n < T && ok; ++n) {
+          const uint32_t g = g0 + (uint32_t)n;
+          const int st = g & 1;
+          const uint32_t e = sm.merged[slot][n];
+          const uint32_t e_next = (n + 1 < T) ? (uint32_t)sm.merged[slot][n + 1] : 0u;
+          ok = mbar_wait(&sm.bar[PB_V_FULL0 + st], (g >> 1) & 1);
+          if (ok && n + 1 < T) ok = mbar_wait(&sm.bar[PB_K_FULL0 + (st ^ 1)], ((g + 1) >> 1) & 1);
+          if (!ok) break;
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            if ((e >> (12 + 2 * x)) & 3u) {
+              int& cnt = x == 0 ? cnt0 : cnt1;
+              uint32_t& done = x == 0 ? done0 : done1;
+#pragma unroll
+              for (int hf = 0; hf < 2; ++hf) {
+                ok = mbar_wait(&sm.bar[(hf == 0 ? PB_PH0 : PB_P0) + x], done & 1);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = hf * 4; ks < hf * 4 + 4; ++ks)
+                  if (leader)
+                    mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, dv0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)),
+                           idesc_o, (cnt > 0) || (ks > 0));
+              }
+              if (!ok) break;
+              if (leader) mma_commit(&sm.bar[PB_O0 + x]);
+              ++cnt;
+              ++done;
+            }
+            if ((e_next >> (12 + 2 * x)) & 3u) {
+              need_q(x);
+              if (!ok) break;
+              tc_fence_after();
+              issue_s(x, st ^ 1);
+            }
+          }
+          if (!ok) break;
+          if (leader) {
+            mma_commit(&sm.bar[PB_V_FREE0 + st]);
+            if (n + 1 < T) mma_commit(&sm.bar[PB_K_FREE0 + (st ^ 1)]);
+          }
+        }
+        if (!ok) break;
+        g0 += (uint32_t)T;
+        if (leader) mbar_arrive(&sm.bar[PB_LIST_FREE0 + slot]);
+      }
+      if (!ok && leader) report_device_error(p.status, 120);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warpgroups
+    setmaxnreg_inc_208();
+    const int x = wg;
+    const int row = threadIdx.x & 127;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem + x * 128 + lane_base, tmem_o = tmem + 256 + x * 128 + lane_base;
+    const int sh = 12 + 2 * x;
+    bool ok = true;
+    uint32_t done = 0;    // tiles of this q tile processed over all items (phase counter of S / PH / P / O)
+    uint32_t syncs = 0;   // rendezvous of this tile's 128 threads so far
+    for (int it = 0; ok; ++it) {
+      const int slot = it & 1;
+      ok = mbar_wait(&sm.bar[PB_LIST_FULL0 + slot], (it >> 1) & 1);
+      if (!ok) break;
+      const int4 item = sm.item[slot];
+      const int T = item.w;
+      if (T < 0) break;
+      const int pair = item.x, h = item.y, b = item.z;
+      const int qi = pair * 2 + x;
+      const int q = qi * BM + row;
+      const float kb2 = (KB && a.key_bias) ? __ldg(a.key_bias + h) * kLog2e : 0.f;
+      float m_ref = -INFINITY;
+      float l = 0.f;
+      int cnt = 0;
+
+      for (int n = 0; n < T; ++n) {
+        const uint32_t e = sm.merged[slot][n];
+        const uint32_t cls = (e >> sh) & 3u;
+        if (cls == 0) continue;
+        const int k0 = (int)(e & 0xfffu) * BN;
+        ok = mbar_wait(&sm.bar[PB_S0 + x], done & 1);
+        if (!ok) break;
+        tc_fence_after();
+        float s[BN];
+        {
+          uint32_t r0[32], r1[32], r2[32], r3[32];
+          tmem_ld32(tmem_s + 0, r0);
+          tmem_ld32(tmem_s + 32, r1);
+          tmem_ld32(tmem_s + 64, r2);
+          tmem_ld32(tmem_s + 96, r3);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            s[j] = __uint_as_float(r0[j]);
+            s[32 + j] = __uint_as_float(r1[j]);
+            s[64 + j] = __uint_as_float(r2[j]);
+            s[96 + j] = __uint_as_float(r3[j]);
+          }
+        }
+        const float sc = KB ? 1.f : p.scale_log2;
+        if constexpr (KB) {
+          const float base = kb2 * (float)(p.spec.k_offset + k0);
+#pragma unroll
+          for (int j = 0; j < BN; ++j) s[j] = fmaf(s[j], p.scale_log2, fmaf((float)j, kb2, base));
+        }
+        if (cls == 1) {
+          uint32_t bits[4];
+          {
+            // the mask description is rebuilt from the kernel parameters here rather than carried in registers through the full tiles
+            const MaskView mv = make_mask_view(p.spec, b, h);
+            int jlo, jhi;
+            row_interval(mv, q, k0, jlo, jhi);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const int lo = max(jlo - c * 32, 0), hi = min(jhi - c * 32, 31);
+              bits[c] = (lo <= hi) ? ((0xffffffffu >> (31 - hi)) & (0xffffffffu << lo)) : 0u;
+            }
+            if (mv.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP)) {
+#pragma unroll
+              for (int c = 0; c < 4; ++c)
+                if (bits[c]) bits[c] &= table_bits_row32(mv, q, k0 + c * 32);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < BN; ++j) s[j] = (bits[j >> 5] >> (j & 31)) & 1u ? s[j] : -INFINITY;
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < BN; j += 8) {
+          mx0 = max3(mx0, s[j], s[j + 1]);
+          mx1 = max3(mx1, s[j + 2], s[j + 3]);
+          mx2 = max3(mx2, s[j + 4], s[j + 5]);
+          mx3 = max3(mx3, s[j + 6], s[j + 7]);
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        const float m_cand = fmaxf(m_ref, mx * sc);
+        const bool grow = (m_cand - m_ref) > kRescaleThreshold;
+        float alpha = 1.f;
+        if (grow) {
+          alpha = ex2(m_ref - m_cand);
+          m_ref = m_cand;
+        }
+        if (cnt > 0 && __any_sync(0xffffffffu, grow)) {
+          ok = mbar_wait(&sm.bar[PB_O0 + x], (done - 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tmem_o + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+            tmem_st32(tmem_o + c * 32, r);
+          }
+        }
+        const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
+        float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float e0 = ex2(fmaf(s[c * 64 + 2 * j], sc, -m_sub));
+            const float e1 = ex2(fmaf(s[c * 64 + 2 * j + 1], sc, -m_sub));
+#if BMA_FWD_POLY >= 2
+            const float e2 = exp2_fma(fmaf(s[c * 64 + 2 * j + 2], sc, -m_sub));
+#else
+            const float e2 = ex2(fmaf(s[c * 64 + 2 * j + 2], sc, -m_sub));
+#endif
+#if BMA_FWD_POLY >= 1
+            const float e3 = exp2_fma(fmaf(s[c * 64 + 2 * j + 3], sc, -m_sub));
+#else
+            const float e3 = ex2(fmaf(s[c * 64 + 2 * j + 3], sc, -m_sub));
+#endif
+            rs0 += e0; rs1 += e1; rs2 += e2; rs3 += e3;
+            pk[j] = pack_bf16(e0, e1);
+            pk[j + 1] = pack_bf16(e2, e3);
+          }
+          tmem_st32(tmem_s + c * 32, pk);
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(&sm.bar[(c == 0 ? PB_PH0 : PB_P0) + x]);
+        }
+        l = l * alpha + ((rs0 + rs1) + (rs2 + rs3));
+        ++cnt;
+        ++done;
+      }
+      if (!ok) break;
+      mbar_arrive(&sm.bar[PB_LIST_FREE0 + slot]);   // this thread has read the last list entry it needs
+
+      // ---- epilogue of the item: O / l and the log-sum-exp.  O is staged in the tile's own Q buffer (every S MMA that
+      // read it has completed once the last P V has) and leaves as TMA stores; the buffer goes back to the producer after.
+      if (cnt > 0) ok = mbar_wait(&sm.bar[PB_O0 + x], (done - 1) & 1);
+      else ok = mbar_wait(&sm.bar[PB_Q_FULL0 + x], it & 1);   // nobody consumed Q: let its load land before the buffer is written
+      if (!ok) break;
+      tc_fence_after();
+      const bool dead = (m_ref == -INFINITY);
+      const float inv = (l > 0.f && !dead) ? 1.f / l : 0.f;
+      uint8_t* q_row = sm.q[x] + row * 128;
+      auto rendezvous = [&]() {
+        mbar_arrive(&sm.bar[PB_EPI0 + x]);
+        ok = ok && mbar_wait(&sm.bar[PB_EPI0 + x], syncs & 1);
+        ++syncs;
+      };
+      if (a.o.dtype == BMA_DTYPE_F32) {
+        constexpr int kBoxes = HD / 64;
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+#pragma unroll
+          for (int cc = 0; cc < kBoxes; ++cc) {
+            uint32_t r[32];
+            if (cnt > 0) {
+              tmem_ld32(tmem_o + (pass * kBoxes + cc) * 32, r);
+              tmem_wait_ld();
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const float4 v4 = make_float4(__uint_as_float(r[u * 4]) * inv, __uint_as_float(r[u * 4 + 1]) * inv,
+                                            __uint_as_float(r[u * 4 + 2]) * inv, __uint_as_float(r[u * 4 + 3]) * inv);
+              *reinterpret_cast<float4*>(q_row + cc * kHalfTile + ((u ^ (row & 7)) * 16)) = v4;
+            }
+          }
+          if (pass == 1) tc_fence_before();   // the O columns are free for the next item's first P V (ordered by this tile's next P arrival)
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          rendezvous();
+          if (ok && row == 0) {
+            if (qi < NQ) {
+#pragma unroll
+              for (int cc = 0; cc < kBoxes; ++cc) tma_store_4d(&map_o, sm.q[x] + cc * kHalfTile, (pass * kBoxes + cc) * 32, h, qi * BM, b);
+              bulk_commit();
+              bulk_wait_read0();
+            }
+            if (pass == 1) mbar_arrive(&sm.bar[PB_Q_FREE0 + x]);
+          }
+          if (pass == 0) rendezvous();
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t r[32];
+          if (cnt > 0) {
+            tmem_ld32(tmem_o + c * 32, r);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int j = u * 8;
+            uint4 v4;
+            v4.x = pack_bf16(__uint_as_float(r[j]) * inv, __uint_as_float(r[j + 1]) * inv);
+            v4.y = pack_bf16(__uint_as_float(r[j + 2]) * inv, __uint_as_float(r[j + 3]) * inv);
+            v4.z = pack_bf16(__uint_as_float(r[j + 4]) * inv, __uint_as_float(r[j + 5]) * inv);
+            v4.w = pack_bf16(__uint_as_float(r[j + 6]) * inv, __uint_as_float(r[j + 7]) * inv);
+            const int chunk = ((c & 1) * 4 + u) ^ (row & 7);
+            *reinterpret_cast<uint4*>(q_row + (c >> 1) * kHalfTile + chunk * 16) = v4;
+          }
+        }
+        tc_fence_before();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        rendezvous();
+        if (ok && row == 0) {
+          if (qi < NQ) {
+#pragma unroll
+            for (int box = 0; box < HD / 64; ++box) tma_store_4d(&map_o, sm.q[x] + box * kHalfTile, box * 64, h, qi * BM, b);
+            bulk_commit();
+            bulk_wait_read0();
+          }
+          mbar_arrive(&sm.bar[PB_Q_FREE0 + x]);
+        }
+      }
+      if (!ok) break;
+      if (qi < NQ && q < a.N && a.lse)
+        a.lse[((int64_t)b * a.Hq + h) * a.N + q] = (l > 0.f && !dead) ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+    }
+    if (!ok) report_device_error(p.status, 200 + warp);
+  }
+
+  // ---- teardown: every thread arrives here (all waits above are bounded)
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem, kTmemCols);
+}
+
 }  // namespace
 
 // ---- host ------------------------------------------------------------------------------------
@@ -551,6 +1082,43 @@ static bool tma_compatible(const bma_tensor& t) {
          t.stride_h > 0;
 }
 
+// Work counters of the persistent kernels: a small pool inside the library image (nothing is allocated), handed out
+// round robin and zeroed on the launch's stream before each launch.  Two launches share a counter only if more than
+// kWorkCounters persistent launches are in flight at once on different streams of one device.
+namespace {
+constexpr int kWorkCounters = 256;
+__device__ int g_work_counters[kWorkCounters];
+}  // namespace
+int* work_counter_slot() {
+  static std::mutex mu;
+  static int* base[64] = {};
+  static unsigned next = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!base[dev]) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_work_counters);
+    if (e != cudaSuccess) { set_last_cuda_error(e, "cudaGetSymbolAddress(work counters)"); return nullptr; }
+    base[dev] = static_cast<int*>(ptr);
+  }
+  return base[dev] + (next++ % kWorkCounters);
+}
+
+// Which forward kernel: the persistent one wins where a row of the mask has few kv tiles (a sliding window: set-up,
+// pipeline fill and the output store are a large share of such an item and overlap the next item there; measured
+// +15 % on a +-256-token window at L = 8192) and loses a few per cent on long rows (its main loop is 3-4 % slower per
+// tile than the one-item-per-CTA kernel's, which the saved set-up no longer outweighs at 17 tiles per item).
+// BMA_FWD_PERSISTENT=0 / 1 forces one of the two (A/B measurements).
+static bool fwd_persistent_enabled(const bma_mask_spec& spec) {
+  const char* e = getenv("BMA_FWD_PERSISTENT");   // read per call, so that a test can switch it
+  if (e && e[0]) return e[0] != '0';
+  int64_t width = INT64_MAX;   // upper bound of the keys a query row can see
+  if (spec.flags & BMA_MASK_BAND) width = std::min<int64_t>(width, (int64_t)spec.band_left + spec.band_right + 1);
+  if (spec.flags & BMA_MASK_BLOCK_WINDOW) width = std::min<int64_t>(width, (int64_t)(spec.win_left + spec.win_right) * spec.win_block);
+  return width <= 10 * BN;
+}
+
 bool sm100_supported(const bma_attn_args& a) {
   static int cc_major = -1;
   if (cc_major < 0) {
@@ -587,13 +1155,40 @@ int sm100_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   p.interval_mask = (spec.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP)) ? 0 : 1;
   p.status = device_status_ptr();
   BMA_REQUIRE(p.status != nullptr, BMA_ERR_CUDA);
+  const bool kb = a.key_bias != nullptr || a.scale < 0.f;
+  if (fwd_persistent_enabled(spec)) {
+    // One CTA per SM for the whole launch; items are drawn from a counter that is zeroed on the stream first.
+    int dev = 0, sms = 148;
+    BMA_CUDA_TRY(cudaGetDevice(&dev));
+    BMA_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    FwdPersistentParams pp;
+    pp.f = p;
+    pp.n_pairs = ceil_div(ceil_div(a.N, BM), 2);
+    const int64_t n_items = (int64_t)pp.n_pairs * a.Hq * a.B;
+    BMA_REQUIRE(n_items < (int64_t)INT32_MAX - sms - 1, BMA_ERR_LIMIT);
+    pp.group_heads = std::max(1, std::min(a.B * a.Hq, ceil_div(2 * sms, pp.n_pairs)));
+    pp.counter = work_counter_slot();
+    BMA_REQUIRE(pp.counter != nullptr, BMA_ERR_CUDA);
+    BMA_CUDA_TRY(cudaMemsetAsync(pp.counter, 0, sizeof(int), st));
+    const dim3 pgrid((unsigned)std::min<int64_t>(n_items, sms));
+    auto plaunch = [&](auto kernel, size_t smem) -> int {
+      BMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      kernel<<<pgrid, kThreads, smem, st>>>(mq, mk, mv, mo, pp);
+      return BMA_OK;
+    };
+    if (a.d == 128) rc = kb ? plaunch(fwd_persistent_kernel<128, true>, sizeof(FwdPersistentSmem<128>)) : plaunch(fwd_persistent_kernel<128, false>, sizeof(FwdPersistentSmem<128>));
+    else rc = kb ? plaunch(fwd_persistent_kernel<64, true>, sizeof(FwdPersistentSmem<64>)) : plaunch(fwd_persistent_kernel<64, false>, sizeof(FwdPersistentSmem<64>));
+    if (rc) return rc;
+    count_launches(1);
+    BMA_CUDA_TRY(cudaGetLastError());
+    return BMA_OK;
+  }
   dim3 grid(ceil_div(ceil_div(a.N, BM), 2), a.Hq, a.B);
   auto launch = [&](auto kernel, size_t smem) -> int {
     BMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kernel<<<grid, kThreads, smem, st>>>(mq, mk, mv, mo, p);
     return BMA_OK;
   };
-  const bool kb = a.key_bias != nullptr || a.scale < 0.f;
   if (a.d == 128) rc = kb ? launch(fwd_kernel<128, true>, sizeof(FwdSmem<128>)) : launch(fwd_kernel<128, false>, sizeof(FwdSmem<128>));
   else rc = kb ? launch(fwd_kernel<64, true>, sizeof(FwdSmem<64>)) : launch(fwd_kernel<64, false>, sizeof(FwdSmem<64>));
   if (rc) return rc;

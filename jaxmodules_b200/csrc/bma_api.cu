@@ -7,6 +7,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "ptx_sm100.cuh"
 
 namespace bma {
 
@@ -27,12 +28,6 @@ std::mutex g_status_mutex;
 std::atomic<unsigned long long> g_launches{0};
 }  // namespace
 
-static thread_local cudaEvent_t g_bwd_mark = nullptr;
-static cudaEvent_t take_bwd_mark() {
-  cudaEvent_t ev = g_bwd_mark;
-  g_bwd_mark = nullptr;
-  return ev;
-}
 void count_launches(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
 void set_last_cuda_error(cudaError_t e, const char* where) {
@@ -189,6 +184,25 @@ __global__ void merge_kernel(bma_attn_args a) {
     }
     for (int c = lane; c < a.d; c += 32) oa[c] = wa * oa[c] + wb * ob[c];
     if (lane == 0) a.lse[li] = l;
+  }
+}
+
+// ---- self-test of the bounded waits ------------------------------------------------------------
+// One CTA waits on an mbarrier that nobody arrives at, with the same polling scheme as the attention kernels but a
+// caller-chosen time limit; when the limit passes it records `code` in the status word and returns.  Nothing
+// faults, traps or hangs: this is how a host learns of a lost producer without losing the context.
+__global__ void expire_wait_kernel(int* status, unsigned long long limit_ns, int code) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bar, 1);
+    ptx::fence_barrier_init();
+    const uint64_t t0 = ptx::global_timer_ns();
+    bool done = false;
+    for (uint32_t i = 0; i < (1u << 26) && !done; ++i) {
+      if (ptx::mbar_try_wait(&bar, 0)) done = true;
+      else if ((i & 63u) == 63u && ptx::global_timer_ns() - t0 > limit_ns) break;
+    }
+    if (!done) report_device_error(status, code);
   }
 }
 
@@ -363,16 +377,30 @@ size_t bma_attn_bwd_workspace_bytes(const bma_attn_args* args) {
   return pick_backend_bwd(args) == BMA_BACKEND_TCGEN05 ? sm100_bwd_workspace_bytes(*args) : 0;
 }
 
-void bma_attn_bwd_mark(void* cuda_event) { g_bwd_mark = static_cast<cudaEvent_t>(cuda_event); }
+size_t bma_attn_bwd_scratch_bytes(const bma_attn_args* args, const bma_block_lists* lists, const int64_t* visited_host) {
+  if (validate_common(args) != BMA_OK || !lists) return 0;
+  return pick_backend_bwd(args) == BMA_BACKEND_TCGEN05 ? sm100_bwd_scratch_bytes(*args, *lists, visited_host) : 0;
+}
 
-size_t bma_attn_bwd_scratch_bytes(const bma_attn_args* args) {
-  if (validate_common(args) != BMA_OK) return 0;
-  return pick_backend_bwd(args) == BMA_BACKEND_TCGEN05 ? sm100_bwd_scratch_bytes(*args) : 0;
+int bma_block_lists_visited(const bma_block_lists* lists, int64_t* visited, bma_stream_t stream) {
+  BMA_REQUIRE(lists && visited, BMA_ERR_ARG);
+  BMA_REQUIRE(lists->B > 0 && lists->H > 0 && lists->NQ > 0 && lists->kv_num && lists->full_kv_num, BMA_ERR_ARG);
+  return block_lists_visited(*lists, visited, static_cast<cudaStream_t>(stream));
+}
+
+int bma_debug_expire_wait(uint64_t limit_ns, int32_t code, bma_stream_t stream) {
+  BMA_REQUIRE(limit_ns > 0 && limit_ns <= 1000000000ull && code > 0, BMA_ERR_ARG);   // at most one second
+  int* status = device_status_ptr();
+  BMA_REQUIRE(status != nullptr, BMA_ERR_CUDA);
+  expire_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, limit_ns, code);
+  count_launches(1);
+  BMA_CUDA_TRY(cudaGetLastError());
+  return BMA_OK;
 }
 
 int bma_attn_bwd(const bma_attn_args* args, const bma_mask_spec* spec, const bma_block_lists* lists, void* workspace,
-                 size_t workspace_bytes, bma_stream_t stream) {
-  cudaEvent_t mark = take_bwd_mark();  // consumed by this call whatever its outcome
+                 size_t workspace_bytes, const int64_t* visited_host, void* mid_event, bma_stream_t stream) {
+  cudaEvent_t mark = static_cast<cudaEvent_t>(mid_event);
   int rc = validate_common(args);
   if (rc != BMA_OK) return rc;
   BMA_REQUIRE(spec != nullptr, BMA_ERR_ARG);
@@ -394,7 +422,7 @@ int bma_attn_bwd(const bma_attn_args* args, const bma_mask_spec* spec, const bma
   if (be == BMA_BACKEND_TCGEN05) {
     const size_t need = sm100_bwd_workspace_bytes(*args);
     BMA_REQUIRE(need == 0 || (workspace && workspace_bytes >= need), BMA_ERR_WORKSPACE);
-    return sm100_bwd(*args, *spec, *lists, workspace, workspace_bytes, mark, st);
+    return sm100_bwd(*args, *spec, *lists, workspace, workspace_bytes, visited_host, mark, st);
   }
   return simt_bwd(*args, *spec, *lists, st);
 }

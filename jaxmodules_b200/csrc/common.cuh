@@ -172,11 +172,23 @@ int simt_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_
 int simt_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, cudaStream_t st);
 int sm100_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, cudaStream_t st);
 int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, void* ws,
-              size_t ws_bytes, cudaEvent_t mark, cudaStream_t st);
+              size_t ws_bytes, const int64_t* visited_host, cudaEvent_t mark, cudaStream_t st);
 size_t sm100_bwd_workspace_bytes(const bma_attn_args& a);
-size_t sm100_bwd_scratch_bytes(const bma_attn_args& a);
+size_t sm100_bwd_scratch_bytes(const bma_attn_args& a, const bma_block_lists& lists, const int64_t* visited_host);
 bool sm100_supported(const bma_attn_args& a);
 bool sm100_bwd_supported(const bma_attn_args& a);
+
+// Compact slot addressing of the backward scratch (bwd_slots.cu): tables at the front of the workspace.
+struct SlotTables {
+  int64_t* head_base;   // [B*Hq + 1] exclusive prefix of visited blocks over (b, h), row-major
+  int64_t* head_total;  // [lists.B * lists.H]
+  int32_t* row_base;    // [lists.B, lists.H, NQ] exclusive prefix inside a list head
+  int32_t* rank;        // [lists.B, lists.H, NQ, NKV] position of kj among the row's visited tiles, -1 = not visited
+  size_t bytes;         // size of the tables (a multiple of 1024); the slots follow
+};
+SlotTables slot_tables_layout(const bma_attn_args& a, const bma_block_lists& l, void* ws);
+int slot_tables_build(const bma_attn_args& a, const bma_block_lists& l, const SlotTables& t, cudaStream_t st);
+int block_lists_visited(const bma_block_lists& l, int64_t* visited, cudaStream_t st);
 
 constexpr int kSimtTile = 64;
 constexpr int kSm100Tile = 128;

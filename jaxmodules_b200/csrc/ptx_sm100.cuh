@@ -55,6 +55,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
+// The same bounded wait for a warp that is in no hurry (a scheduler preparing work an item ahead): it sleeps
+// between polls, so that its spinning does not take issue slots from the warps that share its scheduler.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t i = 0; i < (1u << 24); ++i) {
+    __nanosleep(400);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && global_timer_ns() - t0 > 2000000000ull) return false;
+  }
+  return false;
+}
+
 // ---- TMA -----------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -101,6 +101,14 @@ class _ReadyLists:
             self._consistent = bool(torch.equal(kv, q.transpose(-1, -2)))
         return self._consistent
 
+    def visited_counts(self, lists, device):
+        """Host array of visited (full + partial) blocks per list head (sizes the backward scratch); the lists of a
+        BlockMask do not change, so the counts are fetched from the device once."""
+        if getattr(self, "_visited", None) is None:
+            kv_num, _, fkv_num, _ = self._kv_side()
+            self._visited = (kv_num.sum(dim=-1, dtype=torch.int64) + fkv_num.sum(dim=-1, dtype=torch.int64)).reshape(-1).cpu().numpy()
+        return self._visited
+
     def __call__(self, q_tile: int, kv_tile: int, q_side: bool):
         bm = self.bm
         if q_tile != bm.Q_BLOCK_SIZE or kv_tile != bm.KV_BLOCK_SIZE:

@@ -14,6 +14,7 @@ one of two forms:
 """
 from __future__ import annotations
 
+import weakref
 from dataclasses import dataclass, field, replace
 from typing import Callable, Optional, Tuple
 
@@ -178,6 +179,30 @@ class DeviceMask:
     depends_h: bool = False
 
 
+# Device copies of host-side mask arrays (segment ids, bit tables), kept for as long as the source tensor lives and
+# has not been written to: a mask object built once is shipped to the GPU once, not at every attention call, and the
+# per-mask caches further down (visited-block counts) can recognise it by its device tensor.
+_device_copies = {}   # id(source) -> (weakref to source, {(device, dtype): (source version, copy)})
+
+
+def _on_device(t: torch.Tensor, device, dtype=None) -> torch.Tensor:
+    device = torch.device(device)
+    dtype = dtype or t.dtype
+    if t.device == device and t.dtype == dtype and t.is_contiguous():
+        return t
+    entry = _device_copies.get(id(t))
+    if entry is None or entry[0]() is not t:
+        entry = (weakref.ref(t), {})
+        _device_copies[id(t)] = entry
+        weakref.finalize(t, _device_copies.pop, id(t), None)
+    hit = entry[1].get((device, dtype))
+    if hit is not None and hit[0] == t._version:
+        return hit[1]
+    copy = t.to(device=device, dtype=dtype).contiguous()
+    entry[1][(device, dtype)] = (t._version, copy)
+    return copy
+
+
 def to_device_mask(terms: MaskTerms, N: int, L: int, device) -> DeviceMask:
     s = nat.MaskSpec()
     keep = []
@@ -195,8 +220,8 @@ def to_device_mask(terms: MaskTerms, N: int, L: int, device) -> DeviceMask:
     depends_b = depends_h = False
     if terms.seg_q is not None:
         flags |= nat.BMA_MASK_SEGMENT
-        sq = terms.seg_q.to(device=device, dtype=torch.int32).contiguous()
-        sk = sq if terms.seg_k is terms.seg_q else terms.seg_k.to(device=device, dtype=torch.int32).contiguous()
+        sq = _on_device(terms.seg_q, device, torch.int32)
+        sk = sq if terms.seg_k is terms.seg_q else _on_device(terms.seg_k, device, torch.int32)
         if sq.shape[1] < N + terms.q_offset or sk.shape[1] < L + terms.k_offset:
             raise ValueError("segment id arrays are shorter than the sequences")
         keep += [sq, sk]
@@ -205,7 +230,7 @@ def to_device_mask(terms: MaskTerms, N: int, L: int, device) -> DeviceMask:
         depends_b = True
     if terms.bitmap is not None:
         flags |= nat.BMA_MASK_BITMAP
-        bm = terms.bitmap.to(device=device).contiguous()
+        bm = _on_device(terms.bitmap, device)
         keep.append(bm)
         s.bitmap = bm.data_ptr()
         s.bitmap_B, s.bitmap_H, s.bitmap_q, s.bitmap_words = bm.shape
@@ -231,11 +256,25 @@ def _table_from_program(mask_fn, nargs: int, B: int, Hq: int, N: int, L: int, de
     return mp.build_table(prog, B, Hq, N, L, device)
 
 
+# Bit tables already built for a callable: function object -> {(B, Hq, N, L, device): MaskTerms}.  The reference
+# re-traces mask_fn at every call (jaxmodules/attention.py:70-73); here the table of a given function object is built
+# once per shape and device.  A function whose result depends on state it captured and that state changes must be
+# passed as a new function object (or the cache cleared with clear_mask_cache()).
+_terms_of_callable = weakref.WeakKeyDictionary()
+
+
+def clear_mask_cache() -> None:
+    """Forgets every cached bit table, device copy and per-mask count."""
+    _terms_of_callable.clear()
+    _device_copies.clear()
+    _visited_counts.clear()
+
+
 def terms_from_mask_fn(mask_fn, B: int, Hq: int, N: int, L: int, device=None) -> MaskTerms:
     """Structured masks pass through; any other callable becomes a bit table — built on the GPU
     from the traced mask program when ``device`` is a CUDA device and the function can be traced
     (arithmetic, comparisons, ``& | ~``, ``mask_program.where`` / ``Table``), evaluated on the host
-    over index grids otherwise."""
+    over index grids otherwise.  The table is cached on the function object (see ``clear_mask_cache``)."""
     if mask_fn is None:
         return MaskTerms()
     if isinstance(mask_fn, StructuredMask):
@@ -243,6 +282,22 @@ def terms_from_mask_fn(mask_fn, B: int, Hq: int, N: int, L: int, device=None) ->
         if t.seg_q is not None and t.seg_q.shape[0] != B:
             raise ValueError("document_mask batch size differs from the batch size of Q")
         return t
+    key = (B, Hq, N, L, None if device is None else str(torch.device(device)))
+    try:
+        cached = _terms_of_callable.get(mask_fn)
+    except TypeError:          # not weak-referenceable (a callable object without __weakref__): never cached
+        cached = None
+    if cached is not None and key in cached:
+        return cached[key]
+    terms = _build_terms_from_callable(mask_fn, B, Hq, N, L, device)
+    try:
+        _terms_of_callable.setdefault(mask_fn, {})[key] = terms
+    except TypeError:
+        pass
+    return terms
+
+
+def _build_terms_from_callable(mask_fn, B: int, Hq: int, N: int, L: int, device=None) -> MaskTerms:
     n = argcount(mask_fn)
     if n in (3, 4) and device is not None and torch.device(device).type == "cuda":
         bits = _table_from_program(mask_fn, n, B, Hq, N, L, device)
@@ -254,3 +309,31 @@ def terms_from_mask_fn(mask_fn, B: int, Hq: int, N: int, L: int, device=None) ->
     if n == 4:
         return MaskTerms(bitmap=bitmap_from_callable(mask_fn, B, Hq, N, L, batch_dependent=True))
     raise TypeError("mask_fn must take (b, h, q, k) or (h, q, k)")
+
+
+# ---- visited-block counts per mask ---------------------------------------------------------------
+# The backward scratch is sized by the number of visited blocks, which lives on the device.  It is fetched once per
+# distinct mask (a host synchronisation) and remembered: masks without arrays by their parameters, masks with arrays
+# by the identity and version of their device tensors.
+_visited_counts = {}   # key -> (weakrefs of the mask's device tensors, numpy int64 [LB * LH])
+
+
+def visited_counts(dmask: DeviceMask, lists: "nat.BlockLists", device, extra_key=()):
+    """Host int64 array [lists.B * lists.H] of visited (full + partial) blocks per list head for the lists just
+    compiled from ``dmask``; cached per mask, shape and tile size."""
+    import ctypes as C
+    s = dmask.spec
+    key = (s.flags, s.q_valid, s.k_valid, s.q_offset, s.k_offset, s.band_left, s.band_right, s.win_block, s.win_left,
+           s.win_right, s.win_nblk, tuple((id(t), t._version, tuple(t.shape)) for t in dmask.keep),
+           lists.B, lists.H, lists.NQ, lists.NKV, lists.q_block, lists.kv_block, str(torch.device(device))) + tuple(extra_key)
+    hit = _visited_counts.get(key)
+    if hit is not None and all(r() is t for r, t in zip(hit[0], dmask.keep)):
+        return hit[1]
+    out = torch.empty((lists.B * lists.H,), dtype=torch.int64, device=device)
+    nat.check(nat.lib().bma_block_lists_visited(C.byref(lists), out.data_ptr(), torch.cuda.current_stream(device).cuda_stream),
+              "bma_block_lists_visited")
+    counts = out.cpu().numpy().copy()          # synchronises once per distinct mask
+    if len(_visited_counts) > 256:
+        _visited_counts.clear()
+    _visited_counts[key] = (tuple(weakref.ref(t) for t in dmask.keep), counts)
+    return counts

@@ -15,6 +15,7 @@ counterpart there.
 from __future__ import annotations
 
 import ctypes as C
+from datetime import timedelta
 from typing import Callable, List, Optional, Tuple
 
 import torch
@@ -159,9 +160,48 @@ def _pair_is_empty(terms: _masks.MaskTerms, q0: int, qn: int, k0: int, kn: int) 
     return False
 
 
+class RingTransferError(RuntimeError):
+    """A ring step could not complete: a neighbour holds a chunk of another shape, or a transfer did not finish
+    within the deadline (a rank that died, left, or never entered the call)."""
+
+
+def _wait_all(reqs, timeout_s: Optional[float], what: str) -> None:
+    """Waits for point-to-point requests, turning a time-out or a transport error into RingTransferError.  The
+    deadline is enforced on the host by backends whose wait blocks the host (gloo; NCCL with blocking wait);
+    otherwise the process group's own timeout ends a transfer whose peer is gone."""
+    for r in reqs:
+        try:
+            if timeout_s is None:
+                r.wait()
+            else:
+                r.wait(timedelta(seconds=timeout_s))
+        except Exception as e:   # gloo raises RuntimeError, NCCL DistBackendError
+            raise RingTransferError(f"{what}: transfer did not complete ({type(e).__name__}: {e})") from e
+
+
+def _check_neighbours(K: torch.Tensor, rank: int, world: int, group, timeout_s: Optional[float]) -> None:
+    """Exchanges the chunk geometry with both ring neighbours before any K/V moves: every rank must hold chunks of the
+    same shape and dtype (a receive buffer of the wrong size would corrupt or stall the ring).  Costs one tiny
+    message each way and a host synchronisation per call."""
+    import torch.distributed as dist
+    if world == 1:
+        return
+    mine = tuple(int(x) for x in K.shape) + (K.element_size(),)
+    send = torch.tensor(mine, dtype=torch.int64, device=K.device)
+    recv = torch.empty_like(send)
+    dst, src = (rank + 1) % world, (rank - 1) % world
+    reqs = dist.batch_isend_irecv([dist.P2POp(dist.isend, send, dst, group), dist.P2POp(dist.irecv, recv, src, group)])
+    _wait_all(reqs, timeout_s, f"rank {rank}: geometry exchange with ranks {src} / {dst}")
+    theirs = tuple(int(x) for x in recv.cpu())
+    if theirs != mine:
+        raise RingTransferError(f"rank {rank}: rank {src} holds K/V chunks of shape {theirs[:-1]} ({theirs[-1]} bytes per "
+                                f"element), this rank {mine[:-1]} ({mine[-1]}): every rank must hold an equal share")
+
+
 def ring_attention_forward(Q, K, V, *, rank: int, world: int, is_causal: bool = False,
                            terms: Optional[_masks.MaskTerms] = None, group=None,
-                           attend: Callable = cuda_attend, merge: Callable = cuda_merge, layout=None):
+                           attend: Callable = cuda_attend, merge: Callable = cuda_merge, layout=None,
+                           timeout_s: Optional[float] = None, validate: bool = True):
     """Forward attention over a sequence split across ``world`` ranks.
 
     Q ``[B, n, Hq, d]`` and K, V ``[B, n, Hkv, d]`` are this rank's tokens (equal sizes on every
@@ -171,12 +211,18 @@ def ring_attention_forward(Q, K, V, *, rank: int, world: int, is_causal: bool = 
     computes, so the transfer runs under the kernels; received data always lands in this device's
     own memory before a kernel reads it.  Within a step every (local query range, visiting key
     range) pair is one attention call with the global offsets in the mask description; pairs the
-    interval terms rule out entirely are skipped."""
+    interval terms rule out entirely are skipped.
+
+    Failure handling: with ``validate`` the ranks first compare chunk shapes with their neighbours; every wait takes
+    ``timeout_s`` (None = the process group's own timeout).  Either check raises ``RingTransferError`` instead of
+    hanging or reading a half-filled buffer."""
     import torch.distributed as dist
     terms = terms or _masks.MaskTerms(causal=is_causal)
     layout = layout or contiguous_layout(Q.shape[1])
     q_segs = _segments(layout, rank, world)
     k_cur, v_cur = K.contiguous(), V.contiguous()
+    if validate:
+        _check_neighbours(k_cur, rank, world, group, timeout_s)
     parts = [None] * len(q_segs)          # (O, lse) per local query range
     for s, owner in enumerate(ring_schedule(rank, world)):
         reqs = []
@@ -192,8 +238,7 @@ def ring_attention_forward(Q, K, V, *, rank: int, world: int, is_causal: bool = 
                     continue
                 O_s, lse_s = attend(Q[:, ql:ql + qn], k_cur[:, kl:kl + kn], v_cur[:, kl:kl + kn], _step_terms(terms, qg, kg))
                 parts[i] = (O_s, lse_s) if parts[i] is None else merge(parts[i][0], parts[i][1], O_s, lse_s)
-        for r in reqs:
-            r.wait()
+        _wait_all(reqs, timeout_s, f"rank {rank}: K/V rotation, ring step {s}")
         if s + 1 < world:
             k_cur, v_cur = k_nxt, v_nxt
     for i, (ql, qg, qn) in enumerate(q_segs):
@@ -221,7 +266,8 @@ def cuda_backward(Q, K, V, O, lse, dO, terms: _masks.MaskTerms):
 
 def ring_attention_backward(Q, K, V, O, lse, dO, *, rank: int, world: int, is_causal: bool = False,
                             terms: Optional[_masks.MaskTerms] = None, group=None,
-                            backward: Callable = cuda_backward, exchange: Optional[Callable] = None, layout=None):
+                            backward: Callable = cuda_backward, exchange: Optional[Callable] = None, layout=None,
+                            timeout_s: Optional[float] = None):
     """dQ, dK, dV for a sequence split across ``world`` ranks (the counterpart of
     ``ring_attention_forward`` with the same ``layout``; ``O`` / ``lse`` are its results for the
     local queries).
@@ -272,8 +318,7 @@ def ring_attention_backward(Q, K, V, O, lse, dO, *, rank: int, world: int, is_ca
                 dv_acc[:, ks] += dv_s
         # the accumulators move on after every step, the last hop returns them to the tokens' owner
         (dk_acc, dv_acc), acc_reqs = start([dk_acc, dv_acc])
-        for r in kv_reqs + acc_reqs:
-            r.wait()
+        _wait_all(kv_reqs + acc_reqs, timeout_s, f"rank {rank}: K/V and dK/dV rotation, backward ring step {s}")
         if kv_next is not None:
             k_cur, v_cur = kv_next
     return dq_acc.to(Q.dtype), dk_acc.to(K.dtype), dv_acc.to(V.dtype)

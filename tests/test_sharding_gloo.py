@@ -137,3 +137,49 @@ def test_two_ranks_gloo():
     results = mgr.dict()
     mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
     assert dict(results) == {0: (True, True, True), 1: (True, True, True)}
+
+
+# ---- failure detection on the host (CPU ranks, nothing faults): a neighbour with a chunk of the wrong size, and a
+# ---- neighbour that never enters the call.  Either way the ring must raise RingTransferError within its deadline.
+
+def _failing_worker(rank, world, port, results, scenario):
+    from datetime import timedelta
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=20))
+    rng = np.random.default_rng(rank)
+    B, Hq, Hkv, d = 1, 2, 2, 8
+    n = 32 if not (scenario == "wrong_size" and rank == 1) else 24      # rank 1 holds a shorter chunk
+    Q, K, V = (torch.from_numpy(rng.standard_normal((B, n, h, d))) for h in (Hq, Hkv, Hkv))
+    t0 = time.monotonic()
+    outcome = "completed"
+    if scenario == "absent_peer" and rank == 1:
+        time.sleep(6.0)                                                  # never posts its send
+        outcome = "absent"
+    else:
+        try:
+            S.ring_attention_forward(Q, K, V, rank=rank, world=world, terms=M.MaskTerms(causal=True), attend=_oracle_attend,
+                                     merge=_oracle_merge, timeout_s=3.0)
+        except S.RingTransferError as e:
+            outcome = "RingTransferError: " + str(e)[:60]
+    results[rank] = (outcome, time.monotonic() - t0)
+    os._exit(0)      # a transfer may still be pending: leave without the collective teardown
+
+
+@pytest.mark.parametrize("scenario", ["wrong_size", "absent_peer"])
+def test_ring_reports_a_failed_neighbour(scenario):
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mgr = mp.Manager()
+    results = mgr.dict()
+    ctx = mp.spawn(_failing_worker, args=(world, port, results, scenario), nprocs=world, join=False)
+    for p in ctx.processes:
+        p.join(60)
+        assert not p.is_alive(), "a rank hung instead of reporting the failure"
+    res = dict(results)
+    assert res[0][0].startswith("RingTransferError") and res[0][1] < 15.0, res
+    if scenario == "wrong_size":
+        assert res[1][0].startswith("RingTransferError") and "shape" in res[0][0] + res[1][0], res

@@ -54,9 +54,15 @@ def _segments(B, L, seed):
     return seg
 
 
-def test_static_scratch_matches_workspace_variant_twice():
+def _devices():
+    # the array's device address is looked up once per device: cover a second GPU where the box has one
+    return [0, 1] if torch.cuda.device_count() >= 2 else [0]
+
+
+@pytest.mark.parametrize("index", _devices())
+def test_static_scratch_matches_workspace_variant_twice(index):
     lib = nat.lib()
-    dev = torch.device("cuda", 0)
+    dev = torch.device("cuda", index)
     torch.cuda.set_device(dev)
     stream = torch.cuda.current_stream(dev).cuda_stream
     assert lib.bma_mask_compile_static_limit() == 4 << 20
@@ -74,6 +80,19 @@ def test_static_scratch_matches_workspace_variant_twice():
         torch.cuda.synchronize(dev)
         for f in FIELDS:
             assert torch.equal(got[f], want[f]), f
+        # what the entry point exists for: a further call (the device address is known by now) allocates nothing --
+        # neither through the caching allocator nor behind its back (free device memory as the driver reports it)
+        free_before, _ = torch.cuda.mem_get_info(dev)
+        stats_before = torch.cuda.memory_stats(dev)
+        nat.check(lib.bma_mask_compile_static(C.byref(dmask.spec), B, H, C.byref(lists), stream), "bma_mask_compile_static")
+        torch.cuda.synchronize(dev)
+        stats_after = torch.cuda.memory_stats(dev)
+        for k in ("allocation.all.allocated", "segment.all.allocated", "num_alloc_retries"):
+            assert stats_after.get(k, 0) == stats_before.get(k, 0), k
+        assert torch.cuda.mem_get_info(dev)[0] >= free_before - (1 << 20)     # a cudaMalloc would take at least 2 MiB
+        for f in FIELDS:
+            assert torch.equal(got[f], want[f]), f
+    torch.cuda.set_device(0)
 
 
 def test_static_scratch_rejects_oversized_masks():
