@@ -473,10 +473,46 @@ def ring_entry(w, rank, world, local_rank, dev, dist, steps, warmup, ring="zigza
         O, lse = S.ring_attention_forward(Q, K, V, rank=rank, world=world, terms=terms, layout=layout)
         return S.ring_attention_backward(Q, K, V, O, lse, dO, rank=rank, world=world, terms=terms, layout=layout)
 
+    # The same ring with one half switched off, to show how much of the transfer hides under the kernels: the kernels
+    # alone (the exchange hands back local buffers of the right shape) and the transfers alone (the kernels are stubs).
+    local = lambda tensors, dst, src: [torch.empty_like(t) for t in tensors]
+
+    def compute_only():
+        O, lse = S.ring_attention_forward(Q, K, V, rank=rank, world=world, terms=terms, layout=layout, exchange=local)
+        return S.ring_attention_backward(Q, K, V, O, lse, dO, rank=rank, world=world, terms=terms, layout=layout, exchange=local)
+
+    stub_o = torch.zeros((B, n // (2 if ring == "zigzag" else 1), H, d), dtype=torch.float32, device=dev)
+    stub_lse = torch.zeros((B, H, stub_o.shape[1]), dtype=torch.float32, device=dev)
+    stub_g = [torch.zeros((B, stub_o.shape[1], H, d), dtype=dt, device=dev) for _ in range(3)]
+
+    def transfer_only():
+        O, lse = S.ring_attention_forward(Q, K, V, rank=rank, world=world, terms=terms, layout=layout,
+                                          attend=lambda q, k, v, t: (stub_o, stub_lse), merge=lambda o, l, o2, l2: (o, l))
+        O = torch.zeros((B, n, H, d), dtype=torch.float32, device=dev) if O.shape[1] != n else O
+        lse = torch.zeros((B, H, n), dtype=torch.float32, device=dev) if lse.shape[2] != n else lse
+        return S.ring_attention_backward(Q, K, V, O, lse, dO, rank=rank, world=world, terms=terms, layout=layout,
+                                         backward=lambda q, k, v, o, l, g, t: stub_g)
+
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize(dev)
+
+    def timed(fn, reps):
+        fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / reps
+        if dist is not None:
+            tt = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt[0])
+        return ms
 
     nblk = L // 128
     blocks = B * H * nblk * (nblk + 1) // 2                      # non-empty 128x128 blocks of the whole causal sequence
@@ -504,6 +540,7 @@ def ring_entry(w, rank, world, local_rank, dev, dist, steps, warmup, ring="zigza
         ms_step = float(t[0])
     sustained, burst, hbm, peak_kind = peaks()
     tf = step_flops / (ms_step * 1e-3) / 1e12
+    compute_ms, transfer_ms = timed(compute_only, 2), (timed(transfer_only, 2) if world > 1 else 0.0)
     del Q, K, V, dO
     torch.cuda.empty_cache()
     return {
@@ -518,6 +555,9 @@ def ring_entry(w, rank, world, local_rank, dev, dist, steps, warmup, ring="zigza
                      "peak": sustained, "unit": "TFLOP/s per GPU", "frac": tf / world / sustained, "traffic": None,
                      "peak_kind": f"{peak_kind} sustained dense bf16"},
         "per_gpu": tf / world, "frac_of_burst_per_gpu": tf / world / burst,
+        # max over ranks each: the whole step, its kernels without any transfer, its transfers without any kernel
+        "overlap": {"step_ms": ms_step, "compute_only_ms": compute_ms, "transfer_only_ms": transfer_ms,
+                    "transfer_hidden_ms": max(0.0, compute_ms + transfer_ms - ms_step)},
         "clocks": clocks, "gpu_launches": int(launches)}
 
 
@@ -761,7 +801,7 @@ def main():
             extra["c5_head_shards"] = c5_head_shards(rank, world, dev, dist)
             if WORKLOADS["c5"]["L"] % (2 * world * 128) == 0:
                 r = ring_entry(WORKLOADS["c5"], rank, world, local_rank, dev, dist, steps=3, warmup=2, ring="zigzag", sample_clocks=False)
-                extra["ring_c5"] = {k: r[k] for k in ("value", "ms_per_step", "steps", "warmup", "scaling", "per_gpu", "frac_of_burst_per_gpu", "gpu_launches")}
+                extra["ring_c5"] = {k: r[k] for k in ("value", "ms_per_step", "steps", "warmup", "scaling", "per_gpu", "frac_of_burst_per_gpu", "overlap", "gpu_launches")}
                 extra["ring_c5"]["parallelism"] = r["config"]["parallelism"]
                 extra["ring_c5"]["workload"] = r["config"]["workload"]
 

@@ -275,6 +275,9 @@ int bma_block_lists_visited(const bma_block_lists* lists, int64_t* visited, bma_
  * rounding of dS either way.  The workspace must be 256-byte aligned. */
 size_t bma_attn_bwd_scratch_bytes(const bma_attn_args* args, const bma_block_lists* lists,
                                   const int64_t* visited_host);
+/* The smallest workspace that still takes the hand-over path: the tables plus the largest unit. */
+size_t bma_attn_bwd_scratch_min_bytes(const bma_attn_args* args, const bma_block_lists* lists,
+                                      const int64_t* visited_host);
 
 /* Backward: dQ, dK, dV from (Q, K, V, O, dO, lse, delta).  Replaces
  * _masked_attention_via_map_bwd, jaxmodules/attention.py:266-342.  `lists` must carry the

@@ -103,6 +103,7 @@ SIGNATURES = {
     "bma_attn_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
     "bma_block_lists_visited": (C.c_int, [C.POINTER(BlockLists), C.c_void_p, C.c_void_p]),
     "bma_attn_bwd_scratch_bytes": (C.c_size_t, [C.POINTER(AttnArgs), C.POINTER(BlockLists), C.c_void_p]),
+    "bma_attn_bwd_scratch_min_bytes": (C.c_size_t, [C.POINTER(AttnArgs), C.POINTER(BlockLists), C.c_void_p]),
     "bma_attn_bwd": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(MaskSpec), C.POINTER(BlockLists), C.c_void_p, C.c_size_t,
                                C.c_void_p, C.c_void_p, C.c_void_p]),
     "bma_debug_expire_wait": (C.c_int, [C.c_uint64, C.c_int32, C.c_void_p]),

@@ -258,13 +258,15 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
             visited = (C.c_int64 * len(counts))(*[int(c) for c in counts])
             scratch = lib.bma_attn_bwd_scratch_bytes(C.byref(a), C.byref(lists), visited)
         given = min(scratch, _scratch_limit, int(scratch * _scratch_fraction) if _scratch_fraction < 1.0 else scratch)
+        if 0 < given < scratch and given < lib.bma_attn_bwd_scratch_min_bytes(C.byref(a), C.byref(lists), visited):
+            given = 0          # not even the largest (batch, kv head) unit fits: the dQ kernel recomputes, no buffer is needed
         if given > 0:
             ws, ws_bytes = _backward_scratch(dev, max(given, ws_bytes)), max(given, ws_bytes)
         else:
             ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=dev)
         last_backward_info.update(scratch_bytes=int(scratch), workspace_bytes=int(ws_bytes), whole=bool(scratch and given >= scratch))
         mid = None
-        if _profile_sink is not None and be == nat.BMA_BACKEND_TCGEN05 and (scratch == 0 or given >= scratch):
+        if _profile_sink is not None and be == nat.BMA_BACKEND_TCGEN05 and (given == 0 or given >= scratch):
             # the library records this event between its dK/dV pass and its dQ pass (only when it runs as one range)
             mid = torch.cuda.Event(enable_timing=True)
             mid.record(torch.cuda.current_stream(dev))

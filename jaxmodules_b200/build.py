@@ -70,7 +70,26 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    _build_jax_adapter(force)
     return LIB
+
+
+def _build_jax_adapter(force: bool) -> None:
+    """libbma_jax.so (the XLA-FFI handlers of csrc/bma_jax.cc) -- only where jax ships its FFI headers; skipped,
+    silently, everywhere else (the torch/ctypes binding needs none of it)."""
+    try:
+        import jax
+        inc = jax.ffi.include_dir()
+    except Exception:
+        return
+    out, src = PKG / "libbma_jax.so", CSRC / "bma_jax.cc"
+    if not force and not _stale(out, [src, LIB]):
+        return
+    cmd = [_nvcc(), "-shared", "-std=c++17", "-Xcompiler", "-fPIC", "-I", inc, str(src), "-o", str(out),
+           "-L", str(PKG), "-lbma", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN", "-lcudart"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"building the jax adapter failed:\n{r.stdout}\n{r.stderr}")
 
 
 if __name__ == "__main__":

@@ -592,6 +592,9 @@ bool sm100_bwd_supported(const bma_attn_args& a) { return sm100_supported(a) && 
 
 size_t sm100_bwd_workspace_bytes(const bma_attn_args&) { return 0; }
 
+// tables + the largest (batch, kv head) unit: the smallest workspace that still takes the hand-over path
+size_t sm100_bwd_scratch_min_bytes(const bma_attn_args& a, const bma_block_lists& lists, const int64_t* visited_host);
+
 template <typename P>
 static int launch_dkdv(const bma_attn_args& a, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
                        const CUtensorMap& mdk, const CUtensorMap& mdv, P& p, int b0, int nb, int hk0, int nhk, cudaStream_t st) {
@@ -629,6 +632,14 @@ size_t sm100_bwd_scratch_bytes(const bma_attn_args& a, const bma_block_lists& li
   for (int b = 0; b < a.B; ++b)
     for (int hk = 0; hk < a.Hkv; ++hk) blocks += unit_blocks(a, lists, visited_host, b, hk);
   return slot_tables_layout(a, lists, nullptr).bytes + (size_t)blocks * kDsBytes;
+}
+
+size_t sm100_bwd_scratch_min_bytes(const bma_attn_args& a, const bma_block_lists& lists, const int64_t* visited_host) {
+  if (lists.NKV > 1024 || lists.NQ <= 0 || lists.B <= 0 || lists.H <= 0) return 0;
+  int64_t largest = 0;
+  for (int b = 0; b < a.B; ++b)
+    for (int hk = 0; hk < a.Hkv; ++hk) largest = std::max(largest, unit_blocks(a, lists, visited_host, b, hk));
+  return slot_tables_layout(a, lists, nullptr).bytes + (size_t)std::max<int64_t>(largest, 1) * kDsBytes;
 }
 
 int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block_lists& lists, void* ws, size_t ws_bytes,

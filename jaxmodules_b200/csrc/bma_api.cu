@@ -382,6 +382,11 @@ size_t bma_attn_bwd_scratch_bytes(const bma_attn_args* args, const bma_block_lis
   return pick_backend_bwd(args) == BMA_BACKEND_TCGEN05 ? sm100_bwd_scratch_bytes(*args, *lists, visited_host) : 0;
 }
 
+size_t bma_attn_bwd_scratch_min_bytes(const bma_attn_args* args, const bma_block_lists* lists, const int64_t* visited_host) {
+  if (validate_common(args) != BMA_OK || !lists) return 0;
+  return pick_backend_bwd(args) == BMA_BACKEND_TCGEN05 ? sm100_bwd_scratch_min_bytes(*args, *lists, visited_host) : 0;
+}
+
 int bma_block_lists_visited(const bma_block_lists* lists, int64_t* visited, bma_stream_t stream) {
   BMA_REQUIRE(lists && visited, BMA_ERR_ARG);
   BMA_REQUIRE(lists->B > 0 && lists->H > 0 && lists->NQ > 0 && lists->kv_num && lists->full_kv_num, BMA_ERR_ARG);

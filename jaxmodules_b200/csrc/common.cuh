@@ -175,6 +175,7 @@ int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
               size_t ws_bytes, const int64_t* visited_host, cudaEvent_t mark, cudaStream_t st);
 size_t sm100_bwd_workspace_bytes(const bma_attn_args& a);
 size_t sm100_bwd_scratch_bytes(const bma_attn_args& a, const bma_block_lists& lists, const int64_t* visited_host);
+size_t sm100_bwd_scratch_min_bytes(const bma_attn_args& a, const bma_block_lists& lists, const int64_t* visited_host);
 bool sm100_supported(const bma_attn_args& a);
 bool sm100_bwd_supported(const bma_attn_args& a);
 

@@ -201,7 +201,7 @@ def _check_neighbours(K: torch.Tensor, rank: int, world: int, group, timeout_s: 
 def ring_attention_forward(Q, K, V, *, rank: int, world: int, is_causal: bool = False,
                            terms: Optional[_masks.MaskTerms] = None, group=None,
                            attend: Callable = cuda_attend, merge: Callable = cuda_merge, layout=None,
-                           timeout_s: Optional[float] = None, validate: bool = True):
+                           timeout_s: Optional[float] = None, validate: bool = True, exchange: Optional[Callable] = None):
     """Forward attention over a sequence split across ``world`` ranks.
 
     Q ``[B, n, Hq, d]`` and K, V ``[B, n, Hkv, d]`` are this rank's tokens (equal sizes on every
@@ -215,23 +215,27 @@ def ring_attention_forward(Q, K, V, *, rank: int, world: int, is_causal: bool = 
 
     Failure handling: with ``validate`` the ranks first compare chunk shapes with their neighbours; every wait takes
     ``timeout_s`` (None = the process group's own timeout).  Either check raises ``RingTransferError`` instead of
-    hanging or reading a half-filled buffer."""
+    hanging or reading a half-filled buffer.  ``exchange(tensors, dst, src)`` replaces the point-to-point transfer
+    and returns the received tensors (measurements of the compute alone pass a stub)."""
     import torch.distributed as dist
     terms = terms or _masks.MaskTerms(causal=is_causal)
     layout = layout or contiguous_layout(Q.shape[1])
     q_segs = _segments(layout, rank, world)
     k_cur, v_cur = K.contiguous(), V.contiguous()
-    if validate:
+    if validate and exchange is None:
         _check_neighbours(k_cur, rank, world, group, timeout_s)
     parts = [None] * len(q_segs)          # (O, lse) per local query range
     for s, owner in enumerate(ring_schedule(rank, world)):
         reqs = []
         if s + 1 < world:
-            k_nxt, v_nxt = torch.empty_like(k_cur), torch.empty_like(v_cur)
             dst, src = (rank + 1) % world, (rank - 1) % world
-            ops = [dist.P2POp(dist.isend, k_cur, dst, group), dist.P2POp(dist.isend, v_cur, dst, group),
-                   dist.P2POp(dist.irecv, k_nxt, src, group), dist.P2POp(dist.irecv, v_nxt, src, group)]
-            reqs = dist.batch_isend_irecv(ops)
+            if exchange is not None:
+                k_nxt, v_nxt = exchange([k_cur, v_cur], dst, src)
+            else:
+                k_nxt, v_nxt = torch.empty_like(k_cur), torch.empty_like(v_cur)
+                ops = [dist.P2POp(dist.isend, k_cur, dst, group), dist.P2POp(dist.isend, v_cur, dst, group),
+                       dist.P2POp(dist.irecv, k_nxt, src, group), dist.P2POp(dist.irecv, v_nxt, src, group)]
+                reqs = dist.batch_isend_irecv(ops)
         for i, (ql, qg, qn) in enumerate(q_segs):
             for kl, kg, kn in _segments(layout, owner, world):
                 if _pair_is_empty(terms, qg, qn, kg, kn):

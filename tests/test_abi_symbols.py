@@ -61,3 +61,17 @@ def test_argument_validation_without_a_device():
     assert lib.bma_attn_plan(C.byref(a), None, None, None) == nat.BMA_ERR_UNSUPPORTED  # head dim
     assert lib.bma_mask_compile(None, 1, 1, None, None, 0, None) == nat.BMA_ERR_ARG
     assert lib.bma_mask_compile_workspace_bytes(None, 1, 1, 1, 1) == 0
+
+
+def test_jax_adapter_is_guarded():
+    """The jax.ffi adapter is source only where jax is absent: importing it must fail with ImportError (not half-load),
+    the package itself must import without it, and the build must skip it silently."""
+    import importlib.util
+    import jaxmodules_b200  # noqa: F401
+    from jaxmodules_b200 import build
+    assert (build.CSRC / "bma_jax.cc").exists()
+    if importlib.util.find_spec("jax") is None:
+        with pytest.raises(ImportError):
+            importlib.import_module("jaxmodules_b200.jax_binding")
+        build._build_jax_adapter(force=False)          # no jax: returns without building anything
+        assert not (build.PKG / "libbma_jax.so").exists()
