@@ -104,7 +104,9 @@ __device__ __forceinline__ void setmaxnreg_inc_208() { asm volatile("setmaxnreg.
 __device__ __forceinline__ void setmaxnreg_dec_80() { asm volatile("setmaxnreg.dec.sync.aligned.u32 80;"); }
 
 // Allowed query interval [jlo, jhi] (tile-local columns, inclusive) of key row k for masks made of
-// interval terms (the block window is constant over the q tile; the host checks that).
+// interval terms.  The block window of query block i starts at s(i) = clamp(i - left, 0, nblk - total): both ends are
+// non-decreasing in i, so the query blocks whose window contains the key form one range, whatever the window's
+// block size is relative to the tile.
 __device__ __forceinline__ void col_interval(const MaskView& m, int k, int q0, int& jlo, int& jhi) {
   jlo = 0;
   jhi = min(BT, m.q_valid - q0) - 1;
@@ -117,9 +119,12 @@ __device__ __forceinline__ void col_interval(const MaskView& m, int k, int q0, i
     jhi = min(jhi, gk + m.band_left - base);
   }
   if (m.flags & BMA_MASK_BLOCK_WINDOW) {
-    int wlo, whi;
-    block_window_range(m, base, wlo, whi);
-    if (gk < wlo || gk >= whi) { jlo = 1; jhi = 0; }
+    const int wb = m.win_block, total = m.win_left + m.win_right, last_start = m.win_nblk - total;
+    const int kb = gk / wb;            // key block of this key
+    const int t = kb - total + 1;      // the window reaches the key iff s(i) >= t ...
+    if (t > last_start) { jlo = 1; jhi = 0; return; }
+    if (t > 0) jlo = max(jlo, (t + m.win_left) * wb - base);
+    if (kb < last_start) jhi = min(jhi, (kb + m.win_left + 1) * wb - 1 - base);   // ... and s(i) <= kb
   }
 }
 
@@ -647,9 +652,7 @@ int sm100_bwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   BMA_REQUIRE(lists.q_block == BT && lists.kv_block == BT && lists.q_num, BMA_ERR_ARG);
   BMA_REQUIRE(a.d_o.dtype == BMA_DTYPE_BF16, BMA_ERR_UNSUPPORTED);  // bma_attn_bwd_preprocess provides the bf16 copy
   BMA_REQUIRE(aligned16(a.d_o) && aligned16(a.dq) && aligned16(a.dk) && aligned16(a.dv), BMA_ERR_UNSUPPORTED);
-  // the per-row form of the block window needs the window to be constant over a 128-query tile
-  int interval = 1;
-  if ((spec.flags & BMA_MASK_BLOCK_WINDOW) && !(spec.win_block % BT == 0 && spec.q_offset % BT == 0)) interval = 0;
+  const int interval = 1;   // every structured term has a closed per-key query interval (col_interval)
 
   CUtensorMap mq, mk, mv, mdo;
   int rc;

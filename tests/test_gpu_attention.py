@@ -181,6 +181,9 @@ BF16_CASES = {
                               kw=lambda L: dict(mask_fn=M.document_mask(document_segments(2, L, 64, 700, 4), causal=True), block_size=128)),
     "ragged_gqa": dict(B=1, L=300, H=4, d=128, scale=1.0, kw=lambda L: dict(is_causal=True, block_size=64), Hkv=2, N=200),
     "d64": dict(B=1, L=512, H=2, d=64, scale=1.0, kw=lambda L: dict(is_causal=True, block_size=128)),
+    # block windows whose block size is not the kernels' tile (several window blocks per 128-query tile), clamped at both ends
+    "window_block32": dict(B=1, L=1024, H=2, d=128, scale=1.0, kw=lambda L: dict(block_size=32, window_size=(100, 40))),
+    "window_block48_causal": dict(B=1, L=960, H=2, d=128, scale=1.0, kw=lambda L: dict(is_causal=True, block_size=48, window_size=(200, 0))),
     "d64_gqa_sliding_ragged": dict(B=2, L=700, H=4, d=64, scale=1.0, Hkv=2, N=333,
                                    kw=lambda L: dict(mask_fn=M.sliding_window_mask(150, 20), block_size=64)),
     "d64_documents": dict(B=2, L=1024, H=2, d=64, scale=1.0,
