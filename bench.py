@@ -75,6 +75,45 @@ def ncu_traffic(workload):
     return {k: v * entry["scale"] for k, v in base.items()}
 
 
+class numa_local:
+    """Runs the enclosed host allocations on CPUs of the NUMA node the GPU hangs off (sysfs: the PCI device's
+    numa_node and that node's cpulist), so that pinned buffers are first touched — and therefore placed — next to the
+    GPU's PCIe root complex instead of wherever the launcher happened to run.  Does nothing when the node cannot be
+    found or the affinity cannot be set.  ``info`` records what was done, for the bench line."""
+
+    def __init__(self, device_index):
+        self.index, self.saved, self.info = device_index, None, {"numa_node": None}
+
+    def __enter__(self):
+        try:
+            pr = torch.cuda.get_device_properties(self.index)
+            bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+            node = int(Path(f"/sys/bus/pci/devices/{bdf.lower()}/numa_node").read_text())
+            if node < 0:
+                return self
+            cpus = set()
+            for part in Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+            allowed = os.sched_getaffinity(0)
+            target = cpus & allowed
+            if target:
+                self.saved = allowed
+                os.sched_setaffinity(0, target)
+                self.info = {"numa_node": node, "cpus_used": len(target)}
+        except Exception as e:           # containers often hide sysfs or forbid the call: measure as is
+            self.info = {"numa_node": None, "why": type(e).__name__}
+        return self
+
+    def __exit__(self, *exc):
+        if self.saved is not None:
+            try:
+                os.sched_setaffinity(0, self.saved)
+            except Exception:
+                pass
+        return False
+
+
 def synth(shape, seed, dtype, scale=1.0, device="cpu", pin=False):
     """Seeded N(0,1) tensors: numpy PCG64(seed) -> float32 -> dtype (the configs' definition)."""
     x = np.random.Generator(np.random.PCG64(seed)).standard_normal(shape, dtype=np.float32)
@@ -624,8 +663,10 @@ def main():
     # every rank owns its own batch (seeds offset by rank): batch x head shards, no collective
     flex = args.api == "flex"
     shape = (B, H, L, d) if flex else (B, L, H, d)
-    hQ, hK, hV = (synth(shape, 10 * rank + s, dt, scale, pin=True) for s in (0, 1, 2))
-    hdO = synth(shape, 10 * rank + 3, torch.float32, pin=True)
+    numa = numa_local(local_rank)
+    with numa:          # pinned host buffers next to this GPU's PCIe root (matters once eight ranks share the host)
+        hQ, hK, hV = (synth(shape, 10 * rank + s, dt, scale, pin=True) for s in (0, 1, 2))
+        hdO = synth(shape, 10 * rank + 3, torch.float32, pin=True)
     Q, K, V = (x.to(dev).requires_grad_(True) for x in (hQ, hK, hV))
     dO = hdO.to(dev)
     kw = mask_kwargs(w, M)
@@ -701,8 +742,9 @@ def main():
         # out inside the timed region; the two copy directions and the kernels merely overlap.
         main = torch.cuda.current_stream(dev)
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-        host_out = [[torch.empty(shape, dtype=torch.float32).pin_memory()] +
-                    [torch.empty(shape, dtype=dt).pin_memory() for _ in range(3)] for _ in range(2)]
+        with numa:
+            host_out = [[torch.empty(shape, dtype=torch.float32).pin_memory()] +
+                        [torch.empty(shape, dtype=dt).pin_memory() for _ in range(3)] for _ in range(2)]
         outs = host_out[0]
         dev_in = [None, None]
         in_ready = [torch.cuda.Event(), torch.cuda.Event()]       # Q, K, V of the slot have arrived
@@ -860,7 +902,8 @@ def main():
             line["e2e"] = {"value": total_flops / (e2e[0] * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e[0],
                            "h2d_bytes_per_step": e2e[1], "d2h_bytes_per_step": e2e[2],
                            # the same copies on the same streams with no kernel in between: the box's own ceiling
-                           "copy_only_ms_per_step": e2e[3], "copy_only_GBps_each_way": e2e[1] / (e2e[3] * 1e-3) / 1e9}
+                           "copy_only_ms_per_step": e2e[3], "copy_only_GBps_each_way": e2e[1] / (e2e[3] * 1e-3) / 1e9,
+                           "pinned_host_buffers": numa.info}
         if extra:
             line["extra"] = extra
         if world == 1 and not args.no_cpu_baseline:
