@@ -33,8 +33,18 @@
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
+// Element-wise math of the dK/dV kernel:
+//   0: scalar arithmetic, every exponential on the MUFU pipe
+//   1: the packed two-wide FP32 instructions of sm_100 (fma / add / mul .f32x2) for the scale-and-shift and for
+//      dS = P * (dP - delta); every exponential on the MUFU pipe
+//   2: as 1, and a quarter of the exponentials as a packed polynomial on the FMA pipe
+// Measured on config 2 / the L=8192 shape (same box): 0: 2.127 / 4.238 ms, 1: 2.233 / 4.366 ms, 2: 2.216 / 4.216 ms -- the
+// kernel is bound by shared-memory operand traffic (2 560 cycles per tile at 128 B/clk), not by instruction issue, so 0.
+#ifndef BMA_DKDV_MATH
+#define BMA_DKDV_MATH 0
+#endif
 #ifndef BMA_DKDV_POLY
-#define BMA_DKDV_POLY 0  // measured: 3.87 ms against 3.78 ms for the whole backward on the config-2 shape, so off
+#define BMA_DKDV_POLY 0  // scalar polynomial (BMA_DKDV_MATH 0 only); measured 3.87 ms against 3.78 ms for the whole backward, so off
 #endif
 
 namespace bma {
@@ -333,8 +343,13 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const int64_t off = ((int64_t)b * a.Hq + h) * a.N + q;
           const float lv = q < a.N ? __ldg(a.lse + off) : -INFINITY;
           // +inf for rows that attend nothing or lie outside: their probabilities become exactly 0
+#if BMA_DKDV_MATH == 0
           sm.lse2[st][idx] = (lv == -INFINITY) ? INFINITY : lv * kLog2e;
           sm.delta[st][idx] = q < a.N ? __ldg(a.delta + off) : 0.f;
+#else     // the packed forms add: -lse2 (and -inf for a dead row) and -delta are what is staged
+          sm.lse2[st][idx] = (lv == -INFINITY) ? -INFINITY : -lv * kLog2e;
+          sm.delta[st][idx] = q < a.N ? -__ldg(a.delta + off) : 0.f;
+#endif
         }
         mbar_arrive(&sm.bar[BAR_STAT0 + st]);
       }
@@ -418,6 +433,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_before();
       mbar_arrive(&sm.bar[BAR_LS]);
       if (!mbar_wait(&sm.bar[BAR_STAT0 + st], (n >> 1) & 1)) return false;
+#if BMA_DKDV_MATH == 0
 #pragma unroll
       for (int j4 = 0; j4 < 8; ++j4) {
         const float4 la = *reinterpret_cast<const float4*>(&sm.lse2[st][(half * 2) * 32 + j4 * 4]);
@@ -440,6 +456,34 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #endif
         }
       }
+#else
+      {
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+#pragma unroll
+        for (int j4 = 0; j4 < 8; ++j4) {
+          float4 la = *reinterpret_cast<const float4*>(&sm.lse2[st][(half * 2) * 32 + j4 * 4]);        // -lse2
+          float4 lb = *reinterpret_cast<const float4*>(&sm.lse2[st][(half * 2 + 1) * 32 + j4 * 4]);
+          if constexpr (KB) {  // key bias of this thread's key row: the same shift for every query column
+            la.x += kbk; la.y += kbk; la.z += kbk; la.w += kbk;
+            lb.x += kbk; lb.y += kbk; lb.z += kbk; lb.w += kbk;
+          }
+          const int j = j4 * 4;
+          const float2 xa0 = __ffma2_rn(make_float2(__uint_as_float(s0[j]), __uint_as_float(s0[j + 1])), sc2, make_float2(la.x, la.y));
+          const float2 xa1 = __ffma2_rn(make_float2(__uint_as_float(s0[j + 2]), __uint_as_float(s0[j + 3])), sc2, make_float2(la.z, la.w));
+          const float2 xb0 = __ffma2_rn(make_float2(__uint_as_float(s1[j]), __uint_as_float(s1[j + 1])), sc2, make_float2(lb.x, lb.y));
+          const float2 xb1 = __ffma2_rn(make_float2(__uint_as_float(s1[j + 2]), __uint_as_float(s1[j + 3])), sc2, make_float2(lb.z, lb.w));
+          pr[j] = ex2(xa0.x); pr[j + 1] = ex2(xa0.y);
+          pr[j + 2] = ex2(xa1.x); pr[j + 3] = ex2(xa1.y);
+          pr[32 + j] = ex2(xb0.x); pr[32 + j + 1] = ex2(xb0.y);
+#if BMA_DKDV_MATH == 2
+          const float2 eb1 = exp2_fma2(xb1);   // two of the eight on the FMA pipe
+          pr[32 + j + 2] = eb1.x; pr[32 + j + 3] = eb1.y;
+#else
+          pr[32 + j + 2] = ex2(xb1.x); pr[32 + j + 3] = ex2(xb1.y);
+#endif
+        }
+      }
+#endif
       if (partial_) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -475,6 +519,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tmem_wait_ld();
         // this thread holds its dPt values: its Pt may take their place (the store completes under the products below)
         tmem_st32(tmem + COL_PT + lane_base + half * 64, pk);  // 64 queries = 32 packed columns, inside this half's dPt columns
+#if BMA_DKDV_MATH == 0
 #pragma unroll
         for (int j4 = 0; j4 < 8; ++j4) {
           const float4 da = *reinterpret_cast<const float4*>(&sm.delta[st][(half * 2) * 32 + j4 * 4]);
@@ -492,6 +537,26 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           dsp[16 + j4 * 2] = pack_bf16(x1[0], x1[1]);
           dsp[16 + j4 * 2 + 1] = pack_bf16(x1[2], x1[3]);
         }
+#else
+#pragma unroll
+        for (int j4 = 0; j4 < 8; ++j4) {
+          const float4 da = *reinterpret_cast<const float4*>(&sm.delta[st][(half * 2) * 32 + j4 * 4]);        // -delta
+          const float4 db = *reinterpret_cast<const float4*>(&sm.delta[st][(half * 2 + 1) * 32 + j4 * 4]);
+          const int j = j4 * 4;
+          const float2 t0 = __fadd2_rn(make_float2(__uint_as_float(d0[j]), __uint_as_float(d0[j + 1])), make_float2(da.x, da.y));
+          const float2 t1 = __fadd2_rn(make_float2(__uint_as_float(d0[j + 2]), __uint_as_float(d0[j + 3])), make_float2(da.z, da.w));
+          const float2 t2 = __fadd2_rn(make_float2(__uint_as_float(d1[j]), __uint_as_float(d1[j + 1])), make_float2(db.x, db.y));
+          const float2 t3 = __fadd2_rn(make_float2(__uint_as_float(d1[j + 2]), __uint_as_float(d1[j + 3])), make_float2(db.z, db.w));
+          const float2 x0 = __fmul2_rn(make_float2(pr[j], pr[j + 1]), t0);
+          const float2 x1 = __fmul2_rn(make_float2(pr[j + 2], pr[j + 3]), t1);
+          const float2 x2 = __fmul2_rn(make_float2(pr[32 + j], pr[32 + j + 1]), t2);
+          const float2 x3 = __fmul2_rn(make_float2(pr[32 + j + 2], pr[32 + j + 3]), t3);
+          dsp[j4 * 2] = pack_bf16(x0.x, x0.y);
+          dsp[j4 * 2 + 1] = pack_bf16(x1.x, x1.y);
+          dsp[16 + j4 * 2] = pack_bf16(x2.x, x2.y);
+          dsp[16 + j4 * 2 + 1] = pack_bf16(x3.x, x3.y);
+        }
+#endif
       }
       // Pt and dSt go over columns of dPt that this very thread has just read (its half's 64 columns: Pt in the first 32,
       // dSt in the second 32), so the consumers need no rendezvous and no buffer to wait for.

@@ -38,9 +38,6 @@ constexpr uint32_t kHalfTile = BM * 64 * 2;     // one [128 x 64] bf16 box
 template <int HD> constexpr uint32_t kTileBytesOf = (HD / 64) * kHalfTile;  // a [128 x HD] operand tile: HD/64 boxes
 constexpr float kRescaleThreshold = 8.0f;       // log2 units: rescale O only when the max grew by > 2^8
 constexpr int kMaxKvTiles = 4096;               // merged kv list kept in shared memory
-#ifndef BMA_FWD_POLY
-#define BMA_FWD_POLY 1
-#endif
 
 enum {
   BAR_Q = 0,
@@ -77,6 +74,82 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
+}
+
+// Exponentials of 64 scores of one row against the reference maximum: p = 2^(s * sc - m), packed to bf16 pairs in pk,
+// returns their sum.  MUFU is the narrowest pipe of the softmax (8 issue cycles per warp instruction, shared by the two
+// warpgroups whose exponential phases overlap), so a share of the exponentials is a polynomial on the FMA pipe, and the
+// scale / subtract, the polynomial and the row sum use the packed two-wide FP32 instructions of sm_100:
+//   BMA_FWD_EXP_MODE 0: scalar arithmetic, a quarter of the exponentials on the FMA pipe
+//   BMA_FWD_EXP_MODE 1: packed arithmetic, half of them on the FMA pipe
+//   BMA_FWD_EXP_MODE 2: packed arithmetic, a quarter on the FMA pipe
+//   BMA_FWD_EXP_MODE 3: packed arithmetic, three eighths on the FMA pipe
+#ifndef BMA_FWD_EXP_MODE
+#define BMA_FWD_EXP_MODE 2
+#endif
+__device__ __forceinline__ float exp_half(const float* s, float sc, float m_sub, uint32_t (&pk)[32]) {
+#if BMA_FWD_EXP_MODE == 0
+  float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    const float e0 = ex2(fmaf(s[2 * j], sc, -m_sub));
+    const float e1 = ex2(fmaf(s[2 * j + 1], sc, -m_sub));
+    const float e2 = ex2(fmaf(s[2 * j + 2], sc, -m_sub));
+    const float e3 = exp2_fma(fmaf(s[2 * j + 3], sc, -m_sub));
+    rs0 += e0; rs1 += e1; rs2 += e2; rs3 += e3;
+    pk[j] = pack_bf16(e0, e1);
+    pk[j + 1] = pack_bf16(e2, e3);
+  }
+  return (rs0 + rs1) + (rs2 + rs3);
+#else
+  const float2 sc2 = make_float2(sc, sc), nm2 = make_float2(-m_sub, -m_sub);
+  float2 ra = make_float2(0.f, 0.f), rb = make_float2(0.f, 0.f);
+#if BMA_FWD_EXP_MODE == 1
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    const float2 xa = __ffma2_rn(make_float2(s[2 * j], s[2 * j + 1]), sc2, nm2);
+    const float2 xb = __ffma2_rn(make_float2(s[2 * j + 2], s[2 * j + 3]), sc2, nm2);
+    const float2 ea = make_float2(ex2(xa.x), ex2(xa.y));
+    const float2 eb = exp2_fma2(xb);
+    ra = __fadd2_rn(ra, ea);
+    rb = __fadd2_rn(rb, eb);
+    pk[j] = pack_bf16(ea.x, ea.y);
+    pk[j + 1] = pack_bf16(eb.x, eb.y);
+  }
+#elif BMA_FWD_EXP_MODE == 3
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    float2 e[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const float2 x = __ffma2_rn(make_float2(s[2 * (j + u)], s[2 * (j + u) + 1]), sc2, nm2);
+      e[u] = (u == 2 || u == 5 || u == 7) ? exp2_fma2(x) : make_float2(ex2(x.x), ex2(x.y));
+      pk[j + u] = pack_bf16(e[u].x, e[u].y);
+    }
+    ra = __fadd2_rn(ra, __fadd2_rn(__fadd2_rn(e[0], e[1]), __fadd2_rn(e[2], e[3])));
+    rb = __fadd2_rn(rb, __fadd2_rn(__fadd2_rn(e[4], e[5]), __fadd2_rn(e[6], e[7])));
+  }
+#else
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float2 x0 = __ffma2_rn(make_float2(s[2 * j], s[2 * j + 1]), sc2, nm2);
+    const float2 x1 = __ffma2_rn(make_float2(s[2 * j + 2], s[2 * j + 3]), sc2, nm2);
+    const float2 x2 = __ffma2_rn(make_float2(s[2 * j + 4], s[2 * j + 5]), sc2, nm2);
+    const float2 x3 = __ffma2_rn(make_float2(s[2 * j + 6], s[2 * j + 7]), sc2, nm2);
+    const float2 e0 = make_float2(ex2(x0.x), ex2(x0.y));
+    const float2 e1 = make_float2(ex2(x1.x), ex2(x1.y));
+    const float2 e2 = make_float2(ex2(x2.x), ex2(x2.y));
+    const float2 e3 = exp2_fma2(x3);
+    ra = __fadd2_rn(ra, __fadd2_rn(e0, e1));
+    rb = __fadd2_rn(rb, __fadd2_rn(e2, e3));
+    pk[j] = pack_bf16(e0.x, e0.y);
+    pk[j + 1] = pack_bf16(e1.x, e1.y);
+    pk[j + 2] = pack_bf16(e2.x, e2.y);
+    pk[j + 3] = pack_bf16(e3.x, e3.y);
+  }
+#endif
+  return (ra.x + ra.y) + (rb.x + rb.y);
+#endif
 }
 
 // Allowed key interval [jlo, jhi] (tile-local, inclusive) of query row q for interval-only masks.
@@ -368,34 +441,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         }
       }
       const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+      float row_sum = 0.f;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t pk[32];
-#pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const float e0 = ex2(fmaf(s[c * 64 + 2 * j], sc, -m_sub));
-          const float e1 = ex2(fmaf(s[c * 64 + 2 * j + 1], sc, -m_sub));
-#if BMA_FWD_POLY >= 2
-          const float e2 = exp2_fma(fmaf(s[c * 64 + 2 * j + 2], sc, -m_sub));
-#else
-          const float e2 = ex2(fmaf(s[c * 64 + 2 * j + 2], sc, -m_sub));
-#endif
-#if BMA_FWD_POLY >= 1
-          const float e3 = exp2_fma(fmaf(s[c * 64 + 2 * j + 3], sc, -m_sub));
-#else
-          const float e3 = ex2(fmaf(s[c * 64 + 2 * j + 3], sc, -m_sub));
-#endif
-          rs0 += e0; rs1 += e1; rs2 += e2; rs3 += e3;
-          pk[j] = pack_bf16(e0, e1);
-          pk[j + 1] = pack_bf16(e2, e3);
-        }
+        row_sum += exp_half(&s[c * 64], sc, m_sub, pk);
         tmem_st32(tmem_s + c * 32, pk);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&sm.bar[(c == 0 ? BAR_PH0 : BAR_P0) + x]);
       }
-      l = l * alpha + ((rs0 + rs1) + (rs2 + rs3));
+      l = l * alpha + row_sum;
       ++cnt;
     }
 
@@ -893,34 +949,17 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           }
         }
         const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
-        float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+        float row_sum = 0.f;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t pk[32];
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const float e0 = ex2(fmaf(s[c * 64 + 2 * j], sc, -m_sub));
-            const float e1 = ex2(fmaf(s[c * 64 + 2 * j + 1], sc, -m_sub));
-#if BMA_FWD_POLY >= 2
-            const float e2 = exp2_fma(fmaf(s[c * 64 + 2 * j + 2], sc, -m_sub));
-#else
-            const float e2 = ex2(fmaf(s[c * 64 + 2 * j + 2], sc, -m_sub));
-#endif
-#if BMA_FWD_POLY >= 1
-            const float e3 = exp2_fma(fmaf(s[c * 64 + 2 * j + 3], sc, -m_sub));
-#else
-            const float e3 = ex2(fmaf(s[c * 64 + 2 * j + 3], sc, -m_sub));
-#endif
-            rs0 += e0; rs1 += e1; rs2 += e2; rs3 += e3;
-            pk[j] = pack_bf16(e0, e1);
-            pk[j + 1] = pack_bf16(e2, e3);
-          }
+          row_sum += exp_half(&s[c * 64], sc, m_sub, pk);
           tmem_st32(tmem_s + c * 32, pk);
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(&sm.bar[(c == 0 ? PB_PH0 : PB_P0) + x]);
         }
-        l = l * alpha + ((rs0 + rs1) + (rs2 + rs3));
+        l = l * alpha + row_sum;
         ++cnt;
         ++done;
       }

@@ -228,6 +228,20 @@ __device__ __forceinline__ float exp2_fma(float x) {
   const float pf = fmaf(fmaf(fmaf(0.05500893f, f, 0.24221096f), f, 0.69328293f), f, 1.0f);
   return __int_as_float(__float_as_int(pf) + (__float_as_int(xr) << 23));
 }
+// The same for two values at once with the packed FP32 instructions of sm_100 (fma.rn.f32x2 / add.rn.f32x2 through the
+// float2 intrinsics): 5 instead of 9 issue slots per exponential.
+__device__ __forceinline__ float2 exp2_fma2(float2 x) {
+  x.x = fmaxf(x.x, -126.0f);
+  x.y = fmaxf(x.y, -126.0f);
+  const float2 xr = __fadd2_rn(x, make_float2(12582912.0f, 12582912.0f));
+  const float2 t = __fadd2_rn(xr, make_float2(-12582912.0f, -12582912.0f));
+  const float2 f = __ffma2_rn(t, make_float2(-1.0f, -1.0f), x);
+  float2 pf = __ffma2_rn(make_float2(0.05500893f, 0.05500893f), f, make_float2(0.24221096f, 0.24221096f));
+  pf = __ffma2_rn(pf, f, make_float2(0.69328293f, 0.69328293f));
+  pf = __ffma2_rn(pf, f, make_float2(1.0f, 1.0f));
+  return make_float2(__int_as_float(__float_as_int(pf.x) + (__float_as_int(xr.x) << 23)),
+                     __int_as_float(__float_as_int(pf.y) + (__float_as_int(xr.y) << 23)));
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
