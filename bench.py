@@ -354,6 +354,11 @@ def measure_config(name, dev, steps=5, warmup=3, seed=100):
     for _ in range(warmup):
         step()
     torch.cuda.synchronize(dev)
+    # short workloads: keep warming until the GPU has been busy for 0.2 s, or its clocks are still ramping when timing starts
+    w0 = time.perf_counter()
+    while time.perf_counter() - w0 < 0.2:
+        step()
+        torch.cuda.synchronize(dev)
     sink = {}
     A.set_profile_sink(sink)
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -38,12 +38,21 @@ constexpr uint32_t kHalfTile = BM * 64 * 2;     // one [128 x 64] bf16 box
 template <int HD> constexpr uint32_t kTileBytesOf = (HD / 64) * kHalfTile;  // a [128 x HD] operand tile: HD/64 boxes
 constexpr float kRescaleThreshold = 8.0f;       // log2 units: rescale O only when the max grew by > 2^8
 constexpr int kMaxKvTiles = 4096;               // merged kv list kept in shared memory
+// P goes from the softmax warps to the MMA warp in this many parts (key ranges of 128 / kPParts), each with its own
+// barrier, so that the first k-steps of P V run under the remaining exponentials: 2 or 4.  Measured (same box, forward
+// TFLOP/s on config 2 / L=8192 / config 5): 2 parts 1091 / 1129 / 1258, 4 parts 1037 / 1065 / 1192 -- each hand-over costs a
+// TMEM store wait, a fence and 128 barrier arrivals, more than the 128 cycles of P V it uncovers.
+#ifndef BMA_FWD_P_PARTS
+#define BMA_FWD_P_PARTS 2
+#endif
+constexpr int kPParts = BMA_FWD_P_PARTS;
+constexpr int kPartWords = 64 / kPParts;        // packed bf16 pairs (TMEM columns) per part
 
 enum {
   BAR_Q = 0,
   BAR_K_FULL0, BAR_K_FULL1, BAR_K_FREE0, BAR_K_FREE1,
   BAR_V_FULL0, BAR_V_FULL1, BAR_V_FREE0, BAR_V_FREE1,
-  BAR_S0, BAR_S1, BAR_PH0, BAR_PH1, BAR_P0, BAR_P1, BAR_O0, BAR_O1, BAR_EPI0, BAR_EPI1,
+  BAR_S0, BAR_S1, BAR_PART, BAR_PART_LAST = BAR_PART + 2 * kPParts - 1, BAR_O0, BAR_O1, BAR_EPI0, BAR_EPI1,
   NUM_BARS
 };
 
@@ -76,7 +85,7 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return r;
 }
 
-// Exponentials of 64 scores of one row against the reference maximum: p = 2^(s * sc - m), packed to bf16 pairs in pk,
+// Exponentials of 2 * WORDS scores of one row against the reference maximum: p = 2^(s * sc - m), packed to bf16 pairs in pk,
 // returns their sum.  MUFU is the narrowest pipe of the softmax (8 issue cycles per warp instruction, shared by the two
 // warpgroups whose exponential phases overlap), so a share of the exponentials is a polynomial on the FMA pipe, and the
 // scale / subtract, the polynomial and the row sum use the packed two-wide FP32 instructions of sm_100:
@@ -87,11 +96,15 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 #ifndef BMA_FWD_EXP_MODE
 #define BMA_FWD_EXP_MODE 2
 #endif
-__device__ __forceinline__ float exp_half(const float* s, float sc, float m_sub, uint32_t (&pk)[32]) {
+__device__ __forceinline__ void tmem_st_words(uint32_t taddr, const uint32_t (&r)[32]) { tmem_st32(taddr, r); }
+__device__ __forceinline__ void tmem_st_words(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st16(taddr, r); }
+
+template <int WORDS>
+__device__ __forceinline__ float exp_part(const float* s, float sc, float m_sub, uint32_t (&pk)[WORDS]) {
 #if BMA_FWD_EXP_MODE == 0
   float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
 #pragma unroll
-  for (int j = 0; j < 32; j += 2) {
+  for (int j = 0; j < WORDS; j += 2) {
     const float e0 = ex2(fmaf(s[2 * j], sc, -m_sub));
     const float e1 = ex2(fmaf(s[2 * j + 1], sc, -m_sub));
     const float e2 = ex2(fmaf(s[2 * j + 2], sc, -m_sub));
@@ -106,7 +119,7 @@ __device__ __forceinline__ float exp_half(const float* s, float sc, float m_sub,
   float2 ra = make_float2(0.f, 0.f), rb = make_float2(0.f, 0.f);
 #if BMA_FWD_EXP_MODE == 1
 #pragma unroll
-  for (int j = 0; j < 32; j += 2) {
+  for (int j = 0; j < WORDS; j += 2) {
     const float2 xa = __ffma2_rn(make_float2(s[2 * j], s[2 * j + 1]), sc2, nm2);
     const float2 xb = __ffma2_rn(make_float2(s[2 * j + 2], s[2 * j + 3]), sc2, nm2);
     const float2 ea = make_float2(ex2(xa.x), ex2(xa.y));
@@ -118,7 +131,7 @@ __device__ __forceinline__ float exp_half(const float* s, float sc, float m_sub,
   }
 #elif BMA_FWD_EXP_MODE == 3
 #pragma unroll
-  for (int j = 0; j < 32; j += 8) {
+  for (int j = 0; j < WORDS; j += 8) {
     float2 e[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
@@ -131,7 +144,7 @@ __device__ __forceinline__ float exp_half(const float* s, float sc, float m_sub,
   }
 #else
 #pragma unroll
-  for (int j = 0; j < 32; j += 4) {
+  for (int j = 0; j < WORDS; j += 4) {
     const float2 x0 = __ffma2_rn(make_float2(s[2 * j], s[2 * j + 1]), sc2, nm2);
     const float2 x1 = __ffma2_rn(make_float2(s[2 * j + 2], s[2 * j + 3]), sc2, nm2);
     const float2 x2 = __ffma2_rn(make_float2(s[2 * j + 4], s[2 * j + 5]), sc2, nm2);
@@ -200,7 +213,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   if (threadIdx.x == 0) {
     mbar_init(&sm.bar[BAR_Q], 1);
     for (int i = BAR_K_FULL0; i < NUM_BARS; ++i)
-      mbar_init(&sm.bar[i], (i == BAR_P0 || i == BAR_P1 || i == BAR_PH0 || i == BAR_PH1 || i == BAR_EPI0 || i == BAR_EPI1) ? 128 : 1);
+      mbar_init(&sm.bar[i], ((i >= BAR_PART && i <= BAR_PART_LAST) || i == BAR_EPI0 || i == BAR_EPI1) ? 128 : 1);
     fence_barrier_init();
   }
   __syncthreads();
@@ -317,12 +330,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             // P arrives in two halves (keys 0..63, then 64..127) so that the first k-steps run under
             // the second half of the exponentials
 #pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-              ok = mbar_wait(&sm.bar[(hf == 0 ? BAR_PH0 : BAR_P0) + x], cnt & 1);
+            for (int hf = 0; hf < kPParts; ++hf) {
+              ok = mbar_wait(&sm.bar[BAR_PART + 2 * hf + x], cnt & 1);
               if (!ok) break;
               tc_fence_after();
 #pragma unroll
-              for (int ks = hf * 4; ks < hf * 4 + 4; ++ks) {
+              for (int ks = hf * (8 / kPParts); ks < (hf + 1) * (8 / kPParts); ++ks) {
                 // B = V[kv rows][d] read MN-major: 16 kv rows per k-step = 2048 B; the two 64-column boxes are kHalfTile apart
                 if (leader)
                   mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, dv0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)),
@@ -443,13 +456,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
       float row_sum = 0.f;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pk[32];
-        row_sum += exp_half(&s[c * 64], sc, m_sub, pk);
-        tmem_st32(tmem_s + c * 32, pk);
+      for (int c = 0; c < kPParts; ++c) {
+        uint32_t pk[kPartWords];
+        row_sum += exp_part<kPartWords>(&s[c * 2 * kPartWords], sc, m_sub, pk);
+        tmem_st_words(tmem_s + c * kPartWords, pk);
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(&sm.bar[(c == 0 ? BAR_PH0 : BAR_P0) + x]);
+        mbar_arrive(&sm.bar[BAR_PART + 2 * c + x]);
       }
       l = l * alpha + row_sum;
       ++cnt;
@@ -575,7 +588,7 @@ enum {
   PB_Q_FULL0, PB_Q_FULL1, PB_Q_FREE0, PB_Q_FREE1,
   PB_K_FULL0, PB_K_FULL1, PB_K_FREE0, PB_K_FREE1,
   PB_V_FULL0, PB_V_FULL1, PB_V_FREE0, PB_V_FREE1,
-  PB_S0, PB_S1, PB_PH0, PB_PH1, PB_P0, PB_P1, PB_O0, PB_O1, PB_EPI0, PB_EPI1,
+  PB_S0, PB_S1, PB_PART, PB_PART_LAST = PB_PART + 2 * kPParts - 1, PB_O0, PB_O1, PB_EPI0, PB_EPI1,
   PB_NUM
 };
 constexpr int kListConsumers = 2 + 256;  // producer, MMA warp (one lane each), every softmax thread
@@ -639,7 +652,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     for (int i = 0; i < PB_NUM; ++i) {
       uint32_t count = 1;
       if (i == PB_LIST_FREE0 || i == PB_LIST_FREE1) count = kListConsumers;
-      else if (i >= PB_PH0 && i <= PB_P1) count = 128;
+      else if (i >= PB_PART && i <= PB_PART_LAST) count = 128;
       else if (i == PB_EPI0 || i == PB_EPI1) count = 128;
       mbar_init(&sm.bar[i], count);
     }
@@ -807,12 +820,12 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
               int& cnt = x == 0 ? cnt0 : cnt1;
               uint32_t& done = x == 0 ? done0 : done1;
 #pragma unroll
-              for (int hf = 0; hf < 2; ++hf) {
-                ok = mbar_wait(&sm.bar[(hf == 0 ? PB_PH0 : PB_P0) + x], done & 1);
+              for (int hf = 0; hf < kPParts; ++hf) {
+                ok = mbar_wait(&sm.bar[PB_PART + 2 * hf + x], done & 1);
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
-                for (int ks = hf * 4; ks < hf * 4 + 4; ++ks)
+                for (int ks = hf * (8 / kPParts); ks < (hf + 1) * (8 / kPParts); ++ks)
                   if (leader)
                     mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, dv0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)),
                            idesc_o, (cnt > 0) || (ks > 0));
@@ -951,13 +964,13 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
         float row_sum = 0.f;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t pk[32];
-          row_sum += exp_half(&s[c * 64], sc, m_sub, pk);
-          tmem_st32(tmem_s + c * 32, pk);
+        for (int c = 0; c < kPParts; ++c) {
+          uint32_t pk[kPartWords];
+          row_sum += exp_part<kPartWords>(&s[c * 2 * kPartWords], sc, m_sub, pk);
+          tmem_st_words(tmem_s + c * kPartWords, pk);
           tmem_wait_st();
           tc_fence_before();
-          mbar_arrive(&sm.bar[(c == 0 ? PB_PH0 : PB_P0) + x]);
+          mbar_arrive(&sm.bar[PB_PART + 2 * c + x]);
         }
         l = l * alpha + row_sum;
         ++cnt;
