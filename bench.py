@@ -325,9 +325,16 @@ def parity_of_slices(w, Q, K, V, dO, O, grads, seg=None, flex=False):
     return out
 
 
-def measure_config(name, dev, steps=5, warmup=3, seed=100):
+def _traced_causal(b, h, q, k):
+    return k <= q
+
+
+def measure_config(name, dev, steps=5, warmup=3, seed=100, traced=False):
     """One side workload, device-timed: forward + backward through masked_attention_via_map on inputs generated
-    on the device; the launch groups are timed separately with CUDA events on the launching stream."""
+    on the device; the launch groups are timed separately with CUDA events on the launching stream.  ``traced``:
+    the causal mask as a plain Python lambda instead of ``is_causal`` — it is traced into a mask program, evaluated
+    on the device into the tile form of the mask description (once, cached on the function) and read by the kernels
+    on the tiles it cuts."""
     import jaxmodules_b200 as jm
     from jaxmodules_b200 import _native as nat, attention as A, masks as M
     from jaxmodules_b200.block_mask import compile_block_lists
@@ -338,8 +345,11 @@ def measure_config(name, dev, steps=5, warmup=3, seed=100):
     Q, K, V = (device_randn((B, L, H, d), seed + i, dt, scale, dev).requires_grad_(True) for i in range(3))
     dO = device_randn((B, L, H, d), seed + 3, torch.float32, 1.0, dev)
     kw = mask_kwargs(w, M)
+    if traced:
+        assert w["mask"] == "causal"
+        kw = dict(mask_fn=_traced_causal, block_size=w["bs"])
     be, tq, tk = A.plan(Q, K, V)
-    terms = M.MaskTerms(causal=True) if kw.get("is_causal") else M.terms_from_mask_fn(kw["mask_fn"], B, H, L, L)
+    terms = M.MaskTerms(causal=True) if kw.get("is_causal") else M.terms_from_mask_fn(kw["mask_fn"], B, H, L, L, device=dev)
     if kw.get("window_size") is not None:
         bs = w["bs"]
         terms = terms.merged(M.MaskTerms(window=(bs, (kw["window_size"][0] + bs - 1) // bs, 1 + (kw["window_size"][1] + bs - 1) // bs, L // bs)))
@@ -372,6 +382,9 @@ def measure_config(name, dev, steps=5, warmup=3, seed=100):
     per = {k: float(np.mean([a.elapsed_time(b) for a, b in v])) for k, v in sink.items()}
     _, burst, _, _ = peaks()
     tf = lambda fl, t: fl / (t * 1e-3) / 1e12 if t else None
+    if traced:
+        t = terms.tiles if terms.tiles is not None else None
+        w = dict(w, desc=w["desc"] + ", mask as a traced Python lambda (" + ("tile form: %d cut tiles of 2 KB" % t[2].shape[0] if t else "dense bit table") + ")")
     out = {"workload": w["desc"], "backend": {1: "simt", 2: "tcgen05"}.get(be, str(be)), "steps": steps, "warmup": warmup,
            "nonempty_blocks": blocks, "ms_per_step": ms, "value": tf(step_flops, ms), "fwd_tflops": tf(fwd_flops, per.get("fwd")),
            "bwd_tflops": tf(step_flops - fwd_flops, per.get("bwd")), "kernel_ms": per, "status": A.device_status(dev)}
@@ -843,6 +856,7 @@ def main():
             extra["parity"] = parity
         if world == 1:
             extra["per_config"] = {name: measure_config(name, dev) for name in ("t0", "c3", "c4", "c5", "d64", "c1") if name != args.workload}
+            extra["traced_mask_t0"] = measure_config("t0", dev, traced=True)
             extra["block_mask_c5"] = block_mask_build_entry(WORKLOADS["c5"], dev, steps=5, warmup=3)
         else:
             extra["c5_head_shards"] = c5_head_shards(rank, world, dev, dist)

@@ -58,6 +58,11 @@ enum { BMA_DTYPE_F32 = 0, BMA_DTYPE_BF16 = 1 };
  *   SEGMENT     : seg_q[b*seg_q_stride + gq] == seg_k[b*seg_k_stride + gk]
  *   BITMAP      : bit (gk & 31) of bitmap[((b%bitmap_B)*bitmap_H + h%bitmap_H)*bitmap_q + gq)*bitmap_words + gk/32]
  *                 (an arbitrary host-evaluated mask_fn; h is the QUERY head, attention.py:72-73)
+ *   TILES       : the same arbitrary predicate stored per 128 x 128 tile of the global (gq, gk) grid, so that its
+ *                 memory grows with the tiles the mask CUTS, not with N*L (bma_mask_tiles_build makes it from a mask
+ *                 program).  t = ((b%tiles_B)*tiles_H + h%tiles_H)*tiles_q + gq/128)*tiles_k + gk/128:
+ *                 tile_class[t] = 0 no pair of the tile is allowed, 2 every pair is, 1 some are -- and then bit (gk & 31)
+ *                 of tile_bits[(tile_slot[t]*128 + gq%128)*4 + (gk%128)/32] decides.
  */
 enum {
   BMA_MASK_CAUSAL = 1,
@@ -65,6 +70,7 @@ enum {
   BMA_MASK_BLOCK_WINDOW = 4,
   BMA_MASK_SEGMENT = 8,
   BMA_MASK_BITMAP = 16,
+  BMA_MASK_TILES = 32,
   /* Not a mask term but a request to bma_mask_compile: segment-id blocks that the per-block id ranges
    * cannot decide are reported PARTIAL without scanning their elements.  The lists then may name a block
    * whose exact class is empty (never the reverse, and full blocks stay exact), which is harmless for the
@@ -85,6 +91,10 @@ typedef struct bma_mask_spec {
   const int32_t* seg_k;
   int64_t seg_q_stride, seg_k_stride;
   const uint32_t* bitmap;
+  int32_t tiles_B, tiles_H, tiles_q, tiles_k; /* TILES: extents of the tile grid (tiles_q = ceil(rows / 128) ...) */
+  const uint8_t* tile_class;                   /* [tiles_B, tiles_H, tiles_q, tiles_k]            */
+  const int32_t* tile_slot;                    /* same shape; meaningful where tile_class == 1     */
+  const uint32_t* tile_bits;                   /* [slots, 128, 4]                                  */
 } bma_mask_spec;
 
 /* ---- block lists ---------------------------------------------------------------------
@@ -225,6 +235,17 @@ typedef struct bma_mask_program {
 
 int bma_mask_table_build(const bma_mask_program* program, int32_t B, int32_t H, int32_t N, int32_t L,
                          int32_t q_offset, int32_t k_offset, int32_t* bits, bma_stream_t stream);
+
+/* The same evaluation into the TILES form of the mask description: classifies every 128 x 128 tile of the
+ * [B, H, N, L] box (global indices q + q_offset, k + k_offset must be tile-aligned: both offsets multiples of 128)
+ * and stores the bits of the tiles that are cut.  tile_class / tile_slot: [B, H, ceil(N/128), ceil(L/128)];
+ * tile_bits: room for `capacity` tiles of 2 KB (may be NULL with capacity 0 to count only); *counter (device int32,
+ * zeroed by the caller) receives the number of cut tiles -- when it exceeds `capacity` the surplus tiles were not
+ * stored and the call has to be repeated with more room.  Elements outside N x L count as not allowed in the bits
+ * and are ignored by the class.  B or H may be 1 when the program does not read that index. */
+int bma_mask_tiles_build(const bma_mask_program* program, int32_t B, int32_t H, int32_t N, int32_t L,
+                         int32_t q_offset, int32_t k_offset, uint8_t* tile_class, int32_t* tile_slot,
+                         uint32_t* tile_bits, int32_t capacity, int32_t* counter, bma_stream_t stream);
 
 /* Which backend and tile sizes bma_attn_fwd (bma_attn_plan) and bma_attn_bwd
  * (bma_attn_bwd_plan) will use for these arguments; the block lists passed to each must be

@@ -15,7 +15,7 @@ BMA_OK = 0
 BMA_ERR_ARG, BMA_ERR_UNSUPPORTED, BMA_ERR_WORKSPACE, BMA_ERR_CUDA, BMA_ERR_LIMIT = -1, -2, -3, -4, -5
 BMA_ERR_DEVICE_CHECK = 1
 BMA_DTYPE_F32, BMA_DTYPE_BF16 = 0, 1
-BMA_MASK_CAUSAL, BMA_MASK_BAND, BMA_MASK_BLOCK_WINDOW, BMA_MASK_SEGMENT, BMA_MASK_BITMAP = 1, 2, 4, 8, 16
+BMA_MASK_CAUSAL, BMA_MASK_BAND, BMA_MASK_BLOCK_WINDOW, BMA_MASK_SEGMENT, BMA_MASK_BITMAP, BMA_MASK_TILES = 1, 2, 4, 8, 16, 32
 BMA_MASK_COMPILE_CONSERVATIVE = 256
 BMA_BACKEND_AUTO, BMA_BACKEND_SIMT, BMA_BACKEND_TCGEN05 = 0, 1, 2
 
@@ -32,6 +32,8 @@ class MaskSpec(C.Structure):
         ("seg_q", C.c_void_p), ("seg_k", C.c_void_p),
         ("seg_q_stride", C.c_int64), ("seg_k_stride", C.c_int64),
         ("bitmap", C.c_void_p),
+        ("tiles_B", C.c_int32), ("tiles_H", C.c_int32), ("tiles_q", C.c_int32), ("tiles_k", C.c_int32),
+        ("tile_class", C.c_void_p), ("tile_slot", C.c_void_p), ("tile_bits", C.c_void_p),
     ]
 
 
@@ -96,6 +98,8 @@ SIGNATURES = {
     "bma_mask_compile_static": (C.c_int, [C.POINTER(MaskSpec), C.c_int32, C.c_int32, C.POINTER(BlockLists), C.c_void_p]),
     "bma_mask_table_build": (C.c_int, [C.POINTER(MaskProgram), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                        C.c_void_p, C.c_void_p]),
+    "bma_mask_tiles_build": (C.c_int, [C.POINTER(MaskProgram), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "bma_attn_plan": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "bma_attn_bwd_plan": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "bma_attn_fwd": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(MaskSpec), C.POINTER(BlockLists), C.c_void_p]),

@@ -366,7 +366,7 @@ if constexpr (KB) {  // key bias: + kb2 * (global key index) on every column
             const int lo = max(jlo - c * 32, 0), hi = min(jhi - c * 32, 31);
             bits[c] = (lo <= hi) ? ((0xffffffffu >> (31 - hi)) & (0xffffffffu << lo)) : 0u;
           }
-          if (mv.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP)) {  // segment ids / bit table: 32 keys per word
+          if (mv.flags & kTableTerms) {  // segment ids / bit table: 32 keys per word
 #pragma unroll
             for (int c = 0; c < 4; ++c)
               if (bits[c]) bits[c] &= table_bits_row32(mv, q, k0 + c * 32);
@@ -473,7 +473,7 @@ int sm100_bwd_dq(const bma_attn_args& a, const bma_mask_spec& spec, const bma_bl
   DqParams p;
   p.a = a; p.spec = spec; p.l = lists;
   p.scale_log2 = a.scale * kLog2e;
-  p.interval_mask = (spec.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP)) ? 0 : 1;
+  p.interval_mask = (spec.flags & kTableTerms) ? 0 : 1;
   p.status = device_status_ptr();
   BMA_REQUIRE(p.status != nullptr, BMA_ERR_CUDA);
 

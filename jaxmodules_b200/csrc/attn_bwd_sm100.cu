@@ -38,11 +38,14 @@
 //   1: the packed two-wide FP32 instructions of sm_100 (fma / add / mul .f32x2) for the scale-and-shift and for
 //      dS = P * (dP - delta); every exponential on the MUFU pipe
 //   2: as 1, and a quarter of the exponentials as a packed polynomial on the FMA pipe
+//   3: packed scale-and-shift with the polynomial quarter, scalar dS;  4: scalar exponentials, packed dS;  5: packed scale-and-shift only
 // Measured on config 2 / the L=8192 shape (same box): 0: 2.127 / 4.238 ms, 1: 2.233 / 4.366 ms, 2: 2.216 / 4.216 ms -- the
 // kernel is bound by shared-memory operand traffic (2 560 cycles per tile at 128 B/clk), not by instruction issue, so 0.
 #ifndef BMA_DKDV_MATH
 #define BMA_DKDV_MATH 0
 #endif
+#define BMA_DKDV_PACKED_EXP (BMA_DKDV_MATH == 1 || BMA_DKDV_MATH == 2 || BMA_DKDV_MATH == 3 || BMA_DKDV_MATH == 5)
+#define BMA_DKDV_PACKED_DS (BMA_DKDV_MATH == 1 || BMA_DKDV_MATH == 2 || BMA_DKDV_MATH == 4)
 #ifndef BMA_DKDV_POLY
 #define BMA_DKDV_POLY 0  // scalar polynomial (BMA_DKDV_MATH 0 only); measured 3.87 ms against 3.78 ms for the whole backward, so off
 #endif
@@ -343,12 +346,16 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const int64_t off = ((int64_t)b * a.Hq + h) * a.N + q;
           const float lv = q < a.N ? __ldg(a.lse + off) : -INFINITY;
           // +inf for rows that attend nothing or lie outside: their probabilities become exactly 0
-#if BMA_DKDV_MATH == 0
-          sm.lse2[st][idx] = (lv == -INFINITY) ? INFINITY : lv * kLog2e;
-          sm.delta[st][idx] = q < a.N ? __ldg(a.delta + off) : 0.f;
-#else     // the packed forms add: -lse2 (and -inf for a dead row) and -delta are what is staged
+          // the packed forms add: -lse2 (and -inf for a dead row) and -delta are what is staged for them
+#if BMA_DKDV_PACKED_EXP
           sm.lse2[st][idx] = (lv == -INFINITY) ? -INFINITY : -lv * kLog2e;
+#else
+          sm.lse2[st][idx] = (lv == -INFINITY) ? INFINITY : lv * kLog2e;
+#endif
+#if BMA_DKDV_PACKED_DS
           sm.delta[st][idx] = q < a.N ? -__ldg(a.delta + off) : 0.f;
+#else
+          sm.delta[st][idx] = q < a.N ? __ldg(a.delta + off) : 0.f;
 #endif
         }
         mbar_arrive(&sm.bar[BAR_STAT0 + st]);
@@ -415,7 +422,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             col_interval(mv, k, q0, jlo, jhi);
             const int lo = max(jlo - cg * 32, 0), hi = min(jhi - cg * 32, 31);
             bits[c] = (lo <= hi) ? ((0xffffffffu >> (31 - hi)) & (0xffffffffu << lo)) : 0u;
-            if (bits[c] && (mv.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP))) bits[c] &= table_bits_col32(mv, k, q0 + cg * 32);
+            if (bits[c] && (mv.flags & kTableTerms)) bits[c] &= table_bits_col32(mv, k, q0 + cg * 32);
           } else {
             uint32_t w = 0;
 #pragma unroll
@@ -433,7 +440,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_before();
       mbar_arrive(&sm.bar[BAR_LS]);
       if (!mbar_wait(&sm.bar[BAR_STAT0 + st], (n >> 1) & 1)) return false;
-#if BMA_DKDV_MATH == 0
+#if !BMA_DKDV_PACKED_EXP
 #pragma unroll
       for (int j4 = 0; j4 < 8; ++j4) {
         const float4 la = *reinterpret_cast<const float4*>(&sm.lse2[st][(half * 2) * 32 + j4 * 4]);
@@ -475,7 +482,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           pr[j] = ex2(xa0.x); pr[j + 1] = ex2(xa0.y);
           pr[j + 2] = ex2(xa1.x); pr[j + 3] = ex2(xa1.y);
           pr[32 + j] = ex2(xb0.x); pr[32 + j + 1] = ex2(xb0.y);
-#if BMA_DKDV_MATH == 2
+#if BMA_DKDV_MATH == 2 || BMA_DKDV_MATH == 3
           const float2 eb1 = exp2_fma2(xb1);   // two of the eight on the FMA pipe
           pr[32 + j + 2] = eb1.x; pr[32 + j + 3] = eb1.y;
 #else
@@ -519,7 +526,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tmem_wait_ld();
         // this thread holds its dPt values: its Pt may take their place (the store completes under the products below)
         tmem_st32(tmem + COL_PT + lane_base + half * 64, pk);  // 64 queries = 32 packed columns, inside this half's dPt columns
-#if BMA_DKDV_MATH == 0
+#if !BMA_DKDV_PACKED_DS
 #pragma unroll
         for (int j4 = 0; j4 < 8; ++j4) {
           const float4 da = *reinterpret_cast<const float4*>(&sm.delta[st][(half * 2) * 32 + j4 * 4]);

@@ -365,7 +365,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     const int q = qi * BM + row;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tmem_s = tmem + x * 128 + lane_base, tmem_o = tmem + 256 + x * 128 + lane_base;
-    const MaskView mv = make_mask_view(p.spec, b, h);
     const float kb2 = (KB && a.key_bias) ? __ldg(a.key_bias + h) * kLog2e : 0.f;  // per-head key bias, log2 units
     float m_ref = -INFINITY;  // reference max (log2 domain) the exponentials are taken against
     float l = 0.f;
@@ -398,13 +397,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       }
       const float sc = KB ? 1.f : p.scale_log2;
       if constexpr (KB) {  // key bias: fold the scale and kb2 * (global key index) into the scores once
-        const float base = kb2 * (float)(mv.k_offset + k0);
+        const float base = kb2 * (float)(p.spec.k_offset + k0);
 #pragma unroll
         for (int j = 0; j < BN; ++j) s[j] = fmaf(s[j], p.scale_log2, fmaf((float)j, kb2, base));
       }
       if (cls == 1) {  // partial tile: masked scores become -inf (their exponential is exactly 0)
         uint32_t bits[4];
         {
+          // the mask description is rebuilt from the kernel parameters here rather than carried in registers through the full tiles
+          const MaskView mv = make_mask_view(p.spec, b, h);
           int jlo, jhi;
           row_interval(mv, q, k0, jlo, jhi);
 #pragma unroll
@@ -412,7 +413,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             const int lo = max(jlo - c * 32, 0), hi = min(jhi - c * 32, 31);
             bits[c] = (lo <= hi) ? ((0xffffffffu >> (31 - hi)) & (0xffffffffu << lo)) : 0u;
           }
-          if (mv.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP)) {  // segment ids / bit table: 32 keys per word
+          if (mv.flags & kTableTerms) {  // segment ids / bit table: 32 keys per word
 #pragma unroll
             for (int c = 0; c < 4; ++c)
               if (bits[c]) bits[c] &= table_bits_row32(mv, q, k0 + c * 32);
@@ -922,7 +923,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
               const int lo = max(jlo - c * 32, 0), hi = min(jhi - c * 32, 31);
               bits[c] = (lo <= hi) ? ((0xffffffffu >> (31 - hi)) & (0xffffffffu << lo)) : 0u;
             }
-            if (mv.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP)) {
+            if (mv.flags & kTableTerms) {
 #pragma unroll
               for (int c = 0; c < 4; ++c)
                 if (bits[c]) bits[c] &= table_bits_row32(mv, q, k0 + c * 32);
@@ -1204,7 +1205,7 @@ int sm100_fwd(const bma_attn_args& a, const bma_mask_spec& spec, const bma_block
   FwdParams p;
   p.a = a; p.spec = spec; p.l = lists;
   p.scale_log2 = a.scale * kLog2e;
-  p.interval_mask = (spec.flags & (BMA_MASK_SEGMENT | BMA_MASK_BITMAP)) ? 0 : 1;
+  p.interval_mask = (spec.flags & kTableTerms) ? 0 : 1;
   p.status = device_status_ptr();
   BMA_REQUIRE(p.status != nullptr, BMA_ERR_CUDA);
   const bool kb = a.key_bias != nullptr || a.scale < 0.f;

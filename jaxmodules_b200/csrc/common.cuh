@@ -37,6 +37,9 @@ void count_launches(int n);
 
 __device__ __forceinline__ void report_device_error(int* status, int code) { atomicCAS(status, 0, code); }
 
+// Terms of the mask that are looked up (segment ids, bit table, tile bits) rather than computed from the indices.
+constexpr int kTableTerms = BMA_MASK_SEGMENT | BMA_MASK_BITMAP | BMA_MASK_TILES;
+
 // ---- mask predicate --------------------------------------------------------------------
 // Device copy of bma_mask_spec with the per-(b,h) row pointers resolved once per CTA.
 struct MaskView {
@@ -49,6 +52,10 @@ struct MaskView {
   const int32_t* seg_k_row;
   const uint32_t* bitmap_bh;    // &bitmap[((b%BB)*BH + h%BH) * bitmap_q * words]
   int bitmap_words;
+  const uint8_t* tile_class_bh; // TILES: &tile_class[((b%TB)*TH + h%TH) * tiles_q * tiles_k], likewise tile_slot_bh
+  const int32_t* tile_slot_bh;
+  const uint32_t* tile_bits;
+  int tiles_k;
 };
 
 __device__ __forceinline__ MaskView make_mask_view(const bma_mask_spec& s, int b, int h) {
@@ -66,7 +73,25 @@ __device__ __forceinline__ MaskView make_mask_view(const bma_mask_spec& s, int b
     int64_t bh = (int64_t)(b % s.bitmap_B) * s.bitmap_H + (h % s.bitmap_H);
     m.bitmap_bh = s.bitmap + bh * (int64_t)s.bitmap_q * s.bitmap_words;
   }
+  m.tile_class_bh = nullptr; m.tile_slot_bh = nullptr; m.tile_bits = nullptr; m.tiles_k = 0;
+  if (s.flags & BMA_MASK_TILES) {
+    const int64_t bh = ((int64_t)(b % s.tiles_B) * s.tiles_H + (h % s.tiles_H)) * s.tiles_q * s.tiles_k;
+    m.tile_class_bh = s.tile_class + bh;
+    m.tile_slot_bh = s.tile_slot + bh;
+    m.tile_bits = s.tile_bits;
+    m.tiles_k = s.tiles_k;
+  }
   return m;
+}
+
+// TILES term: the 32 keys [gk32, gk32 + 32) (gk32 a multiple of 32) of global query gq as a bit word.
+__device__ __forceinline__ uint32_t tiles_word(const MaskView& m, int gq, int gk32) {
+  const int64_t t = (int64_t)(gq >> 7) * m.tiles_k + (gk32 >> 7);
+  const int c = __ldg(m.tile_class_bh + t);
+  if (c != 1) return c == 2 ? 0xffffffffu : 0u;
+  const int slot = __ldg(m.tile_slot_bh + t);
+  if (slot < 0) return 0u;   // a cut tile that was not stored (the builder ran out of room): nothing is read
+  return __ldg(m.tile_bits + ((int64_t)slot * 128 + (gq & 127)) * 4 + ((gk32 & 127) >> 5));
 }
 
 // First key index and one-past-last key index of the reference's block window for the
@@ -94,6 +119,7 @@ __device__ __forceinline__ bool mask_allowed(const MaskView& m, int q, int k) {
   if ((m.flags & BMA_MASK_SEGMENT) && ok) ok = (__ldg(m.seg_q_row + gq) == __ldg(m.seg_k_row + gk));
   if ((m.flags & BMA_MASK_BITMAP) && ok)
     ok = (__ldg(m.bitmap_bh + (int64_t)gq * m.bitmap_words + (gk >> 5)) >> (gk & 31)) & 1u;
+  if ((m.flags & BMA_MASK_TILES) && ok) ok = (tiles_word(m, gq, gk & ~31) >> (gk & 31)) & 1u;
   return ok;
 }
 
@@ -134,6 +160,12 @@ __device__ __forceinline__ uint32_t table_bits_row32(const MaskView& m, int q, i
     if (sh && word + 1 < m.bitmap_words) v |= __ldg(rowp + word + 1) << (32 - sh);
     w &= v;
   }
+  if (m.flags & BMA_MASK_TILES) {   // keys past k_valid fall outside the interval bits the caller ANDs with
+    const int sh = gk & 31;
+    uint32_t v = tiles_word(m, gq, gk - sh) >> sh;
+    if (sh && ((gk - sh + 32) >> 7) < m.tiles_k) v |= tiles_word(m, gq, gk - sh + 32) << (32 - sh);
+    w &= v;
+  }
   return w;
 }
 
@@ -150,6 +182,11 @@ __device__ __forceinline__ uint32_t table_bits_col32(const MaskView& m, int k, i
     uint32_t v = 0;
     for (int j = 0; j < n; ++j)
       v |= ((__ldg(m.bitmap_bh + (int64_t)(gq + j) * m.bitmap_words + (gk >> 5)) >> (gk & 31)) & 1u) << j;
+    w &= v;
+  }
+  if (m.flags & BMA_MASK_TILES) {   // stored by query row: gathered bit by bit, one tile row at a time
+    uint32_t v = 0;
+    for (int j = 0; j < n; ++j) v |= ((tiles_word(m, gq + j, gk & ~31) >> (gk & 31)) & 1u) << j;
     w &= v;
   }
   return w;

@@ -25,10 +25,11 @@ constexpr int kThreads = 256;
 constexpr int kMaxRowWidth = 16384;  // widest index row kept in shared memory (2 rows * 4 B * width)
 
 __host__ __device__ inline bool depends_on_b(const bma_mask_spec& s) {
-  return (s.flags & BMA_MASK_SEGMENT) || ((s.flags & BMA_MASK_BITMAP) && s.bitmap_B > 1);
+  return (s.flags & BMA_MASK_SEGMENT) || ((s.flags & BMA_MASK_BITMAP) && s.bitmap_B > 1) ||
+         ((s.flags & BMA_MASK_TILES) && s.tiles_B > 1);
 }
 __host__ __device__ inline bool depends_on_h(const bma_mask_spec& s) {
-  return (s.flags & BMA_MASK_BITMAP) && s.bitmap_H > 1;
+  return ((s.flags & BMA_MASK_BITMAP) && s.bitmap_H > 1) || ((s.flags & BMA_MASK_TILES) && s.tiles_H > 1);
 }
 
 struct SegSummary {  // workspace views, each [B, nblocks]
@@ -144,6 +145,22 @@ __global__ void classify_kernel(bma_mask_spec spec, int CB, int CH, int NQ, int 
         }
       }
       if (decided && any && (spec.flags & BMA_MASK_BITMAP)) scan = true;
+      if (decided && any && (spec.flags & BMA_MASK_TILES)) {
+        // a block that IS a stored tile takes the tile's class (exactly, when no other term cuts the block); any other
+        // block geometry is scanned element by element
+        const bool is_tile = QB == 128 && KVB == 128 && (spec.q_offset & 127) == 0 && (spec.k_offset & 127) == 0;
+        if (!is_tile) scan = true;
+        else {
+          const int64_t t = (((int64_t)(c.cb % spec.tiles_B) * spec.tiles_H + (c.ch % spec.tiles_H)) * spec.tiles_q +
+                             ((c.qi * QB + spec.q_offset) >> 7)) * spec.tiles_k + ((c.kj * KVB + spec.k_offset) >> 7);
+          const int tc = spec.tile_class[t];
+          if (tc == 0) { any = false; all = false; }
+          else if (tc == 1) {
+            if (all || (spec.flags & BMA_MASK_COMPILE_CONSERVATIVE)) all = false;   // cut by the tile alone: partial
+            else scan = true;                                                        // cut by two terms: may be empty
+          }
+        }
+      }
       flags[w] = all ? 2 : (any ? 1 : 0);   // rewritten by pass 1b when `scan`
     }
     const unsigned m = __ballot_sync(0xffffffffu, scan);
@@ -308,6 +325,11 @@ int mask_compile_validate(const bma_mask_spec& s, int B, int H, const bma_block_
   if (s.flags & BMA_MASK_SEGMENT) BMA_REQUIRE(s.seg_q && s.seg_k, BMA_ERR_ARG);
   if (s.flags & BMA_MASK_BITMAP)
     BMA_REQUIRE(s.bitmap && s.bitmap_B > 0 && s.bitmap_H > 0 && s.bitmap_words > 0 && s.bitmap_q > 0, BMA_ERR_ARG);
+  if (s.flags & BMA_MASK_TILES) {
+    BMA_REQUIRE(s.tile_class && s.tile_slot && s.tiles_B > 0 && s.tiles_H > 0 && s.tiles_q > 0 && s.tiles_k > 0, BMA_ERR_ARG);
+    BMA_REQUIRE((int64_t)s.tiles_q * 128 >= (int64_t)s.q_valid + s.q_offset && (int64_t)s.tiles_k * 128 >= (int64_t)s.k_valid + s.k_offset,
+                BMA_ERR_ARG);
+  }
   if (s.flags & BMA_MASK_BLOCK_WINDOW)
     BMA_REQUIRE(s.win_block > 0 && s.win_left >= 0 && s.win_right >= 0 && s.win_left + s.win_right <= s.win_nblk,
                 BMA_ERR_ARG);
@@ -343,7 +365,7 @@ int mask_compile_launch(const bma_mask_spec& spec, int B, int H, const bma_block
     const int64_t blocks = (int64_t)p.CB * p.CH * l.NQ * l.NKV;
     const int grid = (int)std::min<int64_t>((blocks + kThreads - 1) / kThreads, (int64_t)sm_count * 16);
     // blocks that closed forms cannot decide exist only with these terms; without them pass 1b is not launched
-    const bool may_scan = (spec.flags & (BMA_MASK_BITMAP | BMA_MASK_BLOCK_WINDOW)) ||
+    const bool may_scan = (spec.flags & (BMA_MASK_BITMAP | BMA_MASK_BLOCK_WINDOW | BMA_MASK_TILES)) ||
                           ((spec.flags & BMA_MASK_SEGMENT) && !(spec.flags & BMA_MASK_COMPILE_CONSERVATIVE));
     if (may_scan) BMA_CUDA_TRY(cudaMemsetAsync(l.kv_num, 0, sizeof(int32_t), st));
     classify_kernel<<<grid, kThreads, 0, st>>>(spec, p.CB, p.CH, l.NQ, l.NKV, l.q_block, l.kv_block, seg, flags, l.kv_idx, l.kv_num);

@@ -90,18 +90,68 @@ __global__ void __launch_bounds__(256) mask_table_kernel(const __grid_constant__
   }
 }
 
-}  // namespace
-}  // namespace bma
+// The TILES form: one CTA of 128 threads per 128 x 128 tile, thread = query row.  Every thread evaluates its row's 128
+// keys into four words; the CTA reduces "some pair allowed" / "every valid pair allowed"; a cut tile takes the next
+// slot from a counter and stores its 2 KB of bits.  Slots are handed out in completion order: they differ from run to
+// run, the predicate they encode does not.
+struct TilesParams {
+  bma_mask_program prog;
+  int32_t B, H, N, L, TQ, TK, q_offset, k_offset, capacity;
+  uint8_t* tile_class;
+  int32_t* tile_slot;
+  uint32_t* tile_bits;
+  int32_t* counter;
+};
 
-extern "C" int bma_mask_table_build(const bma_mask_program* program, int32_t B, int32_t H, int32_t N, int32_t L,
-                                    int32_t q_offset, int32_t k_offset, int32_t* bits, bma_stream_t stream) {
-  using namespace bma;
-  BMA_REQUIRE(program != nullptr && bits != nullptr, BMA_ERR_ARG);
-  BMA_REQUIRE(B > 0 && H > 0 && N > 0 && L > 0, BMA_ERR_ARG);
+__global__ void __launch_bounds__(128) mask_tiles_kernel(const __grid_constant__ TilesParams p) {
+  __shared__ int s_any, s_open, s_slot;
+  const int64_t tiles = (int64_t)p.B * p.H * p.TQ * p.TK;
+  for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+    const int tk = (int)(t % p.TK);
+    int64_t rest = t / p.TK;
+    const int tq = (int)(rest % p.TQ);
+    rest /= p.TQ;
+    const int h = (int)(rest % p.H), b = (int)(rest / p.H);
+    if (threadIdx.x == 0) { s_any = 0; s_open = 0; }
+    __syncthreads();
+    // tile (tq, tk) of the GLOBAL grid holds local rows / keys [tq*128 - q_offset, ...): offsets are multiples of 128
+    const int q = tq * 128 + (int)threadIdx.x - p.q_offset;
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+    bool any = false, open = false;   // open: a valid pair of this row is NOT allowed
+    if (q >= 0 && q < p.N) {
+      for (int j = 0; j < 128; ++j) {
+        const int k = tk * 128 + j - p.k_offset;
+        if (k < 0 || k >= p.L) continue;
+        if (run_program(p.prog, b, h, q + p.q_offset, k + p.k_offset) != 0) { w[j >> 5] |= 1u << (j & 31); any = true; }
+        else open = true;
+      }
+    }
+    if (any) atomicOr(&s_any, 1);
+    if (open) atomicOr(&s_open, 1);
+    __syncthreads();
+    const int cls = !s_any ? 0 : (s_open ? 1 : 2);
+    if (threadIdx.x == 0) {
+      p.tile_class[t] = (uint8_t)cls;
+      int slot = -1;
+      if (cls == 1) slot = atomicAdd(p.counter, 1);
+      p.tile_slot[t] = (slot >= 0 && slot < p.capacity) ? slot : -1;
+      s_slot = slot;
+    }
+    __syncthreads();
+    const int slot = s_slot;
+    if (cls == 1 && slot >= 0 && slot < p.capacity)
+      *reinterpret_cast<uint4*>(p.tile_bits + ((int64_t)slot * 128 + threadIdx.x) * 4) = make_uint4(w[0], w[1], w[2], w[3]);
+    __syncthreads();
+  }
+}
+
+}  // namespace
+
+// every operand must name an earlier value, every table an existing one: checked on the host, once, so that the
+// kernels need no bounds checks of their own
+int validate_program(const bma_mask_program* program) {
   BMA_REQUIRE(program->n_instr >= 1 && program->n_instr <= BMA_PROGRAM_MAX_INSTR, BMA_ERR_ARG);
   BMA_REQUIRE(program->n_tables >= 0 && program->n_tables <= BMA_PROGRAM_MAX_TABLES, BMA_ERR_ARG);
-  // every operand must name an earlier value, every table an existing one: checked here, once,
-  // so that the kernel needs no bounds checks of its own
   for (int i = 0; i < program->n_instr; ++i) {
     const int32_t op = program->code[4 * i], x = program->code[4 * i + 1], y = program->code[4 * i + 2], z = program->code[4 * i + 3];
     const int32_t defined = 4 + i;
@@ -118,6 +168,43 @@ extern "C" int bma_mask_table_build(const bma_mask_program* program, int32_t B, 
     if (op >= BMA_OP_ADD) BMA_REQUIRE(val(y), BMA_ERR_ARG);
     if (op == BMA_OP_SELECT) BMA_REQUIRE(val(z), BMA_ERR_ARG);
   }
+  return BMA_OK;
+}
+
+}  // namespace bma
+
+extern "C" int bma_mask_tiles_build(const bma_mask_program* program, int32_t B, int32_t H, int32_t N, int32_t L,
+                                    int32_t q_offset, int32_t k_offset, uint8_t* tile_class, int32_t* tile_slot,
+                                    uint32_t* tile_bits, int32_t capacity, int32_t* counter, bma_stream_t stream) {
+  using namespace bma;
+  BMA_REQUIRE(program != nullptr && tile_class != nullptr && tile_slot != nullptr && counter != nullptr, BMA_ERR_ARG);
+  BMA_REQUIRE(B > 0 && H > 0 && N > 0 && L > 0 && capacity >= 0 && (capacity == 0 || tile_bits != nullptr), BMA_ERR_ARG);
+  BMA_REQUIRE(q_offset >= 0 && k_offset >= 0 && q_offset % 128 == 0 && k_offset % 128 == 0, BMA_ERR_ARG);
+  int rc = validate_program(program);
+  if (rc != BMA_OK) return rc;
+  TilesParams p;
+  p.prog = *program;
+  p.B = B; p.H = H; p.N = N; p.L = L;
+  p.TQ = (N + q_offset + 127) / 128; p.TK = (L + k_offset + 127) / 128;
+  p.q_offset = q_offset; p.k_offset = k_offset; p.capacity = capacity;
+  p.tile_class = tile_class; p.tile_slot = tile_slot; p.tile_bits = tile_bits; p.counter = counter;
+  const int64_t tiles = (int64_t)B * H * p.TQ * p.TK;
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = (int)(tiles < (int64_t)sms * 16 ? tiles : (int64_t)sms * 16);
+  mask_tiles_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  count_launches(1);
+  BMA_CUDA_TRY(cudaGetLastError());
+  return BMA_OK;
+}
+
+extern "C" int bma_mask_table_build(const bma_mask_program* program, int32_t B, int32_t H, int32_t N, int32_t L,
+                                    int32_t q_offset, int32_t k_offset, int32_t* bits, bma_stream_t stream) {
+  using namespace bma;
+  BMA_REQUIRE(program != nullptr && bits != nullptr, BMA_ERR_ARG);
+  BMA_REQUIRE(B > 0 && H > 0 && N > 0 && L > 0, BMA_ERR_ARG);
+  int rc = validate_program(program);
+  if (rc != BMA_OK) return rc;
   TableParams p;
   p.prog = *program;
   p.B = B; p.H = H; p.N = N; p.L = L; p.words = (L + 31) / 32;

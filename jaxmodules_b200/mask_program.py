@@ -276,13 +276,10 @@ def run_on_host(prog: Program, b, h, q, k):
     return v[-1] != 0
 
 
-def build_table(prog: Program, B: int, H: int, N: int, L: int, device, q_offset: int = 0, k_offset: int = 0) -> torch.Tensor:
-    """``bma_mask_table_build``: the program evaluated over the box, packed into the bit table
-    ``[Bm, Hm, N, ceil(L/32)]`` int32 on ``device`` (Bm / Hm are 1 when b / h are not read)."""
+def _c_program(prog: Program, device):
+    """(bma_mask_program struct, device tensors it points at)."""
     if not prog.code:
         raise ValueError("empty program")
-    Bm, Hm = (B if prog.uses_b else 1), (H if prog.uses_h else 1)
-    words = (L + 31) // 32
     c = nat.MaskProgram()
     c.n_instr, c.n_tables = len(prog.code), len(prog.tables)
     flat = [w for ins in prog.code for w in ins]
@@ -295,9 +292,44 @@ def build_table(prog: Program, B: int, H: int, N: int, L: int, device, q_offset:
         c.table_rows[i] = dt.shape[0] if dt.ndim == 2 else 1
         c.table_cols[i] = dt.shape[-1]
         c.table_stride[i] = dt.stride(0) if dt.ndim == 2 else 0
+    return c, keep
+
+
+def build_table(prog: Program, B: int, H: int, N: int, L: int, device, q_offset: int = 0, k_offset: int = 0) -> torch.Tensor:
+    """``bma_mask_table_build``: the program evaluated over the box, packed into the bit table
+    ``[Bm, Hm, N, ceil(L/32)]`` int32 on ``device`` (Bm / Hm are 1 when b / h are not read)."""
+    Bm, Hm = (B if prog.uses_b else 1), (H if prog.uses_h else 1)
+    words = (L + 31) // 32
+    c, keep = _c_program(prog, device)
     bits = torch.empty((Bm, Hm, N, words), dtype=torch.int32, device=device)
     with torch.cuda.device(device):
         nat.check(nat.lib().bma_mask_table_build(C.byref(c), Bm, Hm, N, L, q_offset, k_offset, bits.data_ptr(),
                                                  torch.cuda.current_stream(device).cuda_stream), "bma_mask_table_build")
     bits._bma_keep = keep   # the tables must outlive the launch
     return bits
+
+
+def build_tiles(prog: Program, B: int, H: int, N: int, L: int, device):
+    """``bma_mask_tiles_build``: the program evaluated over the box into the TILES form of the mask description —
+    (tile_class uint8 ``[Bm, Hm, TQ, TK]``, tile_slot int32 of the same shape, tile_bits int32 ``[cut tiles, 128, 4]``).
+    Memory grows with the tiles the mask cuts (2 KB each), not with N * L.  Two passes: the first only counts the cut
+    tiles (one host synchronisation, once per mask), the second stores them."""
+    Bm, Hm = (B if prog.uses_b else 1), (H if prog.uses_h else 1)
+    TQ, TK = (N + 127) // 128, (L + 127) // 128
+    c, keep = _c_program(prog, device)
+    cls = torch.empty((Bm, Hm, TQ, TK), dtype=torch.uint8, device=device)
+    slot = torch.empty((Bm, Hm, TQ, TK), dtype=torch.int32, device=device)
+    counter = torch.zeros((1,), dtype=torch.int32, device=device)
+    lib = nat.lib()
+    with torch.cuda.device(device):
+        st = torch.cuda.current_stream(device).cuda_stream
+        nat.check(lib.bma_mask_tiles_build(C.byref(c), Bm, Hm, N, L, 0, 0, cls.data_ptr(), slot.data_ptr(), None, 0,
+                                           counter.data_ptr(), st), "bma_mask_tiles_build")
+        cut = int(counter.item())
+        bits = torch.empty((max(cut, 1), 128, 4), dtype=torch.int32, device=device)
+        if cut:
+            counter.zero_()
+            nat.check(lib.bma_mask_tiles_build(C.byref(c), Bm, Hm, N, L, 0, 0, cls.data_ptr(), slot.data_ptr(), bits.data_ptr(),
+                                               cut, counter.data_ptr(), st), "bma_mask_tiles_build")
+    bits._bma_keep = keep   # the program's tables must outlive the launch
+    return cls, slot, bits

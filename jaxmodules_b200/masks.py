@@ -36,6 +36,7 @@ class MaskTerms:
     seg_k: Optional[torch.Tensor] = None             # [B, >=L] int32
     window: Optional[Tuple[int, int, int, int]] = None   # (block, left_blocks, right_blocks, num_kv_blocks)
     bitmap: Optional[torch.Tensor] = None            # [Bm, Hm, Q, words] int32 (bit pattern of uint32)
+    tiles: Optional[tuple] = None                    # (tile_class uint8 [Bm,Hm,TQ,TK], tile_slot int32, tile_bits int32 [cut,128,4])
     q_offset: int = 0
     k_offset: int = 0
 
@@ -45,7 +46,7 @@ class MaskTerms:
             band = other.band if band is None else (min(band[0], other.band[0]), min(band[1], other.band[1]))
         if self.seg_q is not None and other.seg_q is not None:
             raise NotImplementedError("and_masks: only one document_mask term is supported")
-        if self.bitmap is not None and other.bitmap is not None:
+        if (self.bitmap is not None and other.bitmap is not None) or (self.tiles is not None and other.tiles is not None):
             raise NotImplementedError("and_masks: only one table-backed term is supported")
         return MaskTerms(
             causal=self.causal or other.causal, band=band,
@@ -53,6 +54,7 @@ class MaskTerms:
             seg_k=self.seg_k if self.seg_k is not None else other.seg_k,
             window=self.window or other.window,
             bitmap=self.bitmap if self.bitmap is not None else other.bitmap,
+            tiles=self.tiles if self.tiles is not None else other.tiles,
             q_offset=self.q_offset or other.q_offset, k_offset=self.k_offset or other.k_offset)
 
 
@@ -236,24 +238,41 @@ def to_device_mask(terms: MaskTerms, N: int, L: int, device) -> DeviceMask:
         s.bitmap_B, s.bitmap_H, s.bitmap_q, s.bitmap_words = bm.shape
         depends_b = depends_b or bm.shape[0] > 1
         depends_h = bm.shape[1] > 1
+    if terms.tiles is not None:
+        flags |= nat.BMA_MASK_TILES
+        cls, slot, bits = (_on_device(t, device) for t in terms.tiles)
+        if cls.shape[2] * 128 < N + terms.q_offset or cls.shape[3] * 128 < L + terms.k_offset:
+            raise ValueError("the mask's tile grid is smaller than the sequences")
+        keep += [cls, slot, bits]
+        s.tile_class, s.tile_slot, s.tile_bits = cls.data_ptr(), slot.data_ptr(), bits.data_ptr()
+        s.tiles_B, s.tiles_H, s.tiles_q, s.tiles_k = cls.shape
+        depends_b = depends_b or cls.shape[0] > 1
+        depends_h = depends_h or cls.shape[1] > 1
     s.flags = flags
     return DeviceMask(spec=s, keep=tuple(keep), depends_b=depends_b, depends_h=depends_h)
 
 
-def _table_from_program(mask_fn, nargs: int, B: int, Hq: int, N: int, L: int, device) -> Optional[torch.Tensor]:
-    """The bit table of ``mask_fn`` built on the GPU from its traced program, or None when the
-    function cannot be traced (it is then evaluated on the host)."""
+# A traced mask_fn whose dense table would be larger than this many bits is stored in the TILES form instead (2 KB per
+# 128 x 128 tile that the mask cuts; whole and empty tiles cost a byte): 2^26 bits = 8 MiB of table.
+TILES_ABOVE_BITS = 1 << 26
+
+
+def _table_from_program(mask_fn, nargs: int, B: int, Hq: int, N: int, L: int, device):
+    """``mask_fn`` evaluated on the GPU from its traced program: MaskTerms with the dense bit table (small masks) or
+    with the tile form (large ones), or None when the function cannot be traced (it is then evaluated on the host)."""
     from . import mask_program as mp
     try:
         prog = mp.trace(mask_fn, nargs)
     except mp.TraceError:
         return None
     Bm, Hm = (B if prog.uses_b else 1), (Hq if prog.uses_h else 1)
+    if Bm * Hm * N * L > TILES_ABOVE_BITS:
+        return MaskTerms(tiles=mp.build_tiles(prog, B, Hq, N, L, device))
     if Bm * Hm * N * L > MAX_BITMAP_BITS:
         raise NotImplementedError(
             "the bit table of this mask_fn would exceed 2 GiB; build the mask with "
             "jaxmodules_b200.masks (causal_mask, sliding_window_mask, document_mask, and_masks)")
-    return mp.build_table(prog, B, Hq, N, L, device)
+    return MaskTerms(bitmap=mp.build_table(prog, B, Hq, N, L, device))
 
 
 # Bit tables already built for a callable: function object -> {(B, Hq, N, L, device): MaskTerms}.  The reference
@@ -300,9 +319,9 @@ def terms_from_mask_fn(mask_fn, B: int, Hq: int, N: int, L: int, device=None) ->
 def _build_terms_from_callable(mask_fn, B: int, Hq: int, N: int, L: int, device=None) -> MaskTerms:
     n = argcount(mask_fn)
     if n in (3, 4) and device is not None and torch.device(device).type == "cuda":
-        bits = _table_from_program(mask_fn, n, B, Hq, N, L, device)
-        if bits is not None:
-            return MaskTerms(bitmap=bits)
+        terms = _table_from_program(mask_fn, n, B, Hq, N, L, device)
+        if terms is not None:
+            return terms
     if n == 3:
         fn = lambda b, h, q, k: mask_fn(h, q, k)
         return MaskTerms(bitmap=bitmap_from_callable(fn, B, Hq, N, L, batch_dependent=False))

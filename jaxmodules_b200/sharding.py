@@ -120,7 +120,7 @@ def ring_schedule(rank: int, world: int) -> List[int]:
 
 def _step_terms(terms: _masks.MaskTerms, q_offset: int, k_offset: int) -> _masks.MaskTerms:
     return _masks.MaskTerms(causal=terms.causal, band=terms.band, seg_q=terms.seg_q, seg_k=terms.seg_k,
-                            window=terms.window, bitmap=terms.bitmap, q_offset=terms.q_offset + q_offset,
+                            window=terms.window, bitmap=terms.bitmap, tiles=terms.tiles, q_offset=terms.q_offset + q_offset,
                             k_offset=terms.k_offset + k_offset)
 
 

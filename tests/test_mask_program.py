@@ -147,3 +147,95 @@ def test_traced_masks_drive_block_mask_and_attention():
         out = jm.masked_attention_via_map(Q.cuda(), K.cuda(), V.cuda(), mask_fn=fn)
         want = ao.masked_attention_dense(Q.numpy(), K.numpy(), V.numpy(), mask_fn=fn)["O"]
         assert np.abs(out.cpu().numpy() - want).max() < 1e-4
+
+
+def _tiles_to_dense(cls, slot, bits, N, L):
+    """Expands the tile form back into a dense bool array [Bm, Hm, N, L] on the host."""
+    cls, slot, bits = cls.cpu().numpy(), slot.cpu().numpy(), bits.cpu().numpy().view(np.uint32)
+    Bm, Hm, TQ, TK = cls.shape
+    out = np.zeros((Bm, Hm, TQ * 128, TK * 128), dtype=bool)
+    for b, h, tq, tk in np.ndindex(Bm, Hm, TQ, TK):
+        c = cls[b, h, tq, tk]
+        if c == 2:
+            out[b, h, tq * 128:(tq + 1) * 128, tk * 128:(tk + 1) * 128] = True
+        elif c == 1:
+            words = bits[slot[b, h, tq, tk]]                       # [128, 4]
+            tile = np.unpackbits(words.view(np.uint8).reshape(128, 16), axis=-1, bitorder="little").astype(bool)
+            out[b, h, tq * 128:(tq + 1) * 128, tk * 128:(tk + 1) * 128] = tile
+    return out[:, :, :N, :L]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fn", [batch_sliding_window, complex_batch, causal, alternating, documents], ids=lambda f: f.__name__)
+def test_device_tiles_are_bit_exact(fn):
+    """The TILES form of a traced mask: classes and bits equal the function over the index grid; whole and empty tiles
+    carry no bits; ragged edges are class 2 when every VALID pair is allowed."""
+    B, H, N, L = 2, 3, 300, 40 if fn is documents else 421
+    if fn is documents:
+        N = 40
+    prog = P.trace(fn)
+    cls, slot, bits = P.build_tiles(prog, B, H, N, L, "cuda")
+    Bm, Hm = (B if prog.uses_b else 1), (H if prog.uses_h else 1)
+    want = grid(fn, Bm, Hm, N, L)
+    got = _tiles_to_dense(cls, slot, bits, N, L)
+    # a class-2 tile at a ragged edge claims "allowed" outside the box too: compare inside the box only
+    assert np.array_equal(got, want)
+    cut = int((cls == 1).sum())
+    assert bits.shape[0] == max(cut, 1) and sorted(slot[cls == 1].cpu().tolist()) == list(range(cut))
+    if fn is causal:                     # 3 x 4 tiles: the diagonal ones are cut, above it empty, below it whole
+        c = cls[0, 0].cpu().numpy()
+        assert (c == np.array([[1, 0, 0, 0], [2, 1, 0, 0], [2, 2, 1, 0]])).all()
+
+
+@pytest.mark.gpu
+def test_traced_mask_takes_the_tile_form_and_matches_the_table(monkeypatch):
+    """The same traced, batch- and head-dependent mask through the dense bit table and through the tile form: identical
+    block lists (exact and conservative), identical attention results on both backends, bf16 gradients included."""
+    from oracle import attention_oracle as ao
+    fn = lambda b, h, q, k: (abs(q - k) <= 40 * (b + 1) + 17 * h) & ((q + k) % (h + 2) != 0)
+    B, H, N, d = 2, 2, 640, 128
+    assert M.terms_from_mask_fn(fn, B, H, N, N, device="cuda").bitmap is not None
+    table_bm = jm.create_block_mask(fn, B, H, N, N, 64)
+    M.clear_mask_cache()
+    monkeypatch.setattr(M, "TILES_ABOVE_BITS", 0)
+    terms = M.terms_from_mask_fn(fn, B, H, N, N, device="cuda")
+    assert terms.tiles is not None and terms.bitmap is None
+    tiles_bm = jm.create_block_mask(fn, B, H, N, N, 64)          # 64-blocks: two per tile edge, scanned from the tile bits
+    for f in ("kv_num_blocks", "kv_indices", "full_kv_num_blocks", "full_kv_indices", "q_num_blocks", "q_indices", "full_q_indices"):
+        assert torch.equal(getattr(tiles_bm, f), getattr(table_bm, f)), f
+    g = torch.Generator().manual_seed(0)
+    Q, K, V = (torch.randn(B, N, H, d, generator=g).to(torch.bfloat16) for _ in range(3))
+    dO = torch.randn(B, N, H, d, generator=g)
+    ref = ao.masked_attention_dense(Q.float().numpy(), K.float().numpy(), V.float().numpy(), mask_fn=fn, dO=dO.numpy())
+    for backend in (nat.BMA_BACKEND_AUTO, nat.BMA_BACKEND_SIMT):
+        q, k, v = (t.cuda().requires_grad_(True) for t in (Q, K, V))
+        out = jm.masked_attention_via_map(q, k, v, mask_fn=fn, backend=backend)
+        out.backward(dO.cuda())
+        for name, got in (("O", out), ("dQ", q.grad), ("dK", k.grad), ("dV", v.grad)):
+            err = np.abs(got.detach().float().cpu().numpy() - ref[name])
+            assert (err / np.maximum(1.0, np.abs(ref[name]))).max() <= 2e-2 and err.mean() <= 2e-3, (backend, name, err.max())
+    M.clear_mask_cache()
+
+
+@pytest.mark.gpu
+def test_batch_head_dependent_mask_at_16k_without_a_table():
+    """L = 16384 with a mask that depends on batch and head (tests/test_mapped_attention.py:1249-1307 at scale): the
+    dense table would be 2 x 2 x 16384^2 bits = 128 MiB; the tile form stores the ~130 cut tiles per (b, h) (1 MB in all).
+    Checked on sampled query rows against a dense float32 computation over all keys."""
+    B, H, L, d = 2, 2, 16384, 128
+    fn = lambda b, h, q, k: (k <= q) & (q - k <= 1000 * (b + 1) + 300 * h)
+    M.clear_mask_cache()
+    terms = M.terms_from_mask_fn(fn, B, H, L, L, device="cuda")
+    assert terms.tiles is not None and terms.tiles[2].numel() * 4 < 8 << 20
+    g = torch.Generator(device="cuda").manual_seed(2)
+    Q, K, V = (torch.randn(B, L, H, d, device="cuda", generator=g).to(torch.bfloat16) for _ in range(3))
+    O = jm.masked_attention_via_map(Q, K, V, mask_fn=fn)
+    rows = torch.tensor([0, 1, 127, 128, 1500, 5000, 9999, 16383], device="cuda")
+    ki = torch.arange(L, device="cuda")[None, :]
+    for b in range(B):
+        for h in range(H):
+            s = (Q[b, rows, h].float() @ K[b, :, h].float().T) / d ** 0.5
+            allowed = (ki <= rows[:, None]) & (rows[:, None] - ki <= 1000 * (b + 1) + 300 * h)
+            p = torch.softmax(s.masked_fill(~allowed, float("-inf")), dim=-1)
+            assert float((O[b, rows, h] - p @ V[b, :, h].float()).abs().max()) <= 2e-2
+    M.clear_mask_cache()
