@@ -384,7 +384,7 @@ def measure_config(name, dev, steps=5, warmup=3, seed=100, traced=False):
     tf = lambda fl, t: fl / (t * 1e-3) / 1e12 if t else None
     if traced:
         t = terms.tiles if terms.tiles is not None else None
-        w = dict(w, desc=w["desc"] + ", mask as a traced Python lambda (" + ("tile form: %d cut tiles of 2 KB" % t[2].shape[0] if t else "dense bit table") + ")")
+        w = dict(w, desc=w["desc"] + ", mask as a traced Python lambda (" + ("tile form: %d cut tiles of 4 KB" % t[2].shape[0] if t else "dense bit table") + ")")
     out = {"workload": w["desc"], "backend": {1: "simt", 2: "tcgen05"}.get(be, str(be)), "steps": steps, "warmup": warmup,
            "nonempty_blocks": blocks, "ms_per_step": ms, "value": tf(step_flops, ms), "fwd_tflops": tf(fwd_flops, per.get("fwd")),
            "bwd_tflops": tf(step_flops - fwd_flops, per.get("bwd")), "kernel_ms": per, "status": A.device_status(dev)}

@@ -62,7 +62,9 @@ enum { BMA_DTYPE_F32 = 0, BMA_DTYPE_BF16 = 1 };
  *                 memory grows with the tiles the mask CUTS, not with N*L (bma_mask_tiles_build makes it from a mask
  *                 program).  t = ((b%tiles_B)*tiles_H + h%tiles_H)*tiles_q + gq/128)*tiles_k + gk/128:
  *                 tile_class[t] = 0 no pair of the tile is allowed, 2 every pair is, 1 some are -- and then bit (gk & 31)
- *                 of tile_bits[(tile_slot[t]*128 + gq%128)*4 + (gk%128)/32] decides.
+ *                 of tile_bits[(tile_slot[t]*256 + gq%128)*4 + (gk%128)/32] decides.  A cut tile is stored twice, by
+ *                 query row and (second 2 KB) by key row -- bit (gq & 31) of
+ *                 tile_bits[(tile_slot[t]*256 + 128 + gk%128)*4 + (gq%128)/32] -- for the kernels that walk keys.
  */
 enum {
   BMA_MASK_CAUSAL = 1,
@@ -94,7 +96,7 @@ typedef struct bma_mask_spec {
   int32_t tiles_B, tiles_H, tiles_q, tiles_k; /* TILES: extents of the tile grid (tiles_q = ceil(rows / 128) ...) */
   const uint8_t* tile_class;                   /* [tiles_B, tiles_H, tiles_q, tiles_k]            */
   const int32_t* tile_slot;                    /* same shape; meaningful where tile_class == 1     */
-  const uint32_t* tile_bits;                   /* [slots, 128, 4]                                  */
+  const uint32_t* tile_bits;                   /* [slots, 2, 128, 4]: by query row, by key row     */
 } bma_mask_spec;
 
 /* ---- block lists ---------------------------------------------------------------------
@@ -239,7 +241,7 @@ int bma_mask_table_build(const bma_mask_program* program, int32_t B, int32_t H, 
 /* The same evaluation into the TILES form of the mask description: classifies every 128 x 128 tile of the
  * [B, H, N, L] box (global indices q + q_offset, k + k_offset must be tile-aligned: both offsets multiples of 128)
  * and stores the bits of the tiles that are cut.  tile_class / tile_slot: [B, H, ceil(N/128), ceil(L/128)];
- * tile_bits: room for `capacity` tiles of 2 KB (may be NULL with capacity 0 to count only); *counter (device int32,
+ * tile_bits: room for `capacity` tiles of 4 KB (may be NULL with capacity 0 to count only); *counter (device int32,
  * zeroed by the caller) receives the number of cut tiles -- when it exceeds `capacity` the surplus tiles were not
  * stored and the call has to be repeated with more room.  Elements outside N x L count as not allowed in the bits
  * and are ignored by the class.  B or H may be 1 when the program does not read that index. */

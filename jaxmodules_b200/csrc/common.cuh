@@ -91,7 +91,16 @@ __device__ __forceinline__ uint32_t tiles_word(const MaskView& m, int gq, int gk
   if (c != 1) return c == 2 ? 0xffffffffu : 0u;
   const int slot = __ldg(m.tile_slot_bh + t);
   if (slot < 0) return 0u;   // a cut tile that was not stored (the builder ran out of room): nothing is read
-  return __ldg(m.tile_bits + ((int64_t)slot * 128 + (gq & 127)) * 4 + ((gk32 & 127) >> 5));
+  return __ldg(m.tile_bits + ((int64_t)slot * 256 + (gq & 127)) * 4 + ((gk32 & 127) >> 5));
+}
+// The transposed copy: the 32 queries [gq32, gq32 + 32) (gq32 a multiple of 32) of global key gk.
+__device__ __forceinline__ uint32_t tiles_word_t(const MaskView& m, int gk, int gq32) {
+  const int64_t t = (int64_t)(gq32 >> 7) * m.tiles_k + (gk >> 7);
+  const int c = __ldg(m.tile_class_bh + t);
+  if (c != 1) return c == 2 ? 0xffffffffu : 0u;
+  const int slot = __ldg(m.tile_slot_bh + t);
+  if (slot < 0) return 0u;
+  return __ldg(m.tile_bits + ((int64_t)slot * 256 + 128 + (gk & 127)) * 4 + ((gq32 & 127) >> 5));
 }
 
 // First key index and one-past-last key index of the reference's block window for the
@@ -184,10 +193,11 @@ __device__ __forceinline__ uint32_t table_bits_col32(const MaskView& m, int k, i
       v |= ((__ldg(m.bitmap_bh + (int64_t)(gq + j) * m.bitmap_words + (gk >> 5)) >> (gk & 31)) & 1u) << j;
     w &= v;
   }
-  if (m.flags & BMA_MASK_TILES) {   // stored by query row: gathered bit by bit, one tile row at a time
-    uint32_t v = 0;
-    for (int j = 0; j < n; ++j) v |= ((tiles_word(m, gq + j, gk & ~31) >> (gk & 31)) & 1u) << j;
-    w &= v;
+  if (m.flags & BMA_MASK_TILES) {   // every cut tile is stored by key row as well: one word per 32 queries
+    const int sh = gq & 31;
+    uint32_t v = tiles_word_t(m, gk, gq - sh) >> sh;
+    if (sh && n > 32 - sh) v |= tiles_word_t(m, gk, gq - sh + 32) << (32 - sh);
+    w &= v;             // queries past q_valid fall outside the interval bits the caller ANDs with
   }
   return w;
 }

@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(256) mask_table_kernel(const __grid_constant__
 
 // The TILES form: one CTA of 128 threads per 128 x 128 tile, thread = query row.  Every thread evaluates its row's 128
 // keys into four words; the CTA reduces "some pair allowed" / "every valid pair allowed"; a cut tile takes the next
-// slot from a counter and stores its 2 KB of bits.  Slots are handed out in completion order: they differ from run to
+// slot from a counter and stores its bits twice, by query row and by key row (4 KB).  Slots are handed out in completion order: they differ from run to
 // run, the predicate they encode does not.
 struct TilesParams {
   bma_mask_program prog;
@@ -105,6 +105,8 @@ struct TilesParams {
 
 __global__ void __launch_bounds__(128) mask_tiles_kernel(const __grid_constant__ TilesParams p) {
   __shared__ int s_any, s_open, s_slot;
+  __shared__ uint32_t s_cols[128][4];   // the tile by key row: word w of key j = the ballot of warp w (query rows 32w ..)
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t tiles = (int64_t)p.B * p.H * p.TQ * p.TK;
   for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
     const int tk = (int)(t % p.TK);
@@ -116,15 +118,17 @@ __global__ void __launch_bounds__(128) mask_tiles_kernel(const __grid_constant__
     __syncthreads();
     // tile (tq, tk) of the GLOBAL grid holds local rows / keys [tq*128 - q_offset, ...): offsets are multiples of 128
     const int q = tq * 128 + (int)threadIdx.x - p.q_offset;
+    const bool row_valid = q >= 0 && q < p.N;
     uint32_t w[4] = {0u, 0u, 0u, 0u};
     bool any = false, open = false;   // open: a valid pair of this row is NOT allowed
-    if (q >= 0 && q < p.N) {
-      for (int j = 0; j < 128; ++j) {
-        const int k = tk * 128 + j - p.k_offset;
-        if (k < 0 || k >= p.L) continue;
-        if (run_program(p.prog, b, h, q + p.q_offset, k + p.k_offset) != 0) { w[j >> 5] |= 1u << (j & 31); any = true; }
-        else open = true;
-      }
+    for (int j = 0; j < 128; ++j) {   // the whole warp walks the keys together: the ballot is the key's column word
+      const int k = tk * 128 + j - p.k_offset;
+      const bool valid = row_valid && k >= 0 && k < p.L;
+      const bool ok = valid && run_program(p.prog, b, h, q + p.q_offset, k + p.k_offset) != 0;
+      if (ok) { w[j >> 5] |= 1u << (j & 31); any = true; }
+      else if (valid) open = true;
+      const uint32_t col = __ballot_sync(0xffffffffu, ok);
+      if (lane == 0) s_cols[j][warp] = col;
     }
     if (any) atomicOr(&s_any, 1);
     if (open) atomicOr(&s_open, 1);
@@ -139,8 +143,12 @@ __global__ void __launch_bounds__(128) mask_tiles_kernel(const __grid_constant__
     }
     __syncthreads();
     const int slot = s_slot;
-    if (cls == 1 && slot >= 0 && slot < p.capacity)
-      *reinterpret_cast<uint4*>(p.tile_bits + ((int64_t)slot * 128 + threadIdx.x) * 4) = make_uint4(w[0], w[1], w[2], w[3]);
+    if (cls == 1 && slot >= 0 && slot < p.capacity) {
+      uint32_t* out = p.tile_bits + (int64_t)slot * 256 * 4;
+      *reinterpret_cast<uint4*>(out + threadIdx.x * 4) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(out + (128 + threadIdx.x) * 4) =
+          make_uint4(s_cols[threadIdx.x][0], s_cols[threadIdx.x][1], s_cols[threadIdx.x][2], s_cols[threadIdx.x][3]);
+    }
     __syncthreads();
   }
 }

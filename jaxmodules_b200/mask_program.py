@@ -311,8 +311,8 @@ def build_table(prog: Program, B: int, H: int, N: int, L: int, device, q_offset:
 
 def build_tiles(prog: Program, B: int, H: int, N: int, L: int, device):
     """``bma_mask_tiles_build``: the program evaluated over the box into the TILES form of the mask description —
-    (tile_class uint8 ``[Bm, Hm, TQ, TK]``, tile_slot int32 of the same shape, tile_bits int32 ``[cut tiles, 128, 4]``).
-    Memory grows with the tiles the mask cuts (2 KB each), not with N * L.  Two passes: the first only counts the cut
+    (tile_class uint8 ``[Bm, Hm, TQ, TK]``, tile_slot int32 of the same shape, tile_bits int32 ``[cut tiles, 2, 128, 4]``:
+    every cut tile by query row and by key row).  Memory grows with the tiles the mask cuts (4 KB each), not with N * L.  Two passes: the first only counts the cut
     tiles (one host synchronisation, once per mask), the second stores them."""
     Bm, Hm = (B if prog.uses_b else 1), (H if prog.uses_h else 1)
     TQ, TK = (N + 127) // 128, (L + 127) // 128
@@ -326,7 +326,7 @@ def build_tiles(prog: Program, B: int, H: int, N: int, L: int, device):
         nat.check(lib.bma_mask_tiles_build(C.byref(c), Bm, Hm, N, L, 0, 0, cls.data_ptr(), slot.data_ptr(), None, 0,
                                            counter.data_ptr(), st), "bma_mask_tiles_build")
         cut = int(counter.item())
-        bits = torch.empty((max(cut, 1), 128, 4), dtype=torch.int32, device=device)
+        bits = torch.empty((max(cut, 1), 2, 128, 4), dtype=torch.int32, device=device)
         if cut:
             counter.zero_()
             nat.check(lib.bma_mask_tiles_build(C.byref(c), Bm, Hm, N, L, 0, 0, cls.data_ptr(), slot.data_ptr(), bits.data_ptr(),

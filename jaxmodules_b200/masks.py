@@ -36,7 +36,7 @@ class MaskTerms:
     seg_k: Optional[torch.Tensor] = None             # [B, >=L] int32
     window: Optional[Tuple[int, int, int, int]] = None   # (block, left_blocks, right_blocks, num_kv_blocks)
     bitmap: Optional[torch.Tensor] = None            # [Bm, Hm, Q, words] int32 (bit pattern of uint32)
-    tiles: Optional[tuple] = None                    # (tile_class uint8 [Bm,Hm,TQ,TK], tile_slot int32, tile_bits int32 [cut,128,4])
+    tiles: Optional[tuple] = None                    # (tile_class uint8 [Bm,Hm,TQ,TK], tile_slot int32, tile_bits int32 [cut,2,128,4])
     q_offset: int = 0
     k_offset: int = 0
 
@@ -252,7 +252,7 @@ def to_device_mask(terms: MaskTerms, N: int, L: int, device) -> DeviceMask:
     return DeviceMask(spec=s, keep=tuple(keep), depends_b=depends_b, depends_h=depends_h)
 
 
-# A traced mask_fn whose dense table would be larger than this many bits is stored in the TILES form instead (2 KB per
+# A traced mask_fn whose dense table would be larger than this many bits is stored in the TILES form instead (4 KB per
 # 128 x 128 tile that the mask cuts; whole and empty tiles cost a byte): 2^26 bits = 8 MiB of table.
 TILES_ABOVE_BITS = 1 << 26
 
@@ -266,7 +266,7 @@ def _table_from_program(mask_fn, nargs: int, B: int, Hq: int, N: int, L: int, de
     except mp.TraceError:
         return None
     Bm, Hm = (B if prog.uses_b else 1), (Hq if prog.uses_h else 1)
-    if Bm * Hm * N * L > TILES_ABOVE_BITS:
+    if Bm * Hm * N * L >= TILES_ABOVE_BITS:
         return MaskTerms(tiles=mp.build_tiles(prog, B, Hq, N, L, device))
     if Bm * Hm * N * L > MAX_BITMAP_BITS:
         raise NotImplementedError(

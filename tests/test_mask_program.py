@@ -159,8 +159,10 @@ def _tiles_to_dense(cls, slot, bits, N, L):
         if c == 2:
             out[b, h, tq * 128:(tq + 1) * 128, tk * 128:(tk + 1) * 128] = True
         elif c == 1:
-            words = bits[slot[b, h, tq, tk]]                       # [128, 4]
-            tile = np.unpackbits(words.view(np.uint8).reshape(128, 16), axis=-1, bitorder="little").astype(bool)
+            words = bits[slot[b, h, tq, tk]]                       # [2, 128, 4]: by query row, by key row
+            tile = np.unpackbits(words[0].view(np.uint8).reshape(128, 16), axis=-1, bitorder="little").astype(bool)
+            by_key = np.unpackbits(words[1].view(np.uint8).reshape(128, 16), axis=-1, bitorder="little").astype(bool)
+            assert np.array_equal(by_key, tile.T)                 # the transposed copy the kv-major kernel reads
             out[b, h, tq * 128:(tq + 1) * 128, tk * 128:(tk + 1) * 128] = tile
     return out[:, :, :N, :L]
 
