@@ -385,7 +385,10 @@ def measure_config(name, dev, steps=5, warmup=3, seed=100, traced=False):
     if traced:
         t = terms.tiles if terms.tiles is not None else None
         w = dict(w, desc=w["desc"] + ", mask as a traced Python lambda (" + ("tile form: %d cut tiles of 4 KB" % t[2].shape[0] if t else "dense bit table") + ")")
-    out = {"workload": w["desc"], "backend": {1: "simt", 2: "tcgen05"}.get(be, str(be)), "steps": steps, "warmup": warmup,
+    in_bytes = 3 * B * L * H * d * Q.element_size() + dO.numel() * 4
+    out = {"l2": ("inputs (%.0f MB) exceed the 126 MB L2; no flush needed" % (in_bytes / 1e6)) if in_bytes > 126e6 else
+                 ("inputs (%.2f MB) fit in L2 and are not flushed: a latency figure, not a bandwidth one" % (in_bytes / 1e6)),
+           "workload": w["desc"], "backend": {1: "simt", 2: "tcgen05"}.get(be, str(be)), "steps": steps, "warmup": warmup,
            "nonempty_blocks": blocks, "ms_per_step": ms, "value": tf(step_flops, ms), "fwd_tflops": tf(fwd_flops, per.get("fwd")),
            "bwd_tflops": tf(step_flops - fwd_flops, per.get("bwd")), "kernel_ms": per, "status": A.device_status(dev)}
     if be == 2:
@@ -426,7 +429,7 @@ def block_mask_build_entry(w, dev, steps, warmup):
     torch.cuda.empty_cache()
     return {"workload": "create_block_mask, " + w["desc"], "ms": ms, "list_bytes_per_build": out_bytes, "GB/s": gbs,
             "frac_of_hbm": gbs / hbm, "peak": hbm, "peak_kind": peak_kind,
-            "kernels": "classify_kernel + compact_kernel<0> + compact_kernel<1>"}
+            "kernels": "classify_kernel + compact_both_kernel"}
 
 
 def c5_head_shards(rank, world, dev, dist, steps=3, warmup=2):

@@ -207,9 +207,9 @@ __global__ void scan_kernel(bma_mask_spec spec, int CH, int NQ, int NKV, int QB,
 // pass 2: one CTA per (classification row, replica chunk).  TRANSPOSED = q-side lists.
 // Shared memory: 2 index rows of `NC` int32, the row's `NC` flag bytes, + scan scratch.
 template <bool TRANSPOSED>
-__global__ void compact_kernel(const uint8_t* __restrict__ flags, int CB, int CH, int NQ, int NKV, int out_B,
-                               int out_H, int32_t* __restrict__ part_num, int32_t* __restrict__ part_idx,
-                               int32_t* __restrict__ full_num, int32_t* __restrict__ full_idx) {
+__device__ __forceinline__ void compact_row(const uint8_t* __restrict__ flags, int CB, int CH, int NQ, int NKV, int out_B,
+                                            int out_H, int32_t* __restrict__ part_num, int32_t* __restrict__ part_idx,
+                                            int32_t* __restrict__ full_num, int32_t* __restrict__ full_idx) {
   extern __shared__ int32_t smem[];
   const int NR = TRANSPOSED ? NKV : NQ;   // rows of the output
   const int NC = TRANSPOSED ? NQ : NKV;   // row width
@@ -285,6 +285,26 @@ __global__ void compact_kernel(const uint8_t* __restrict__ flags, int CB, int CH
     } else {
       for (int i = threadIdx.x; i < NC; i += kThreads) { dp[i] = row_p[i]; df[i] = row_f[i]; }
     }
+  }
+}
+
+template <bool TRANSPOSED>
+__global__ void compact_kernel(const uint8_t* __restrict__ flags, int CB, int CH, int NQ, int NKV, int out_B,
+                               int out_H, int32_t* __restrict__ part_num, int32_t* __restrict__ part_idx,
+                               int32_t* __restrict__ full_num, int32_t* __restrict__ full_idx) {
+  compact_row<TRANSPOSED>(flags, CB, CH, NQ, NKV, out_B, out_H, part_num, part_idx, full_num, full_idx);
+}
+
+// Both list sides in ONE launch (blockIdx.z = 0: kv side, 1: q side): no launch gap between them, and the tail of one
+// side fills with the other's rows.  The builder is bound by the HBM writes of the index arrays.
+__global__ void compact_both_kernel(const uint8_t* __restrict__ flags, int CB, int CH, int NQ, int NKV, int out_B, int out_H,
+                                    bma_block_lists l) {
+  if (blockIdx.z == 0) {
+    if ((int)blockIdx.x < CB * CH * NQ)
+      compact_row<false>(flags, CB, CH, NQ, NKV, out_B, out_H, l.kv_num, l.kv_idx, l.full_kv_num, l.full_kv_idx);
+  } else {
+    if ((int)blockIdx.x < CB * CH * NKV)
+      compact_row<true>(flags, CB, CH, NQ, NKV, out_B, out_H, l.q_num, l.q_idx, l.full_q_num, l.full_q_idx);
   }
 }
 
@@ -397,10 +417,20 @@ int mask_compile_launch(const bma_mask_spec& spec, int B, int H, const bma_block
     count_launches(1);
     return BMA_OK;
   };
-  int rc = launch_compact(false);
-  if (rc != BMA_OK) return rc;
-  if (l.q_num) {
-    rc = launch_compact(true);
+  int rc = BMA_OK;
+  if (l.q_num) {   // both sides: one launch
+    const int rows = p.CB * p.CH * std::max(l.NQ, l.NKV);
+    const int reps = ((p.CB == l.B) ? 1 : l.B) * ((p.CH == l.H) ? 1 : l.H);
+    int gy = std::max(1, std::min(reps, (sm_count * 4 + rows - 1) / rows));
+    gy = std::min(gy, 65535);
+    const int NC = std::max(l.NQ, l.NKV);
+    const size_t smem = sizeof(int32_t) * 2 * (size_t)NC + align_up((size_t)NC, 16);
+    if (smem > 48 * 1024)
+      BMA_CUDA_TRY(cudaFuncSetAttribute(compact_both_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    compact_both_kernel<<<dim3(rows, gy, 2), kThreads, smem, st>>>(flags, p.CB, p.CH, l.NQ, l.NKV, l.B, l.H, l);
+    count_launches(1);
+  } else {
+    rc = launch_compact(false);
     if (rc != BMA_OK) return rc;
   }
   BMA_CUDA_TRY(cudaGetLastError());
