@@ -430,12 +430,16 @@ def test_virtual_ring_offsets_and_merge():
     B, L, H, d, world = 1, 1024, 2, 128, 4
     Q, K, V = (gen((B, L, H, d), i, torch.bfloat16).cuda() for i in range(3))
     n = L // world
-    for terms in (M.MaskTerms(causal=True), M.MaskTerms(band=(300, 40))):
+    # the third mask is an arbitrary traced function in the tile form: its tiles are indexed by GLOBAL positions, so the
+    # shards only move the offsets
+    from jaxmodules_b200 import mask_program as P
+    tiles = P.build_tiles(P.trace(lambda b, h, q, k: (k <= q) & ((q - k) % 3 != 1) | (k == q)), B, H, L, L, "cuda")
+    for terms in (M.MaskTerms(causal=True), M.MaskTerms(band=(300, 40)), M.MaskTerms(tiles=tiles)):
         full, full_lse = S.cuda_attend(Q, K, V, terms)
         for r in range(world):
             O = lse = None
             for owner in S.ring_schedule(r, world):
-                t = M.MaskTerms(causal=terms.causal, band=terms.band, q_offset=r * n, k_offset=owner * n)
+                t = M.MaskTerms(causal=terms.causal, band=terms.band, tiles=terms.tiles, q_offset=r * n, k_offset=owner * n)
                 O_s, lse_s = S.cuda_attend(Q[:, r * n:(r + 1) * n], K[:, owner * n:(owner + 1) * n].contiguous(),
                                            V[:, owner * n:(owner + 1) * n].contiguous(), t)
                 O, lse = (O_s, lse_s) if O is None else S.cuda_merge(O, lse, O_s, lse_s)
