@@ -38,15 +38,18 @@ constexpr uint32_t kHalfTile = BM * 64 * 2;     // one [128 x 64] bf16 box
 template <int HD> constexpr uint32_t kTileBytesOf = (HD / 64) * kHalfTile;  // a [128 x HD] operand tile: HD/64 boxes
 constexpr float kRescaleThreshold = 8.0f;       // log2 units: rescale O only when the max grew by > 2^8
 constexpr int kMaxKvTiles = 4096;               // merged kv list kept in shared memory
-// P goes from the softmax warps to the MMA warp in this many parts (key ranges of 128 / kPParts), each with its own
-// barrier, so that the first k-steps of P V run under the remaining exponentials: 2 or 4.  Measured (same box, forward
-// TFLOP/s on config 2 / L=8192 / config 5): 2 parts 1091 / 1129 / 1258, 4 parts 1037 / 1065 / 1192 -- each hand-over costs a
-// TMEM store wait, a fence and 128 barrier arrivals, more than the 128 cycles of P V it uncovers.
-#ifndef BMA_FWD_P_PARTS
-#define BMA_FWD_P_PARTS 2
+// P goes from the softmax warps to the MMA warp in two parts, each with its own barrier, so that the first k-steps of
+// P V run under the remaining exponentials.  The exponentials are taken in four chunks of 32 keys (two k-steps) whose
+// TMEM stores are issued as they become ready; the first part is kSplitChunks chunks long.
+// Measured (same box, forward TFLOP/s on config 2 / L=8192 / config 5): four parts of one chunk 1037 / 1065 / 1192 against
+// 1091 / 1129 / 1258 for two even parts -- each hand-over costs a TMEM store wait, a fence and 128 barrier arrivals; a
+// 96 + 32 split (fewer k-steps of P V behind the last exponential) 1069 / 1122 / 1242 against 1067 / 1131 / 1248 for
+// 64 + 64: the tail of P V is not what the next S waits for -- it queues behind the other tile's MMAs.
+#ifndef BMA_FWD_P_SPLIT
+#define BMA_FWD_P_SPLIT 2
 #endif
-constexpr int kPParts = BMA_FWD_P_PARTS;
-constexpr int kPartWords = 64 / kPParts;        // packed bf16 pairs (TMEM columns) per part
+constexpr int kPParts = 2;
+constexpr int kSplitChunks = BMA_FWD_P_SPLIT;   // 2: 64 + 64 keys, 3: 96 + 32 keys
 
 enum {
   BAR_Q = 0,
@@ -96,9 +99,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 #ifndef BMA_FWD_EXP_MODE
 #define BMA_FWD_EXP_MODE 2
 #endif
-__device__ __forceinline__ void tmem_st_words(uint32_t taddr, const uint32_t (&r)[32]) { tmem_st32(taddr, r); }
-__device__ __forceinline__ void tmem_st_words(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st16(taddr, r); }
-
 template <int WORDS>
 __device__ __forceinline__ float exp_part(const float* s, float sc, float m_sub, uint32_t (&pk)[WORDS]) {
 #if BMA_FWD_EXP_MODE == 0
@@ -335,7 +335,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
               if (!ok) break;
               tc_fence_after();
 #pragma unroll
-              for (int ks = hf * (8 / kPParts); ks < (hf + 1) * (8 / kPParts); ++ks) {
+              for (int ks = (hf == 0 ? 0 : 2 * kSplitChunks); ks < (hf == 0 ? 2 * kSplitChunks : 8); ++ks) {
                 // B = V[kv rows][d] read MN-major: 16 kv rows per k-step = 2048 B; the two 64-column boxes are kHalfTile apart
                 if (leader)
                   mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, dv0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)),
@@ -457,13 +457,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
       float row_sum = 0.f;
 #pragma unroll
-      for (int c = 0; c < kPParts; ++c) {
-        uint32_t pk[kPartWords];
-        row_sum += exp_part<kPartWords>(&s[c * 2 * kPartWords], sc, m_sub, pk);
-        tmem_st_words(tmem_s + c * kPartWords, pk);
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&sm.bar[BAR_PART + 2 * c + x]);
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t pk[16];
+        row_sum += exp_part<16>(&s[ch * 32], sc, m_sub, pk);
+        tmem_st16(tmem_s + ch * 16, pk);
+        if (ch == kSplitChunks - 1 || ch == 3) {   // end of a part: its stores have landed, the MMA warp may read it
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(&sm.bar[BAR_PART + 2 * (ch == 3 ? 1 : 0) + x]);
+        }
       }
       l = l * alpha + row_sum;
       ++cnt;
@@ -826,7 +828,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
-                for (int ks = hf * (8 / kPParts); ks < (hf + 1) * (8 / kPParts); ++ks)
+                for (int ks = (hf == 0 ? 0 : 2 * kSplitChunks); ks < (hf == 0 ? 2 * kSplitChunks : 8); ++ks)
                   if (leader)
                     mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, dv0 + (uint32_t)(st * kStageUnits + ks * (2048 >> 4)),
                            idesc_o, (cnt > 0) || (ks > 0));
@@ -965,13 +967,15 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
         float row_sum = 0.f;
 #pragma unroll
-        for (int c = 0; c < kPParts; ++c) {
-          uint32_t pk[kPartWords];
-          row_sum += exp_part<kPartWords>(&s[c * 2 * kPartWords], sc, m_sub, pk);
-          tmem_st_words(tmem_s + c * kPartWords, pk);
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(&sm.bar[PB_PART + 2 * c + x]);
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t pk[16];
+          row_sum += exp_part<16>(&s[ch * 32], sc, m_sub, pk);
+          tmem_st16(tmem_s + ch * 16, pk);
+          if (ch == kSplitChunks - 1 || ch == 3) {   // end of a part: its stores have landed, the MMA warp may read it
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sm.bar[PB_PART + 2 * (ch == 3 ? 1 : 0) + x]);
+          }
         }
         l = l * alpha + row_sum;
         ++cnt;
