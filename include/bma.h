@@ -263,7 +263,9 @@ int bma_attn_fwd(const bma_attn_args* args, const bma_mask_spec* spec,
                  const bma_block_lists* lists, bma_stream_t stream);
 
 /* Backward preprocess: delta = rowsum(dO * O); when d_o_bf16 is non-NULL also writes a
- * bf16 copy of dO there as a DENSE [B, N, Hq, d] array (the caller allocates B*N*Hq*d bf16
+ * bf16 copy of dO there (and takes delta from that rounded copy, the values the backward's
+ * dO V^T product sees, so that dP - delta cancels exactly where it should) as a DENSE
+ * [B, N, Hq, d] array (the caller allocates B*N*Hq*d bf16
  * elements and describes it to bma_attn_bwd with strides N*Hq*d, Hq*d, d -- whatever the
  * strides of args->o and args->d_o are).  The cotangent arrives in float32 because the
  * reference returns O in float32, jaxmodules/attention.py:173.  Part of what jax.vjp

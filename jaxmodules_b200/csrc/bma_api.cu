@@ -90,18 +90,23 @@ __global__ void __launch_bounds__(256) bwd_preprocess_rows4_kernel(bma_attn_args
         for (int e = 0; e < 4; ++e) { gv[i][e] = 0.f; ov[i][e] = 0.f; }
       }
     }
+    // With a bf16 copy, delta is taken from the ROUNDED cotangent -- the values the dP = dO V^T product of the backward
+    // kernels sees -- so that dP - delta cancels where it should (a row that attends one key has dS = 0 exactly; with
+    // the float32 cotangent in delta and the bf16 one in dP the difference of the two roundings would survive).
     float acc[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      acc[i] = fmaf(gv[i][0], ov[i][0], fmaf(gv[i][1], ov[i][1], fmaf(gv[i][2], ov[i][2], gv[i][3] * ov[i][3])));
       const int q = q0 + i;
-      if (do_bf16 && act && q < a.N) {
+      if (do_bf16) {
         __nv_bfloat162 lo = __floats2bfloat162_rn(gv[i][0], gv[i][1]), hi = __floats2bfloat162_rn(gv[i][2], gv[i][3]);
         uint2 w;
         w.x = *reinterpret_cast<uint32_t*>(&lo);
         w.y = *reinterpret_cast<uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(do_bf16 + (((int64_t)b * a.N + q) * a.Hq + h) * a.d + c) = w;
+        gv[i][0] = __uint_as_float(w.x << 16); gv[i][1] = __uint_as_float(w.x & 0xffff0000u);
+        gv[i][2] = __uint_as_float(w.y << 16); gv[i][3] = __uint_as_float(w.y & 0xffff0000u);
+        if (act && q < a.N) *reinterpret_cast<uint2*>(do_bf16 + (((int64_t)b * a.N + q) * a.Hq + h) * a.d + c) = w;
       }
+      acc[i] = fmaf(gv[i][0], ov[i][0], fmaf(gv[i][1], ov[i][1], fmaf(gv[i][2], ov[i][2], gv[i][3] * ov[i][3])));
     }
 #pragma unroll
     for (int off = 16; off; off >>= 1) {
@@ -139,21 +144,27 @@ __global__ void bwd_preprocess_kernel(bma_attn_args a, __nv_bfloat16* __restrict
         float gv[4], ov[4];
         load4(g + c, gv);
         load4(o + c, ov);
-        acc = fmaf(gv[0], ov[0], acc); acc = fmaf(gv[1], ov[1], acc);
-        acc = fmaf(gv[2], ov[2], acc); acc = fmaf(gv[3], ov[3], acc);
-        if (do_bf16) {
+        if (do_bf16) {   // delta from the rounded cotangent, see bwd_preprocess_rows4_kernel
           __nv_bfloat162 lo = __floats2bfloat162_rn(gv[0], gv[1]), hi = __floats2bfloat162_rn(gv[2], gv[3]);
           uint2 w;
           w.x = *reinterpret_cast<uint32_t*>(&lo);
           w.y = *reinterpret_cast<uint32_t*>(&hi);
           *reinterpret_cast<uint2*>(do_bf16 + r * a.d + c) = w;
+          gv[0] = __uint_as_float(w.x << 16); gv[1] = __uint_as_float(w.x & 0xffff0000u);
+          gv[2] = __uint_as_float(w.y << 16); gv[3] = __uint_as_float(w.y & 0xffff0000u);
         }
+        acc = fmaf(gv[0], ov[0], acc); acc = fmaf(gv[1], ov[1], acc);
+        acc = fmaf(gv[2], ov[2], acc); acc = fmaf(gv[3], ov[3], acc);
       }
     } else {
       for (int c = lane; c < a.d; c += 32) {
-        const float gv = to_float(g[c]);
+        float gv = to_float(g[c]);
+        if (do_bf16) {
+          const __nv_bfloat16 gb = __float2bfloat16_rn(gv);
+          do_bf16[r * a.d + c] = gb;
+          gv = __bfloat162float(gb);
+        }
         acc = fmaf(gv, to_float(o[c]), acc);
-        if (do_bf16) do_bf16[r * a.d + c] = __float2bfloat16_rn(gv);
       }
     }
     for (int off = 16; off; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);

@@ -535,3 +535,45 @@ def test_negative_scale_kernel_bf16():
         assert np.isfinite(g).all(), name
         err, top = np.abs(g - r), (1.0 if name == "O" else max(1.0, float(np.abs(r).max())))
         assert err.max() <= 2e-2 * top and err.mean() <= 2e-3 * top, (name, err.max(), err.mean(), top)
+
+
+@pytest.mark.parametrize("N,L", [(1, 1), (1, 128), (128, 1), (5, 300), (300, 5), (129, 129), (127, 257)])
+@pytest.mark.parametrize("d", [128, 64])
+def test_degenerate_lengths_bf16(N, L, d):
+    """Single tokens, one side shorter than a tile, lengths one past a tile boundary: the tensor-core kernels clip every
+    tile against the valid box (TMA zero fill on the way in, clipped stores on the way out).  GQA 4:1, with and
+    without a mask, forward and backward against the oracle."""
+    B, Hq, Hkv = 2, 4, 1
+    Q = gen((B, N, Hq, d), 0, torch.bfloat16)
+    K, V = (gen((B, L, Hkv, d), i, torch.bfloat16) for i in (1, 2))
+    dO = gen((B, N, Hq, d), 3, torch.float32)
+    # block_size 7 divides none of the lengths: the reference's padding path, which takes any number of keys
+    # (jaxmodules/attention.py:426-437); without window_size the result does not depend on it
+    for kw in (dict(block_size=7), dict(mask_fn=M.sliding_window_mask(3, 100), block_size=7)):
+        got = run(Q, K, V, dO, **kw)
+        # The oracle gets the cotangent as the tensor-core backward uses it, rounded to bf16: with one key, 512 (query,
+        # head) cotangents add up in a single dV row, and the rounding of each of them -- not of anything the kernels
+        # compute -- would dominate the comparison (0.2 absolute on a sum whose terms cancel to 4).
+        ref = oracle(Q, K, V, dO.to(torch.bfloat16).float(), **kw)
+        for name, g in zip(ALL, got):
+            g, r = g.float().numpy().astype(np.float64), ref[name]
+            assert np.isfinite(g).all(), name
+            err = np.abs(g - r)
+            # O absolute.  Gradients relative to their own largest entry: a handful of keys collect the bf16-rounded dS and
+            # P of up to 1200 (query, head) rows each, and the sum of those roundings grows with the row count while
+            # single entries cancel towards zero
+            top = 1.0 if name == "O" else max(1.0, float(np.abs(r).max()))
+            assert err.max() <= 2e-2 * top and err.mean() <= 2e-3 * top, (N, L, d, sorted(kw), name, err.max(), err.mean(), top)
+
+
+def test_mask_that_allows_nothing_bf16():
+    """mask_fn == False everywhere: every row is empty, O = 0, lse = -inf and all gradients are exactly zero
+    (jaxmodules/attention.py:99-100), without a single block in the lists."""
+    Q, K, V = (gen((1, 256, 2, 128), i, torch.bfloat16) for i in range(3))
+    dO = gen((1, 256, 2, 128), 3, torch.float32)
+    never = lambda b, h, q, k: (q < 0) & (k < 0)
+    got = run(Q, K, V, dO, mask_fn=never)
+    for t in got:
+        assert float(t.float().abs().max()) == 0.0
+    _, lse = jm.masked_attention_via_map(Q.cuda(), K.cuda(), V.cuda(), mask_fn=never, return_lse=True)
+    assert bool(torch.isinf(lse).all())
