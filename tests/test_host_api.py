@@ -138,3 +138,59 @@ def test_kernel_log_affine():
     q, k = torch.arange(4.0) / 4, torch.ones(4)
     assert float(jm.default_kernel(q, k)) == pytest.approx(math.exp(1.5 / 2))
     assert float(jm.threshold_kernel(1.0)(q, k)) == pytest.approx(math.exp(1.5 - 0.5))
+
+
+def test_ring_wait_turns_transport_errors_into_ring_transfer_error():
+    """Host-side failure handling of the ring, without any process group: a request whose wait raises (a time-out, a
+    peer that went away) must surface as RingTransferError naming the step; a healthy one passes through."""
+    from jaxmodules_b200 import sharding as S
+
+    class Req:
+        def __init__(self, fail):
+            self.fail, self.timeouts = fail, []
+
+        def wait(self, timeout=None):
+            self.timeouts.append(timeout)
+            if self.fail:
+                raise RuntimeError("Timed out waiting 3000ms for recv operation to complete")
+
+    ok = Req(False)
+    S._wait_all([ok], 3.0, "step 0")
+    assert ok.timeouts[0].total_seconds() == 3.0
+    S._wait_all([Req(False)], None, "step 0")          # no deadline: plain wait()
+    with pytest.raises(S.RingTransferError, match="step 5.*Timed out"):
+        S._wait_all([Req(False), Req(True)], 1.0, "rank 0: K/V rotation, ring step 5")
+
+
+def test_mask_caches_and_scratch_knobs():
+    """Host-side state: the per-callable table cache is keyed by function object and shape, device copies of a mask's
+    arrays are made once per (tensor, device, version), and lowering the scratch limit drops larger buffers."""
+    import torch
+    from jaxmodules_b200 import attention as A
+    from jaxmodules_b200 import masks as M
+    M.clear_mask_cache()
+    fn = lambda b, h, q, k: (q + k) % 2 == 0
+    t1 = M.terms_from_mask_fn(fn, 1, 1, 8, 8)
+    assert M.terms_from_mask_fn(fn, 1, 1, 8, 8) is t1                       # same function object, same shape: cached
+    assert M.terms_from_mask_fn(fn, 1, 1, 8, 16) is not t1                  # another shape
+    assert M.terms_from_mask_fn(lambda b, h, q, k: (q + k) % 2 == 0, 1, 1, 8, 8) is not t1   # another object
+    M.clear_mask_cache()
+    assert M.terms_from_mask_fn(fn, 1, 1, 8, 8) is not t1
+    seg = torch.zeros((2, 16), dtype=torch.int64)
+    a = M._on_device(seg, "cpu", torch.int32)
+    assert a.dtype == torch.int32 and M._on_device(seg, "cpu", torch.int32) is a
+    seg[0, 0] = 1                                                           # an in-place write bumps the version
+    b = M._on_device(seg, "cpu", torch.int32)
+    assert b is not a and int(b[0, 0]) == 1
+    same = torch.zeros((2, 16), dtype=torch.int32)
+    assert M._on_device(same, "cpu", torch.int32) is same                   # already in place: no copy
+    limit, frac = A._scratch_limit, A._scratch_fraction
+    try:
+        A._scratch_buffers[("test", 0)] = torch.empty(1024, dtype=torch.uint8)
+        A.set_backward_scratch_limit(512)
+        assert ("test", 0) not in A._scratch_buffers and A._scratch_limit == 512
+        A._scratch_buffers[("test", 1)] = torch.empty(16, dtype=torch.uint8)
+        A.release_backward_scratch()
+        assert not A._scratch_buffers
+    finally:
+        A.set_backward_scratch_limit(limit, frac)
