@@ -6,7 +6,10 @@ never does.
 
 Parity status: PINNED for integer work.  Every literal known-answer array in the
 reference's tests/test_block_mask.py (stored as tests/golden/block_mask_known_answers.json)
-is reproduced by these functions (tests/test_oracle_block_mask.py).
+is reproduced by these functions (tests/test_oracle_block_mask.py), and so is every index array that the
+reference's own create_block_mask / BlockMask.causal_mask / full_mask produce for the eleven masks of
+tests/golden/reference_cases.py (the reference's source run on a stand-in for jax by
+tests/golden/make_reference_vectors.py; tests/test_reference_vectors.py).
 
 Each function names the reference code it follows (paths inside acutkosky/jaxmodules).
 """

@@ -9,7 +9,8 @@ float64, so the result is the reference's up to its float32 rounding.
 
 Pinned by tests/test_oracle_flex.py against ``torch.nn.attention.flex_attention`` — the same
 cross-check the reference's own tests use (tests/test_attention.py:17-118, 223-356) — and
-against the dense float64 softmax.
+against the dense float64 softmax; and by tests/test_reference_vectors.py against outputs of the reference's own
+flex_attention source, run on a stand-in for jax by tests/golden/make_reference_vectors.py.
 """
 from __future__ import annotations
 
