@@ -16,7 +16,26 @@ from . import numpy  # noqa: F401  (jax.numpy)
 from . import lax    # noqa: F401
 
 Array = torch.Tensor
-torch.Tensor.astype = lambda self, dtype: self.to(dtype)   # ndarray methods the reference calls on arrays
+def _astype(self, dtype):
+    if self.dtype.is_floating_point and not dtype.is_floating_point and dtype != torch.bool:
+        info = torch.iinfo(dtype)             # XLA saturates a float -> integer conversion (-inf becomes the minimum)
+        return torch.nan_to_num(self, nan=0.0, posinf=float(info.max), neginf=float(info.min)).clamp(info.min, info.max).to(dtype)
+    return self.to(dtype)
+
+
+torch.Tensor.astype = _astype   # ndarray methods the reference calls on arrays
+
+_plain_repeat = torch.Tensor.repeat
+
+
+def _repeat(self, *sizes, axis=None):
+    """ndarray.repeat(n, axis=k) repeats elements; torch's own repeat (tiling) is kept for calls without ``axis``."""
+    if axis is None:
+        return _plain_repeat(self, *sizes)
+    return torch.repeat_interleave(self, sizes[0], dim=axis)
+
+
+torch.Tensor.repeat = _repeat
 
 
 class _At:
@@ -28,20 +47,34 @@ class _At:
     def __getitem__(self, idx):
         return _At(self.x, idx)
 
+    def _in_bounds(self):
+        """jax drops a scatter update whose integer index is out of range."""
+        items = self.idx if isinstance(self.idx, tuple) else (self.idx,)
+        for dim, i in enumerate(items):
+            if isinstance(i, (int, torch.Tensor)) and not isinstance(i, bool):
+                if isinstance(i, torch.Tensor) and (i.ndim != 0 or i.dtype == torch.bool):
+                    continue
+                if not -self.x.shape[dim] <= int(i) < self.x.shape[dim]:
+                    return False
+        return True
+
     def set(self, v):
         y = self.x.clone()
-        y[self.idx] = v
+        if self._in_bounds():
+            _plain_setitem(y, self.idx, v)
         return y
 
     def add(self, v):
         y = self.x.clone()
-        y[self.idx] += v
+        if self._in_bounds():
+            _plain_setitem(y, self.idx, _plain_getitem(y, self.idx) + v)
         return y
 
 
 torch.Tensor.at = property(lambda self: _At(self))
 
 _plain_getitem = torch.Tensor.__getitem__
+_plain_setitem = torch.Tensor.__setitem__
 
 
 def _clamping_getitem(self, idx):
@@ -50,12 +83,15 @@ def _clamping_getitem(self, idx):
     past a row's count)."""
     items = idx if isinstance(idx, tuple) else (idx,)
     is_index = lambda i: isinstance(i, torch.Tensor) and i.dtype not in (torch.bool, torch.uint8) and not i.dtype.is_floating_point
-    if any(is_index(i) for i in items) and all(isinstance(i, (int, slice)) or is_index(i) for i in items):
+    plain_int = lambda i: isinstance(i, int) and not isinstance(i, bool)
+    if all(plain_int(i) or isinstance(i, slice) or is_index(i) for i in items) and len(items) <= self.ndim:
         fixed = []
         for dim, i in enumerate(items):
+            n = self.shape[dim]
             if is_index(i):
-                n = self.shape[dim]
                 i = torch.where(i < 0, i + n, i).clamp(0, n - 1)
+            elif plain_int(i) and n > 0:
+                i = min(max(i + n if i < 0 else i, 0), n - 1)
             fixed.append(i)
         idx = tuple(fixed)
     return _plain_getitem(self, idx)
@@ -171,3 +207,56 @@ class nn:
     @staticmethod
     def softmax(x, axis=-1):
         return torch.softmax(x, dim=axis)
+
+
+from . import random  # noqa: E402,F401
+
+
+def _tree_leaves(tree):
+    if isinstance(tree, (tuple, list)):
+        return [leaf for part in tree for leaf in _tree_leaves(part)]
+    if isinstance(tree, dict):
+        return [leaf for part in tree.values() for leaf in _tree_leaves(part)]
+    return [tree]
+
+
+def _tree_like(tree, leaves):
+    if isinstance(tree, (tuple, list)):
+        return type(tree)(_tree_like(part, leaves) for part in tree)
+    if isinstance(tree, dict):
+        return {k: _tree_like(part, leaves) for k, part in tree.items()}
+    return next(leaves)
+
+
+def value_and_grad(fun, argnums=0, has_aux=False):
+    """Reverse-mode derivative through torch autograd (the custom_vjp rules above are honoured); a differentiated
+    argument may be a tuple / list / dict of arrays."""
+    single = isinstance(argnums, int)
+    nums = (argnums,) if single else tuple(argnums)
+
+    def wrapped(*args, **kwargs):
+        args = list(args)
+        with torch.enable_grad():
+            for i in nums:
+                args[i] = _tree_like(args[i], iter([x.detach().requires_grad_(True) for x in _tree_leaves(args[i])]))
+            out = fun(*args, **kwargs)
+            value, aux = out if has_aux else (out, None)
+            leaves = [x for i in nums for x in _tree_leaves(args[i])]
+            flat = torch.autograd.grad(value, leaves, allow_unused=True)
+        flat = iter([torch.zeros_like(x) if g is None else g for x, g in zip(leaves, flat)])
+        grads = tuple(_tree_like(args[i], flat) for i in nums)
+        value = value.detach()
+        result = (value, aux) if has_aux else value
+        return result, (grads[0] if single else grads)
+
+    return wrapped
+
+
+def grad(fun, argnums=0, has_aux=False):
+    both = value_and_grad(fun, argnums, has_aux)
+
+    def wrapped(*args, **kwargs):
+        value, grads = both(*args, **kwargs)
+        return (grads, value[1]) if has_aux else grads
+
+    return wrapped

@@ -12,6 +12,8 @@ The block walk, window clamp, padding, head mapping, running average and the str
 reference's; the floating-point primitives underneath are torch's, not XLA's, so float agreement with a real jax run is
 to rounding, not to the bit.  Integer results do not depend on that.
 
+The stand-in is itself validated by the reference's own test files (run_reference_tests_on_stand_in.py: 93 passed).
+
     python tests/golden/make_reference_vectors.py /path/to/jaxmodules-checkout
 """
 import sys
