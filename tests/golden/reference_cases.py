@@ -72,6 +72,12 @@ ATTENTION = {
     "bf16_gqa_causal_d128": dict(shape=(1, 256, 256, 2, 1, 128), kw=dict(is_causal=True, block_size=128), dtype="bfloat16"),
     "bf16_documents_d128": dict(shape=(1, 256, 256, 2, 2, 128), kw=dict(block_size=128), dtype="bfloat16",
                                 mask=lambda flavour: documents_causal(segments(1, 256, 20, 90, 11), flavour)),
+    # the shapes of BASELINE configs 3 and 4 at L = 1024 (8 x 8 blocks of 128): band inside a block window, packed documents
+    "bf16_band_window_8_blocks": dict(shape=(1, 1024, 1024, 2, 2, 128), kw=dict(block_size=128, window_size=(256, 256)),
+                                      dtype="bfloat16", mask=plain(lambda b, h, q, k: (q - k <= 256) & (k - q <= 256))),
+    "bf16_documents_8_blocks": dict(shape=(2, 1024, 1024, 4, 2, 128), kw=dict(block_size=128), dtype="bfloat16",
+                                    mask=lambda flavour: documents_causal(segments(2, 1024, 64, 400, 4), flavour)),
+    "bf16_causal_d64_8_blocks": dict(shape=(1, 1024, 1024, 4, 4, 64), kw=dict(is_causal=True, block_size=128), dtype="bfloat16"),
 }
 
 
@@ -80,7 +86,7 @@ def attention_inputs(name):
     c = ATTENTION[name]
     B, N, L, Hq, Hkv, d = c["shape"]
     lead = () if B is None else (B,)
-    base = 100 * sorted(ATTENTION).index(name)
+    base = zlib.crc32(name.encode()) % (2 ** 31)
     return (normal(lead + (N, Hq, d), base + 0), normal(lead + (L, Hkv, d), base + 1),
             normal(lead + (L, Hkv, d), base + 2), normal(lead + (N, Hq, d), base + 3))
 
@@ -135,7 +141,7 @@ FLEX = {
 def flex_inputs(name):
     """(query, key, value, d_out) in the [B, H, L, E] layout of flex_attention."""
     B, Hq, Hkv, L, S, E = FLEX[name]["shape"]
-    base = 10000 + 100 * sorted(FLEX).index(name)
+    base = zlib.crc32(("flex/" + name).encode()) % (2 ** 31)
     return (normal((B, Hq, L, E), base), normal((B, Hkv, S, E), base + 1), normal((B, Hkv, S, E), base + 2),
             normal((B, Hq, L, E), base + 3))
 
