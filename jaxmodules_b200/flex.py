@@ -26,8 +26,7 @@ import torch
 from . import _native as nat
 from . import masks as _masks
 from . import attention as _att
-from .block_mask import (BlockMask, compile_block_lists, get_dense_from_kv_blocks, get_sparse_kv_data_from_blocks,
-                         get_sparse_q_data_from_blocks)
+from .block_mask import BlockMask, compile_block_lists, get_dense_from_kv_blocks, get_sparse_q_data_from_blocks
 
 __all__ = ["flex_attention", "flex_route"]
 

@@ -10,7 +10,6 @@ block window); their block lists are compiled on the device inside the jitted pr
 from __future__ import annotations
 
 import ctypes
-import math
 from functools import partial
 from pathlib import Path
 

@@ -15,7 +15,7 @@ one of two forms:
 from __future__ import annotations
 
 import weakref
-from dataclasses import dataclass, field, replace
+from dataclasses import dataclass, field
 from typing import Callable, Optional, Tuple
 
 import numpy as np

@@ -27,7 +27,6 @@ Citations are paths inside acutkosky/jaxmodules.
 from __future__ import annotations
 
 import math
-from typing import Callable, Optional, Tuple
 
 import numpy as np
 import torch
