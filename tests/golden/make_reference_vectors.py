@@ -41,7 +41,7 @@ def main(checkout: str):
         dtype = getattr(torch, case.get("dtype", "float32"))
         Q, K, V, dO = (torch.from_numpy(x).to(dtype) for x in rc.attention_inputs(name))
         Q, K, V = (x.requires_grad_(True) for x in (Q, K, V))
-        O = ref_attention.masked_attention_via_map(Q, K, V, **rc.attention_kwargs(name, "torch"))
+        O = ref_attention.masked_attention_via_map(Q, K, V, **rc.attention_kwargs(name, "torch", ref_attention))
         O.backward(dO.to(O.dtype))
         out[f"attention/{name}/dtype"] = np.asarray(str(O.dtype))
         for key, x in (("O", O), ("dQ", Q.grad), ("dK", K.grad), ("dV", V.grad)):

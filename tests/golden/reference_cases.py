@@ -68,6 +68,11 @@ ATTENTION = {
     "packed_documents_causal": dict(shape=(2, 64, 64, 4, 2, 16), kw=dict(block_size=16),
                                     mask=lambda flavour: documents_causal(segments(2, 64, 5, 24, 7), flavour)),
     "three_dimensional_inputs_gqa": dict(shape=(None, 16, 32, 4, 2, 32), kw=dict(is_causal=True)),
+    # kernel_fn: the reference's threshold_kernel (dot product NOT divided by sqrt(d)) and a custom exp(a q.k)
+    "threshold_kernel_causal": dict(shape=(1, 32, 32, 2, 2, 16), kw=dict(is_causal=True, block_size=8), input_scale=0.5,
+                                    kernel=("threshold", 0.7)),
+    "custom_exponential_kernel_gqa": dict(shape=(2, 16, 24, 4, 2, 16), kw=dict(block_size=8), input_scale=0.7,
+                                          kernel=("exponential", 0.3)),
     # bfloat16 inputs: the reference then computes its scores in bfloat16 (no max subtraction, float32 running sums)
     "bf16_gqa_causal_d128": dict(shape=(1, 256, 256, 2, 1, 128), kw=dict(is_causal=True, block_size=128), dtype="bfloat16"),
     "bf16_documents_d128": dict(shape=(1, 256, 256, 2, 2, 128), kw=dict(block_size=128), dtype="bfloat16",
@@ -87,15 +92,32 @@ def attention_inputs(name):
     B, N, L, Hq, Hkv, d = c["shape"]
     lead = () if B is None else (B,)
     base = zlib.crc32(name.encode()) % (2 ** 31)
-    return (normal(lead + (N, Hq, d), base + 0), normal(lead + (L, Hkv, d), base + 1),
-            normal(lead + (L, Hkv, d), base + 2), normal(lead + (N, Hq, d), base + 3))
+    s = c.get("input_scale", 1.0)
+    return (normal(lead + (N, Hq, d), base + 0, s), normal(lead + (L, Hkv, d), base + 1, s),
+            normal(lead + (L, Hkv, d), base + 2, s), normal(lead + (N, Hq, d), base + 3))
 
 
-def attention_kwargs(name, flavour):
+def attention_kwargs(name, flavour, reference_module=None):
+    """Keyword arguments of the call for one consumer.  ``kernel``: the generator ("torch") takes the reference's own
+    threshold_kernel from ``reference_module`` or a jnp lambda; the oracle ("numpy") takes the (a, b) of exp(a q.k + b);
+    the package takes its threshold_kernel or a torch lambda, which it probes."""
     c = ATTENTION[name]
     kw = dict(c["kw"])
     if "mask" in c:
         kw["mask_fn"] = c["mask"](flavour)
+    if "kernel" in c:
+        kind, value = c["kernel"]
+        d = c["shape"][5]
+        if flavour == "torch":
+            import jax.numpy as jnp
+            kw["kernel_fn"] = (reference_module.threshold_kernel(value) if kind == "threshold"
+                               else (lambda q, k: jnp.exp(value * jnp.dot(q, k))))
+        elif flavour == "numpy":
+            kw["kernel"] = (1.0, -value / d ** 0.5) if kind == "threshold" else (value, 0.0)
+        else:
+            import torch
+            import jaxmodules_b200 as jm
+            kw["kernel_fn"] = jm.threshold_kernel(value) if kind == "threshold" else (lambda q, k: torch.exp(value * torch.dot(q, k)))
     return kw
 
 

@@ -47,7 +47,7 @@ def test_attention_oracle_matches_the_reference_source(vectors, name):
     for key in ALL:
         got = dense[key][0] if lead else dense[key]
         rc.compare(f"attention/{name}/{key}", got, vectors, *tol)
-    if not bf16:
+    if not bf16 and "kernel" not in kw:
         # the faithful blockwise restatement (same walk as the reference, float32) agrees as well
         port = ao.masked_attention_via_map(Q, K, V, dO=dO, **kw)
         for key, got in zip(ALL, port):
