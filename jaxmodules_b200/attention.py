@@ -85,6 +85,34 @@ def kernel_log_affine(kernel_fn: Callable, d: int) -> Tuple[float, float]:
 _DTYPES = {torch.float32: nat.BMA_DTYPE_F32, torch.bfloat16: nat.BMA_DTYPE_BF16}
 
 
+def block_window(N: int, L: int, block_size: Optional[int], window_size: Optional[Tuple[int, int]]):
+    """Block geometry exactly as the reference derives it, and its errors: padding only when N is not a multiple of
+    ``block_size`` (jaxmodules/attention.py:426-434; then any L is accepted), otherwise L must be a whole number of
+    blocks because the keys are cut into blocks of the QUERY block size (:155-158); ``block_size=None`` means one block
+    of N queries (:195-196).  Returns None without ``window_size``, else ``(block, left_blocks, right_blocks, key_blocks)``
+    with ``left = ceil(l / block)``, ``right = 1 + ceil(r / block)`` (:199-204); a window of more blocks than there are
+    key blocks is an error (a shape error inside the reference's slice).  Nothing is physically padded on the CUDA
+    path; the kernels bound-check instead."""
+    bs = N if block_size is None else int(block_size)
+    if bs <= 0:
+        raise ValueError("block_size must be positive")
+    if N % bs != 0:
+        Lp = L + bs - (L % bs)
+    else:
+        Lp = L
+        if L % bs != 0:
+            raise ValueError("number of keys must be a multiple of block_size when the number of queries is")
+    if window_size is None:
+        return None
+    left, right = window_size
+    lb = (left + bs - 1) // bs
+    rb = 1 + (right + bs - 1) // bs
+    nkb = Lp // bs
+    if lb + rb > nkb:
+        raise ValueError("window_size covers more blocks than there are key blocks")
+    return bs, lb, rb, nkb
+
+
 def _tensor(t: Optional[torch.Tensor]) -> nat.Tensor:
     out = nat.Tensor()
     if t is None:
@@ -388,6 +416,7 @@ def masked_attention_via_map(
     assert d == dq and Lv == L and dv == d, f"shape mismatch in K {tuple(K.shape)}, Q {tuple(Q.shape)} and V {tuple(V.shape)}"
     assert Hq % Hk == 0, "Hq must be divisible by Hk"
     assert Hv == Hk, "Hv must be equal to Hk"
+    block_window(N, L, block_size, window_size)      # argument errors first, wherever the tensors live
     if not (Q.is_cuda and K.is_cuda and V.is_cuda):
         raise RuntimeError("masked_attention_via_map needs CUDA tensors; there is no CPU path")
     if Q.dtype not in _DTYPES or K.dtype != Q.dtype or V.dtype != Q.dtype:
@@ -398,26 +427,9 @@ def masked_attention_via_map(
     else:
         terms = _masks.terms_from_mask_fn(mask_fn, B, Hq, N, L, device=Q.device)
 
-    # Block geometry exactly as the reference derives it: padding only when N is not a
-    # multiple of block_size (jaxmodules/attention.py:426-434), kv blocks sized like q blocks
-    # (:155-158).  Nothing is physically padded; the kernels bound-check instead.
-    bs = N if block_size is None else int(block_size)
-    if bs <= 0:
-        raise ValueError("block_size must be positive")
-    if N % bs != 0:
-        Lp = L + bs - (L % bs)
-    else:
-        Lp = L
-        if L % bs != 0:
-            raise ValueError("number of keys must be a multiple of block_size when the number of queries is")
-    if window_size is not None:
-        left, right = window_size
-        lb = (left + bs - 1) // bs
-        rb = 1 + (right + bs - 1) // bs
-        nkb = Lp // bs
-        if lb + rb > nkb:
-            raise ValueError("window_size covers more blocks than there are key blocks")
-        terms = terms.merged(_masks.MaskTerms(window=(bs, lb, rb, nkb)))
+    window = block_window(N, L, block_size, window_size)
+    if window is not None:
+        terms = terms.merged(_masks.MaskTerms(window=window))
 
     fix = lambda t: t if t.stride(-1) == 1 else t.contiguous()
     O, lse = _MaskedAttention.apply(fix(Q), fix(K), fix(V), terms, out_dtype or torch.float32, backend,

@@ -48,6 +48,19 @@ def main(checkout: str):
             rc.pack(f"attention/{name}/{key}", x.detach().float().numpy(), out)
         print("attention", name, tuple(O.shape), O.dtype)
 
+    # which argument combinations the reference accepts (shape and window checks); the values themselves are covered above
+    outcomes = []
+    for case in rc.geometry_cases():
+        Q = torch.from_numpy(rc.normal((1, case["N"], case["Hq"], case["d"]), 1))
+        K = torch.from_numpy(rc.normal((1, case["L"], case["Hkv"], case["d"]), 2))
+        try:
+            ref_attention.masked_attention_via_map(Q, K, K, **case["kw"])
+            outcomes.append(1)
+        except Exception:
+            outcomes.append(0)
+    out["geometry/accepted"] = np.asarray(outcomes, dtype=np.uint8)
+    print("geometry", len(outcomes), "cases,", int(sum(outcomes)), "accepted")
+
     for name, case in rc.BLOCK_MASK.items():
         if "constructor" in case:
             bm = getattr(ref_block_mask.BlockMask, case["constructor"])(*case["args"])

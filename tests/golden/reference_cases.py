@@ -121,6 +121,34 @@ def attention_kwargs(name, flavour, reference_module=None):
     return kw
 
 
+def geometry_cases(count=240):
+    """Random (shape, block_size, window_size, is_causal) combinations — most of them invalid in some way — for which
+    the generator records whether the reference raises.  Returns dicts with N, L, Hq, Hkv, d, kw."""
+    rng = np.random.Generator(np.random.PCG64(2024))
+    cases = []
+    for _ in range(count):
+        Hkv = int(rng.integers(1, 3))
+        Hq = Hkv * int(rng.choice([1, 2])) if rng.random() < 0.85 else Hkv + 1 + int(rng.integers(0, 2))
+        N = int(rng.integers(1, 33))
+        L = N if rng.random() < 0.4 else int(rng.integers(1, 33))
+        kw = {}
+        if rng.random() < 0.5:
+            kw["is_causal"] = True
+        r = rng.random()
+        if r < 0.45:
+            kw["block_size"] = int(rng.integers(1, 13))
+        elif r < 0.7:
+            divisors = [x for x in range(1, N + 1) if N % x == 0]
+            kw["block_size"] = int(rng.choice(divisors))
+        if "block_size" in kw and rng.random() < 0.6:
+            bs = kw["block_size"]
+            kw["window_size"] = (int(rng.integers(0, 3 * bs + 1)), int(rng.integers(0, 2 * bs + 1)))
+        elif rng.random() < 0.1:
+            kw["window_size"] = (int(rng.integers(0, N + 1)), int(rng.integers(0, N + 1)))
+        cases.append(dict(N=N, L=L, Hq=Hq, Hkv=Hkv, d=8, kw=kw))
+    return cases
+
+
 # ---- create_block_mask / BlockMask constructors ---------------------------------------------------------------------
 BLOCK_MASK_FIELDS = ["kv_num_blocks", "kv_indices", "full_kv_num_blocks", "full_kv_indices",
                      "q_num_blocks", "q_indices", "full_q_num_blocks", "full_q_indices"]

@@ -84,3 +84,28 @@ def test_flex_oracle_matches_the_reference_source(vectors, name):
         kw["block_mask"] = types.SimpleNamespace(**t)
     out = flex_attention_oracle(q, k, v, **kw)
     rc.compare(f"flex/{name}/O", np.asarray(out), vectors, 1e-4, 1e-5)
+
+
+def test_argument_errors_match_the_reference(vectors):
+    """The shape / block / window combinations the reference accepts are exactly those the package's host-side check
+    and the oracle's blockwise port accept (240 random combinations, 128 of them valid)."""
+    from jaxmodules_b200.attention import block_window
+    accepted = vectors["geometry/accepted"]
+    cases = rc.geometry_cases()
+    assert len(cases) == len(accepted)
+    for case, ok in zip(cases, accepted):
+        heads_ok = case["Hq"] % case["Hkv"] == 0
+        try:
+            block_window(case["N"], case["L"], case["kw"].get("block_size"), case["kw"].get("window_size"))
+            mine = heads_ok
+        except ValueError:
+            mine = False
+        assert mine == bool(ok), case
+        Q = torch.from_numpy(rc.normal((1, case["N"], case["Hq"], case["d"]), 1))
+        K = torch.from_numpy(rc.normal((1, case["L"], case["Hkv"], case["d"]), 2))
+        try:
+            ao.masked_attention_via_map(Q, K, K, **case["kw"])
+            port = True
+        except Exception:
+            port = False
+        assert port == bool(ok), case
