@@ -225,6 +225,8 @@ def ring_attention_forward(Q, K, V, *, rank: int, world: int, is_causal: bool = 
     if validate and exchange is None:
         _check_neighbours(k_cur, rank, world, group, timeout_s)
     parts = [None] * len(q_segs)          # (O, lse) per local query range
+    # two receive pairs used in turn: the pair received at step s is sent at step s+1 and free again at step s+2
+    kv_bufs = [[torch.empty_like(k_cur), torch.empty_like(v_cur)] for _ in range(2)] if exchange is None and world > 1 else None
     for s, owner in enumerate(ring_schedule(rank, world)):
         reqs = []
         if s + 1 < world:
@@ -232,7 +234,7 @@ def ring_attention_forward(Q, K, V, *, rank: int, world: int, is_causal: bool = 
             if exchange is not None:
                 k_nxt, v_nxt = exchange([k_cur, v_cur], dst, src)
             else:
-                k_nxt, v_nxt = torch.empty_like(k_cur), torch.empty_like(v_cur)
+                k_nxt, v_nxt = kv_bufs[s & 1]
                 ops = [dist.P2POp(dist.isend, k_cur, dst, group), dist.P2POp(dist.isend, v_cur, dst, group),
                        dist.P2POp(dist.irecv, k_nxt, src, group), dist.P2POp(dist.irecv, v_nxt, src, group)]
                 reqs = dist.batch_isend_irecv(ops)
@@ -277,11 +279,14 @@ def ring_attention_backward(Q, K, V, O, lse, dO, *, rank: int, world: int, is_ca
     local queries).
 
     K and V travel round the ring as in the forward pass, and the float32 accumulators of dK and
-    dV travel with them: at step s this rank adds the contribution of its queries to the tokens it
-    holds and hands tokens and accumulators to rank+1.  The K/V transfer of the next step is posted
-    before the kernels of this step and runs under them; the accumulators follow once the step's
-    kernels are queued.  After the last step one more hop brings every accumulator back to the
-    rank that owns the tokens.  dQ stays local (float32 accumulation over the steps).
+    dV travel with them, one step behind: at step s this rank computes the contribution of its
+    queries to the tokens it holds into a buffer of its own, and only then takes the accumulator
+    that the previous rank sent at the end of ITS step s-1 — a transfer that has run under this
+    step's kernels — adds the two and posts the sum to rank+1.  So neither the K/V transfer (posted
+    before the step's kernels) nor the accumulator transfer (posted after them, awaited a step
+    later) sits on the critical path.  After the last step one more wait brings every accumulator
+    home to the rank that owns the tokens.  dQ stays local (float32 accumulation over the steps).
+    Receive buffers are two fixed pairs used in turn; nothing is allocated per step.
 
     ``exchange(tensors, dst, src)`` replaces the point-to-point transfer (it returns the received
     tensors); the default uses ``torch.distributed.batch_isend_irecv`` on ``group``."""
@@ -291,25 +296,33 @@ def ring_attention_backward(Q, K, V, O, lse, dO, *, rank: int, world: int, is_ca
     q_segs = _segments(layout, rank, world)
     dst, src = (rank + 1) % world, (rank - 1) % world
 
-    def default_exchange(tensors, dst_, src_):
-        recv = [torch.empty_like(t) for t in tensors]
-        ops = [dist.P2POp(dist.isend, t, dst_, group) for t in tensors] + [dist.P2POp(dist.irecv, t, src_, group) for t in recv]
-        return recv, dist.batch_isend_irecv(ops)
-
-    def start(tensors):
+    def start(tensors, recv):
+        """Posts send(tensors) -> dst and recv -> src; returns (received tensors, requests to wait for)."""
         if exchange is not None:
             return exchange(tensors, dst, src), []
-        return default_exchange(tensors, dst, src)
+        ops = [dist.P2POp(dist.isend, t, dst, group) for t in tensors] + [dist.P2POp(dist.irecv, t, src, group) for t in recv]
+        return recv, dist.batch_isend_irecv(ops)
 
+    if world == 1 and exchange is None:
+        exchange = lambda tensors, dst_, src_: tensors      # a ring of one: the hop to oneself
+    f32 = dict(dtype=torch.float32, device=K.device)
+    own = exchange is None                        # the default transfer receives into buffers kept here
     k_cur, v_cur = K.contiguous(), V.contiguous()
-    dk_acc = torch.zeros(K.shape, dtype=torch.float32, device=K.device)
-    dv_acc = torch.zeros(V.shape, dtype=torch.float32, device=V.device)
+    # K/V: two receive pairs used in turn (the pair received at step s is sent at step s+1 and free again at s+2)
+    kv_bufs = [[torch.empty_like(k_cur), torch.empty_like(v_cur)] for _ in range(2)] if own else None
+    # accumulators: two pairs for the sums built here (one may still be in flight to rank+1 while the next is built)
+    # and two pairs for the sums arriving from rank-1
+    part_bufs = [[torch.empty(K.shape, **f32), torch.empty(V.shape, **f32)] for _ in range(2)]
+    recv_bufs = [[torch.empty(K.shape, **f32), torch.empty(V.shape, **f32)] for _ in range(2)] if own else None
     dq_acc = torch.zeros(Q.shape, dtype=torch.float32, device=Q.device)
     O, dO = O.contiguous(), dO.contiguous()
+    incoming, acc_reqs = None, []
     for s, owner in enumerate(ring_schedule(rank, world)):
         kv_next, kv_reqs = (None, [])
         if s + 1 < world:
-            kv_next, kv_reqs = start([k_cur, v_cur])
+            kv_next, kv_reqs = start([k_cur, v_cur], kv_bufs[s & 1] if own else None)
+        dk_part, dv_part = part_bufs[s % len(part_bufs)]
+        written = set()
         for ql, qg, qn in q_segs:
             for kl, kg, kn in _segments(layout, owner, world):
                 if _pair_is_empty(terms, qg, qn, kg, kn):
@@ -318,11 +331,27 @@ def ring_attention_backward(Q, K, V, O, lse, dO, *, rank: int, world: int, is_ca
                 dq_s, dk_s, dv_s = backward(Q[:, qs], k_cur[:, ks], v_cur[:, ks], O[:, qs], lse[:, :, qs].contiguous(),
                                             dO[:, qs], _step_terms(terms, qg, kg))
                 dq_acc[:, qs] += dq_s
-                dk_acc[:, ks] += dk_s
-                dv_acc[:, ks] += dv_s
-        # the accumulators move on after every step, the last hop returns them to the tokens' owner
-        (dk_acc, dv_acc), acc_reqs = start([dk_acc, dv_acc])
-        _wait_all(kv_reqs + acc_reqs, timeout_s, f"rank {rank}: K/V and dK/dV rotation, backward ring step {s}")
+                if kl in written:
+                    dk_part[:, ks] += dk_s
+                    dv_part[:, ks] += dv_s
+                else:          # the first contribution to these tokens in this step: no zero-fill, no read
+                    dk_part[:, ks].copy_(dk_s)
+                    dv_part[:, ks].copy_(dv_s)
+                    written.add(kl)
+        for kl, kg, kn in _segments(layout, owner, world):
+            if kl not in written:
+                dk_part[:, kl:kl + kn].zero_()
+                dv_part[:, kl:kl + kn].zero_()
+        if incoming is not None:
+            # sent by rank-1 at the end of its previous step; the transfer ran under this step's kernels
+            _wait_all(acc_reqs, timeout_s, f"rank {rank}: dK/dV rotation, backward ring step {s - 1}")
+            dk_part += incoming[0]
+            dv_part += incoming[1]
+        incoming, acc_reqs = start([dk_part, dv_part], recv_bufs[s & 1] if own else None)
+        _wait_all(kv_reqs, timeout_s, f"rank {rank}: K/V rotation, backward ring step {s}")
         if kv_next is not None:
             k_cur, v_cur = kv_next
+    # the last hop brings every accumulator back to the rank that owns the tokens
+    _wait_all(acc_reqs, timeout_s, f"rank {rank}: dK/dV rotation, last hop")
+    dk_acc, dv_acc = incoming
     return dq_acc.to(Q.dtype), dk_acc.to(K.dtype), dv_acc.to(V.dtype)
