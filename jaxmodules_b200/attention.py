@@ -268,9 +268,16 @@ def attention_backward(Q, K, V, O, lse, dO, ctx, backend=nat.BMA_BACKEND_AUTO):
         do_bf16 = None
         if be == nat.BMA_BACKEND_TCGEN05 and dO.dtype != torch.bfloat16:
             do_bf16 = torch.empty((B, N, Hq, d), dtype=torch.bfloat16, device=dev)
-        with _Span(_profile_sink, "bwd_preprocess", dev):
-            nat.check(lib.bma_attn_bwd_preprocess(C.byref(a), do_bf16.data_ptr() if do_bf16 is not None else None, st),
-                      "bma_attn_bwd_preprocess")
+        reuse = ctx.get("reuse")       # a dict the caller keeps for one (O, dO): delta and the bf16 cotangent are taken once
+        if reuse is not None and "delta" in reuse and (do_bf16 is None or reuse["do_bf16"] is not None):
+            delta, do_bf16 = reuse["delta"], (reuse["do_bf16"] if do_bf16 is not None else None)
+            a.delta = delta.data_ptr()
+        else:
+            with _Span(_profile_sink, "bwd_preprocess", dev):
+                nat.check(lib.bma_attn_bwd_preprocess(C.byref(a), do_bf16.data_ptr() if do_bf16 is not None else None, st),
+                          "bma_attn_bwd_preprocess")
+            if reuse is not None:
+                reuse["delta"], reuse["do_bf16"] = delta, do_bf16
         if do_bf16 is not None:
             a.d_o = _tensor(do_bf16)
         ws_bytes = lib.bma_attn_bwd_workspace_bytes(C.byref(a))

@@ -260,14 +260,16 @@ def ring_attention_forward(Q, K, V, *, rank: int, world: int, is_causal: bool = 
 # ring sequence partition (backward)
 # ---------------------------------------------------------------------------------------------
 
-def cuda_backward(Q, K, V, O, lse, dO, terms: _masks.MaskTerms):
+def cuda_backward(Q, K, V, O, lse, dO, terms: _masks.MaskTerms, reuse: Optional[dict] = None):
     """Gradients of one (query chunk, key chunk) pair on the CUDA kernels.  ``O`` and ``lse`` are
     the FINAL output and log-sum-exp of the local queries over the whole sequence, so that
     ``P = exp(s - lse)`` and ``delta = rowsum(dO * O)`` are the global quantities and the three
-    partial gradients simply add up over the key chunks."""
+    partial gradients simply add up over the key chunks.  ``reuse``: a dict kept by the caller per
+    query chunk — ``delta`` and the bf16 copy of ``dO`` depend on the queries only, so the first call
+    stores them there and the calls against the other key chunks skip the preprocess kernel."""
     from .attention import attention_backward
     dmask = _masks.to_device_mask(terms, Q.shape[1], K.shape[1], Q.device)
-    return attention_backward(Q, K, V, O, lse, dO, dict(dmask=dmask))
+    return attention_backward(Q, K, V, O, lse, dO, dict(dmask=dmask, reuse=reuse))
 
 
 def ring_attention_backward(Q, K, V, O, lse, dO, *, rank: int, world: int, is_causal: bool = False,
@@ -317,6 +319,7 @@ def ring_attention_backward(Q, K, V, O, lse, dO, *, rank: int, world: int, is_ca
     dq_acc = torch.zeros(Q.shape, dtype=torch.float32, device=Q.device)
     O, dO = O.contiguous(), dO.contiguous()
     incoming, acc_reqs = None, []
+    per_query_chunk, lse_chunks = {}, {}      # what depends on the local queries only is taken once, not once per step
     for s, owner in enumerate(ring_schedule(rank, world)):
         kv_next, kv_reqs = (None, [])
         if s + 1 < world:
@@ -328,8 +331,11 @@ def ring_attention_backward(Q, K, V, O, lse, dO, *, rank: int, world: int, is_ca
                 if _pair_is_empty(terms, qg, qn, kg, kn):
                     continue
                 qs, ks = slice(ql, ql + qn), slice(kl, kl + kn)
-                dq_s, dk_s, dv_s = backward(Q[:, qs], k_cur[:, ks], v_cur[:, ks], O[:, qs], lse[:, :, qs].contiguous(),
-                                            dO[:, qs], _step_terms(terms, qg, kg))
+                extra = dict(reuse=per_query_chunk.setdefault(ql, {})) if backward is cuda_backward else {}
+                if ql not in lse_chunks:
+                    lse_chunks[ql] = lse[:, :, qs].contiguous()
+                dq_s, dk_s, dv_s = backward(Q[:, qs], k_cur[:, ks], v_cur[:, ks], O[:, qs], lse_chunks[ql],
+                                            dO[:, qs], _step_terms(terms, qg, kg), **extra)
                 dq_acc[:, qs] += dq_s
                 if kl in written:
                     dk_part[:, ks] += dk_s
