@@ -156,9 +156,18 @@ def _failing_worker(rank, world, port, results, scenario):
     Q, K, V = (torch.from_numpy(rng.standard_normal((B, n, h, d))) for h in (Hq, Hkv, Hkv))
     t0 = time.monotonic()
     outcome = "completed"
-    if scenario == "absent_peer" and rank == 1:
+    if scenario in ("absent_peer", "absent_peer_backward") and rank == 1:
         time.sleep(6.0)                                                  # never posts its send
         outcome = "absent"
+    elif scenario == "absent_peer_backward":
+        # the backward posts its accumulators a step behind the tokens: its deadline must still end the very first wait
+        O = torch.zeros((B, n, Hq, d), dtype=torch.float64)
+        lse = torch.zeros((B, Hq, n), dtype=torch.float64)
+        try:
+            S.ring_attention_backward(Q, K, V, O, lse, torch.ones_like(O), rank=rank, world=world, terms=M.MaskTerms(causal=True),
+                                      backward=_oracle_backward, timeout_s=3.0)
+        except S.RingTransferError as e:
+            outcome = "RingTransferError: " + str(e)[:60]
     else:
         try:
             S.ring_attention_forward(Q, K, V, rank=rank, world=world, terms=M.MaskTerms(causal=True), attend=_oracle_attend,
@@ -169,7 +178,7 @@ def _failing_worker(rank, world, port, results, scenario):
     os._exit(0)      # a transfer may still be pending: leave without the collective teardown
 
 
-@pytest.mark.parametrize("scenario", ["wrong_size", "absent_peer"])
+@pytest.mark.parametrize("scenario", ["wrong_size", "absent_peer", "absent_peer_backward"])
 def test_ring_reports_a_failed_neighbour(scenario):
     world = 2
     with socket.socket() as s:
