@@ -541,17 +541,20 @@ def ring_entry(w, rank, world, local_rank, dev, dist, steps, warmup, ring="zigza
         O, lse = S.ring_attention_forward(Q, K, V, rank=rank, world=world, terms=terms, layout=layout, exchange=local)
         return S.ring_attention_backward(Q, K, V, O, lse, dO, rank=rank, world=world, terms=terms, layout=layout, exchange=local)
 
-    stub_o = torch.zeros((B, n // (2 if ring == "zigzag" else 1), H, d), dtype=torch.float32, device=dev)
-    stub_lse = torch.zeros((B, H, stub_o.shape[1]), dtype=torch.float32, device=dev)
-    stub_g = [torch.zeros((B, stub_o.shape[1], H, d), dtype=dt, device=dev) for _ in range(3)]
+    # stub results, cut to the shape of each call (a ring step joins segments into calls of n/2 or n tokens a side)
+    stub_o = torch.zeros((B, n, H, d), dtype=torch.float32, device=dev)
+    stub_lse = torch.zeros((B, H, n), dtype=torch.float32, device=dev)
+    stub_g = torch.zeros((B, n, H, d), dtype=dt, device=dev)
 
     def transfer_only():
         O, lse = S.ring_attention_forward(Q, K, V, rank=rank, world=world, terms=terms, layout=layout,
-                                          attend=lambda q, k, v, t: (stub_o, stub_lse), merge=lambda o, l, o2, l2: (o, l))
+                                          attend=lambda q, k, v, t: (stub_o[:, :q.shape[1]], stub_lse[:, :, :q.shape[1]]),
+                                          merge=lambda o, l, o2, l2: (o, l))
         O = torch.zeros((B, n, H, d), dtype=torch.float32, device=dev) if O.shape[1] != n else O
         lse = torch.zeros((B, H, n), dtype=torch.float32, device=dev) if lse.shape[2] != n else lse
         return S.ring_attention_backward(Q, K, V, O, lse, dO, rank=rank, world=world, terms=terms, layout=layout,
-                                         backward=lambda q, k, v, o, l, g, t: stub_g)
+                                         backward=lambda q, k, v, o, l, g, t: (stub_g[:, :q.shape[1]], stub_g[:, :k.shape[1]],
+                                                                               stub_g[:, :k.shape[1]]))
 
     def barrier():
         if dist is not None:

@@ -15,6 +15,7 @@ counterpart there.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from datetime import timedelta
 from typing import Callable, List, Optional, Tuple
 
@@ -160,6 +161,49 @@ def _pair_is_empty(terms: _masks.MaskTerms, q0: int, qn: int, k0: int, kn: int) 
     return False
 
 
+def _pair_is_full(terms: _masks.MaskTerms, q0: int, qn: int, k0: int, kn: int) -> bool:
+    """True when the mask consists of interval terms only and they allow every (q, k) of the pair."""
+    if terms.seg_q is not None or terms.bitmap is not None or terms.tiles is not None or terms.window is not None:
+        return False
+    q_lo, q_hi = terms.q_offset + q0, terms.q_offset + q0 + qn - 1
+    k_lo, k_hi = terms.k_offset + k0, terms.k_offset + k0 + kn - 1
+    if terms.causal and k_hi > q_lo:
+        return False
+    if terms.band is not None and (k_lo < q_hi - terms.band[0] or k_hi > q_lo + terms.band[1]):
+        return False
+    return True
+
+
+def _step_calls(terms: _masks.MaskTerms, q_segs, k_segs):
+    """The attention calls of one ring step: [(q local start, q length, k local start, k length, terms)].
+
+    One call per (query segment, key segment) pair that the mask does not empty, except that pairs the mask leaves
+    untouched are joined along the segment axis they share — segments lie back to back in the local buffers — into one
+    unmasked call: under a causal mask with the zig-zag layout every step but the first is then ONE call (both query
+    segments against the older visiting segment, or the later query segment against both visiting segments) instead
+    of two, with half the mask compiles, merges and accumulations."""
+    join = os.environ.get("BMA_RING_JOIN", "1") != "0"      # 0: one call per pair (for measurements)
+    state = [["empty" if _pair_is_empty(terms, qg, qn, kg, kn) else "full" if join and _pair_is_full(terms, qg, qn, kg, kn) else "cut"
+              for (_, kg, kn) in k_segs] for (_, qg, qn) in q_segs]
+    done = [[st == "empty" for st in row] for row in state]
+    calls, free = [], _masks.MaskTerms()
+    q_all = (q_segs[0][0], sum(n for _, _, n in q_segs))
+    for j, (kl, kg, kn) in enumerate(k_segs):            # every query segment sees this key segment whole
+        if len(q_segs) > 1 and all(state[i][j] == "full" for i in range(len(q_segs))):
+            calls.append((q_all[0], q_all[1], kl, kn, free))
+            for i in range(len(q_segs)):
+                done[i][j] = True
+    for i, (ql, qg, qn) in enumerate(q_segs):
+        rest = [j for j in range(len(k_segs)) if not done[i][j]]
+        if len(rest) > 1 and rest == list(range(rest[0], rest[-1] + 1)) and all(state[i][j] == "full" for j in rest):
+            calls.append((ql, qn, k_segs[rest[0]][0], sum(k_segs[j][2] for j in rest), free))
+            continue
+        for j in rest:
+            kl, kg, kn = k_segs[j]
+            calls.append((ql, qn, kl, kn, free if state[i][j] == "full" else _step_terms(terms, qg, kg)))
+    return calls
+
+
 class RingTransferError(RuntimeError):
     """A ring step could not complete: a neighbour holds a chunk of another shape, or a transfer did not finish
     within the deadline (a rank that died, left, or never entered the call)."""
@@ -238,12 +282,15 @@ def ring_attention_forward(Q, K, V, *, rank: int, world: int, is_causal: bool = 
                 ops = [dist.P2POp(dist.isend, k_cur, dst, group), dist.P2POp(dist.isend, v_cur, dst, group),
                        dist.P2POp(dist.irecv, k_nxt, src, group), dist.P2POp(dist.irecv, v_nxt, src, group)]
                 reqs = dist.batch_isend_irecv(ops)
-        for i, (ql, qg, qn) in enumerate(q_segs):
-            for kl, kg, kn in _segments(layout, owner, world):
-                if _pair_is_empty(terms, qg, qn, kg, kn):
+        for ql, qn, kl, kn, call_terms in _step_calls(terms, q_segs, _segments(layout, owner, world)):
+            O_s, lse_s = attend(Q[:, ql:ql + qn], k_cur[:, kl:kl + kn], v_cur[:, kl:kl + kn], call_terms)
+            for i, (sl, _, sn) in enumerate(q_segs):     # a call may cover several local query segments
+                if not ql <= sl < ql + qn:
                     continue
-                O_s, lse_s = attend(Q[:, ql:ql + qn], k_cur[:, kl:kl + kn], v_cur[:, kl:kl + kn], _step_terms(terms, qg, kg))
-                parts[i] = (O_s, lse_s) if parts[i] is None else merge(parts[i][0], parts[i][1], O_s, lse_s)
+                whole = (sl, sn) == (ql, qn)
+                O_i = O_s if whole else O_s[:, sl - ql:sl - ql + sn]
+                lse_i = lse_s if whole else lse_s[:, :, sl - ql:sl - ql + sn].contiguous()
+                parts[i] = (O_i, lse_i) if parts[i] is None else merge(parts[i][0], parts[i][1], O_i, lse_i)
         _wait_all(reqs, timeout_s, f"rank {rank}: K/V rotation, ring step {s}")
         if s + 1 < world:
             k_cur, v_cur = k_nxt, v_nxt
@@ -326,25 +373,28 @@ def ring_attention_backward(Q, K, V, O, lse, dO, *, rank: int, world: int, is_ca
             kv_next, kv_reqs = start([k_cur, v_cur], kv_bufs[s & 1] if own else None)
         dk_part, dv_part = part_bufs[s % len(part_bufs)]
         written = set()
-        for ql, qg, qn in q_segs:
-            for kl, kg, kn in _segments(layout, owner, world):
-                if _pair_is_empty(terms, qg, qn, kg, kn):
+        k_segs = _segments(layout, owner, world)
+        for ql, qn, kl, kn, call_terms in _step_calls(terms, q_segs, k_segs):
+            qs, ks = slice(ql, ql + qn), slice(kl, kl + kn)
+            key = (ql, qn)
+            extra = dict(reuse=per_query_chunk.setdefault(key, {})) if backward is cuda_backward else {}
+            if key not in lse_chunks:
+                lse_chunks[key] = lse[:, :, qs].contiguous()
+            dq_s, dk_s, dv_s = backward(Q[:, qs], k_cur[:, ks], v_cur[:, ks], O[:, qs], lse_chunks[key],
+                                        dO[:, qs], call_terms, **extra)
+            dq_acc[:, qs] += dq_s
+            for sl, _, sn in k_segs:                     # a call may cover several visiting key segments
+                if not kl <= sl < kl + kn:
                     continue
-                qs, ks = slice(ql, ql + qn), slice(kl, kl + kn)
-                extra = dict(reuse=per_query_chunk.setdefault(ql, {})) if backward is cuda_backward else {}
-                if ql not in lse_chunks:
-                    lse_chunks[ql] = lse[:, :, qs].contiguous()
-                dq_s, dk_s, dv_s = backward(Q[:, qs], k_cur[:, ks], v_cur[:, ks], O[:, qs], lse_chunks[ql],
-                                            dO[:, qs], _step_terms(terms, qg, kg), **extra)
-                dq_acc[:, qs] += dq_s
-                if kl in written:
-                    dk_part[:, ks] += dk_s
-                    dv_part[:, ks] += dv_s
+                sub = slice(sl - kl, sl - kl + sn)
+                if sl in written:
+                    dk_part[:, sl:sl + sn] += dk_s[:, sub]
+                    dv_part[:, sl:sl + sn] += dv_s[:, sub]
                 else:          # the first contribution to these tokens in this step: no zero-fill, no read
-                    dk_part[:, ks].copy_(dk_s)
-                    dv_part[:, ks].copy_(dv_s)
-                    written.add(kl)
-        for kl, kg, kn in _segments(layout, owner, world):
+                    dk_part[:, sl:sl + sn].copy_(dk_s[:, sub])
+                    dv_part[:, sl:sl + sn].copy_(dv_s[:, sub])
+                    written.add(sl)
+        for kl, kg, kn in k_segs:
             if kl not in written:
                 dk_part[:, kl:kl + kn].zero_()
                 dv_part[:, kl:kl + kn].zero_()

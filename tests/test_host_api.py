@@ -194,3 +194,37 @@ def test_mask_caches_and_scratch_knobs():
         assert not A._scratch_buffers
     finally:
         A.set_backward_scratch_limit(limit, frac)
+
+
+def test_ring_step_calls_join_untouched_segment_pairs():
+    """Zig-zag layout under a causal mask: the first ring step is two diagonal calls plus one unmasked call, every later
+    step ONE unmasked call over two segments; the joined calls cover exactly the pairs the mask does not empty."""
+    from jaxmodules_b200 import sharding as S
+    world, n = 4, 64
+    layout = S.zigzag_layout(n)
+    for terms in (M.MaskTerms(causal=True), M.MaskTerms(band=(40, 8)), M.MaskTerms(causal=True, band=(70, 1 << 20))):
+        for rank in range(world):
+            q_segs = S._segments(layout, rank, world)
+            for s, owner in enumerate(S.ring_schedule(rank, world)):
+                k_segs = S._segments(layout, owner, world)
+                calls = S._step_calls(terms, q_segs, k_segs)
+                if terms.causal and terms.band is None:
+                    assert len(calls) == (3 if s == 0 else 1)
+                    assert all(not c[4].causal for c in calls) == (s > 0)
+                covered = set()
+                for ql, qn, kl, kn, t in calls:
+                    for sl, sg, sn in q_segs:
+                        for tl, tg, tn in k_segs:
+                            if ql <= sl < ql + qn and kl <= tl < kl + kn:
+                                assert (sl, tl) not in covered
+                                covered.add((sl, tl))
+                                if not (t.causal or t.band):     # an unmasked call: the mask must leave the pair whole
+                                    assert S._pair_is_full(terms, sg, sn, tg, tn)
+                                else:                            # a masked call is one pair with its global offsets
+                                    assert (qn, kn) == (sn, tn) and (t.q_offset, t.k_offset) == (sg, tg)
+                want = {(sl, tl) for sl, sg, sn in q_segs for tl, tg, tn in k_segs if not S._pair_is_empty(terms, sg, sn, tg, tn)}
+                assert covered == want
+    # masks with table or segment terms are never joined into unmasked calls
+    seg = torch.zeros((1, 4 * n), dtype=torch.int32)
+    t = M.MaskTerms(causal=True, seg_q=seg, seg_k=seg)
+    assert not S._pair_is_full(t, 128, 32, 0, 32)
